@@ -1,0 +1,94 @@
+"""ctypes access to the in-tree native libraries.
+
+``cpu()`` returns ``libzc_cpu.so`` (built on first use with g++ when missing).  ``cuda()`` returns
+``libzc_cuda.so``; when a CUDA device is present and the library is missing it is built with nvcc
+or the call fails loudly -- kernels never fall back to eager PyTorch on a GPU box.
+"""
+from __future__ import annotations
+
+import ctypes
+import threading
+from ctypes import c_int, c_int64, c_void_p, c_float, c_double, c_uint64
+from pathlib import Path
+
+import torch
+
+from . import _build
+
+_LOCK = threading.Lock()
+_CPU = None
+_CUDA = None
+
+P = c_void_p
+I = c_int
+L = c_int64
+F = c_float
+
+
+def _sig(fn, restype, *argtypes):
+    fn.restype = restype
+    fn.argtypes = list(argtypes)
+
+
+def cpu() -> ctypes.CDLL:
+    global _CPU
+    if _CPU is None:
+        with _LOCK:
+            if _CPU is None:
+                path = _build.LIB / "libzc_cpu.so"
+                if not path.exists():
+                    _build.build_cpu()
+                lib = ctypes.CDLL(str(path))
+                _sig(lib.zc_cpu_v1_det_bytes, L, L)
+                _sig(lib.zc_cpu_v1_encode_split, None, P, L, P, P, I, I, P, P, P)
+                _sig(lib.zc_cpu_v1_decode_split, None, P, P, P, P, I, L, P, P, P)
+                _sig(lib.zc_cpu_v1_encode_fused, L, P, L, P, I, I, P, P, P)
+                _sig(lib.zc_cpu_v1_decode_fused, None, P, P, P, I, L, P)
+                _sig(lib.zc_cpu_v2_encode, L, P, L, P, P)
+                _sig(lib.zc_cpu_v2_decode, None, P, P, L, P)
+                _sig(lib.zc_cpu_v2_compact, L, P, P, L, P, P)
+                _sig(lib.zc_cpu_v2_expand, None, P, P, L, P)
+                _CPU = lib
+    return _CPU
+
+
+def cuda_available() -> bool:
+    return torch.cuda.is_available()
+
+
+def cuda_lib_path() -> Path:
+    return _build.LIB / "libzc_cuda.so"
+
+
+def cuda() -> ctypes.CDLL:
+    """The CUDA kernel library.  Raises when it cannot be loaded."""
+    global _CUDA
+    if _CUDA is None:
+        with _LOCK:
+            if _CUDA is None:
+                path = cuda_lib_path()
+                if not path.exists():
+                    built = _build.build_cuda()
+                    if built is None:
+                        raise RuntimeError(
+                            "libzc_cuda.so is missing and nvcc was not found; run "
+                            "`python -m fsdp_comm_opt_b200._build` on a host with the CUDA toolkit")
+                lib = ctypes.CDLL(str(path))
+                from . import _cuda_sigs
+
+                _cuda_sigs.declare(lib)
+                _CUDA = lib
+    return _CUDA
+
+
+def ptr(t: torch.Tensor | None) -> int | None:
+    return None if t is None else t.data_ptr()
+
+
+def stream_ptr(device=None) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def check(code: int, what: str) -> None:
+    if code != 0:
+        raise RuntimeError(f"{what} failed with native status {code}")
