@@ -1,0 +1,107 @@
+"""GPT-2-shape decoder (LayerNorm, learned positions, biased projections, tanh-GELU MLP, tied
+output embedding): the family of the reference's shipped run (run.sh:1, GPT-2-XL), discovered by
+the reference at ``model.transformer.h`` (train.py:99-100).  Attention, GEMMs, loss and the
+optimizer are the package's own ops; LayerNorm, GELU and bias adds use PyTorch elementwise ops.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+from torch.utils.checkpoint import checkpoint
+
+from ..ops import attention as attn_ops
+from ..ops import gemm, loss as loss_ops
+from .config import ModelConfig
+from .llama import CausalLMOutput
+
+
+class BiasLinear(nn.Module):
+    def __init__(self, in_features: int, out_features: int, init_std: float):
+        super().__init__()
+        self.init_std = init_std
+        self.weight = nn.Parameter(torch.empty(out_features, in_features))
+        self.bias = nn.Parameter(torch.empty(out_features))
+
+    def reset_parameters(self):
+        nn.init.normal_(self.weight, mean=0.0, std=self.init_std)
+        nn.init.zeros_(self.bias)
+
+    def forward(self, x):
+        return gemm.linear(x, self.weight) + self.bias.to(x.dtype)
+
+
+class GPT2Block(nn.Module):
+    def __init__(self, cfg: ModelConfig):
+        super().__init__()
+        self.cfg = cfg
+        d = cfg.d_model
+        self.c_attn = BiasLinear(d, 3 * d, cfg.init_std)
+        self.c_proj = BiasLinear(d, d, cfg.init_std)
+        self.c_fc = BiasLinear(d, cfg.ffn, cfg.init_std)
+        self.c_mlp_proj = BiasLinear(cfg.ffn, d, cfg.init_std)
+        self.ln_1 = nn.LayerNorm(d, eps=cfg.norm_eps)
+        self.ln_2 = nn.LayerNorm(d, eps=cfg.norm_eps)
+
+    def forward(self, x):
+        cfg = self.cfg
+        B, S, d = x.shape
+        H, hd = cfg.n_heads, cfg.head_dim
+        qkv = self.c_attn(self.ln_1(x)).view(B, S, 3 * H, hd)
+        if x.is_cuda and hd not in (64, 128):
+            q, k, v = (t.transpose(1, 2) for t in qkv.split(H, dim=2))
+            o = F.scaled_dot_product_attention(q, k, v, is_causal=True).transpose(1, 2).reshape(B, S, d)
+        else:
+            o = attn_ops.causal_attention(qkv, H, H).view(B, S, d)
+        x = x + self.c_proj(o)
+        h = F.gelu(self.c_fc(self.ln_2(x)), approximate="tanh")
+        return x + self.c_mlp_proj(h)
+
+
+class GPT2Backbone(nn.Module):
+    def __init__(self, cfg: ModelConfig):
+        super().__init__()
+        self._std = cfg.init_std
+        self.wte = nn.Embedding(cfg.vocab_size, cfg.d_model)
+        self.wpe = nn.Embedding(cfg.max_seq, cfg.d_model)
+        self.h = nn.ModuleList(GPT2Block(cfg) for _ in range(cfg.n_layers))
+        self.ln_f = nn.LayerNorm(cfg.d_model, eps=cfg.norm_eps)
+
+    def reset_parameters(self):
+        nn.init.normal_(self.wte.weight, mean=0.0, std=self._std)
+        nn.init.normal_(self.wpe.weight, mean=0.0, std=self._std)
+
+
+class GPT2ForCausalLM(nn.Module):
+    def __init__(self, cfg: ModelConfig):
+        super().__init__()
+        self.config = cfg
+        self.transformer = GPT2Backbone(cfg)
+        self.activation_checkpointing = False
+
+    def init_weights(self):
+        self.apply(lambda m: m.reset_parameters() if hasattr(m, "reset_parameters") else None)
+
+    def forward(self, input_ids: torch.Tensor, labels: Optional[torch.Tensor] = None,
+                return_logits: bool = False, **_ignored) -> CausalLMOutput:
+        B, S = input_ids.shape
+        t = self.transformer
+        pos = torch.arange(S, device=input_ids.device)
+        x = t.wte(input_ids) + t.wpe(pos)[None]
+        for blk in t.h:
+            if self.activation_checkpointing and torch.is_grad_enabled():
+                x = checkpoint(blk, x, use_reentrant=False)
+            else:
+                x = blk(x)
+        x = t.ln_f(x)
+        logits = gemm.linear(x, t.wte.weight)  # tied output embedding
+        loss = None
+        if labels is not None:
+            shifted = torch.full_like(labels, loss_ops.IGNORE_INDEX)
+            shifted[:, :-1] = labels[:, 1:]
+            keep = logits.detach().clone() if return_logits else None
+            loss = loss_ops.cross_entropy(logits.view(B * S, -1), shifted.reshape(-1))
+            logits = keep
+        return CausalLMOutput(loss=loss, logits=logits)

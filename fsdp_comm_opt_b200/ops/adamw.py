@@ -1,0 +1,85 @@
+"""Fused AdamW on the local shards of FSDP2 parameters.
+
+``FusedAdamW`` keeps the state layout of ``torch.optim.AdamW`` (``step``, ``exp_avg``,
+``exp_avg_sq`` per parameter, DTensor-sharded like the parameter), so
+``torch.distributed.checkpoint.state_dict.get_state_dict`` / ``set_state_dict`` work unchanged
+and checkpoints are interchangeable with the reference's optimizer
+(reference: train.py:146 ``torch.optim.AdamW(..., fused=True)``).
+
+On CUDA each shard is updated by one launch of ``zc_adamw`` (one read of p, g, m, v and one write
+of p, m, v; bias correction and decoupled weight decay folded in; optional gradient zeroing in the
+same pass).  CPU tensors use the same arithmetic in PyTorch.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from .. import _lib
+
+_DT = {torch.bfloat16: 0, torch.float32: 1, torch.float16: 2}
+
+
+def _local(t: torch.Tensor) -> torch.Tensor:
+    return t._local_tensor if hasattr(t, "_local_tensor") else t
+
+
+class FusedAdamW(torch.optim.Optimizer):
+    def __init__(self, params, lr: float = 1e-3, betas=(0.9, 0.999), eps: float = 1e-8,
+                 weight_decay: float = 1e-2, zero_grad_in_step: bool = False):
+        if lr < 0 or eps < 0 or not 0 <= betas[0] < 1 or not 0 <= betas[1] < 1:
+            raise ValueError("invalid AdamW hyper-parameters")
+        defaults = dict(lr=lr, betas=betas, eps=eps, weight_decay=weight_decay)
+        super().__init__(params, defaults)
+        self.zero_grad_in_step = zero_grad_in_step
+        self.kernel_launches = 0
+
+    @torch.no_grad()
+    def step(self, closure=None):
+        loss = None
+        if closure is not None:
+            with torch.enable_grad():
+                loss = closure()
+        for group in self.param_groups:
+            lr = group["lr"]
+            lr = float(lr) if not isinstance(lr, torch.Tensor) else float(lr.item())
+            b1, b2 = group["betas"]
+            eps, wd = group["eps"], group["weight_decay"]
+            for p in group["params"]:
+                if p.grad is None:
+                    continue
+                st = self.state[p]
+                if len(st) == 0:
+                    st["step"] = torch.zeros((), dtype=torch.float32)
+                    st["exp_avg"] = torch.zeros_like(p, memory_format=torch.preserve_format)
+                    st["exp_avg_sq"] = torch.zeros_like(p, memory_format=torch.preserve_format)
+                st["step"] += 1
+                step = int(st["step"].item())  # CPU scalar tensor: no device sync
+                bc1 = 1.0 - b1 ** step
+                bc2 = 1.0 - b2 ** step
+                pl, gl = _local(p), _local(p.grad)
+                ml, vl = _local(st["exp_avg"]), _local(st["exp_avg_sq"])
+                if pl.numel() == 0:
+                    continue
+                if pl.is_cuda:
+                    if not (pl.is_contiguous() and gl.is_contiguous()):
+                        raise ValueError("FusedAdamW needs contiguous shards")
+                    _lib.check(_lib.cuda().zc_adamw(
+                        pl.data_ptr(), gl.data_ptr(), ml.data_ptr(), vl.data_ptr(), pl.numel(),
+                        _DT[pl.dtype], _DT[gl.dtype], _DT[ml.dtype], float(lr), float(b1), float(b2),
+                        float(eps), float(wd), float(bc1), float(bc2), int(self.zero_grad_in_step),
+                        _lib.stream_ptr(pl.device)), "zc_adamw")
+                    self.kernel_launches += 1
+                else:
+                    g = gl.float()
+                    pf = pl.float()
+                    m = ml.float().mul_(b1).add_(g, alpha=1 - b1)
+                    v = vl.float().mul_(b2).addcmul_(g, g, value=1 - b2)
+                    pf.mul_(1 - lr * wd)
+                    denom = (v.sqrt() / math.sqrt(bc2)).add_(eps)
+                    pf.addcdiv_(m, denom, value=-lr / bc1)
+                    pl.copy_(pf), ml.copy_(m), vl.copy_(v)
+                    if self.zero_grad_in_step:
+                        gl.zero_()
+        return loss

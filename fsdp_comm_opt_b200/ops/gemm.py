@@ -1,0 +1,102 @@
+"""bf16 linear layers: ``linear(x, w) = x @ w^T`` with the three GEMMs of training.
+
+Backends (``set_backend``):
+  ``"tcgen05"``  the hand-written sm_100a kernel in ``csrc/gemm_tcgen05.cu``: TMA loads into
+                 128B-swizzled shared memory, ``tcgen05.mma`` with TMEM accumulators issued by one
+                 elected thread, warp-specialised producer / MMA / epilogue, persistent over tiles.
+                 Forward uses K-major operands; dgrad and wgrad use the MN-major descriptor forms,
+                 so no transposed copy of the weight or the activations is made.
+  ``"cublas"``   ``torch.matmul`` (cuBLASLt), the plain library GEMM.
+  ``"auto"``     tcgen05 where the shape is supported (all dims multiples of the tile constraints),
+                 cuBLAS otherwise.
+CPU tensors always use ``torch.matmul``.
+"""
+from __future__ import annotations
+
+import os
+
+import torch
+
+from .. import _lib
+
+_BACKEND = os.environ.get("ZC_GEMM_BACKEND", "auto")
+
+
+def set_backend(name: str) -> None:
+    global _BACKEND
+    if name not in ("auto", "tcgen05", "cublas"):
+        raise ValueError(name)
+    _BACKEND = name
+
+
+def get_backend() -> str:
+    return _BACKEND
+
+
+def _tc_ok(M: int, N: int, K: int) -> bool:
+    return M % 128 == 0 and N % 128 == 0 and K % 64 == 0 and M > 0 and N > 0 and K > 0
+
+
+def _use_tc(a: torch.Tensor, M: int, N: int, K: int) -> bool:
+    if not a.is_cuda or a.dtype != torch.bfloat16 or _BACKEND == "cublas":
+        return False
+    ok = _tc_ok(M, N, K)
+    if _BACKEND == "tcgen05" and not ok:
+        return False
+    return ok
+
+
+def gemm(a: torch.Tensor, b: torch.Tensor, trans_a: bool, trans_b: bool,
+         out: torch.Tensor | None = None, accumulate: bool = False) -> torch.Tensor:
+    """C[M,N] (+)= op(A) @ op(B) for row-major 2-D bf16 tensors.
+
+    op(A) is A ``[M,K]`` (or A^T of a stored ``[K,M]`` when ``trans_a``); op(B) is B ``[K,N]`` (or
+    B^T of a stored ``[N,K]`` when ``trans_b``).
+    """
+    M, K = (a.shape[1], a.shape[0]) if trans_a else (a.shape[0], a.shape[1])
+    N = b.shape[0] if trans_b else b.shape[1]
+    if _use_tc(a, M, N, K) and a.is_contiguous() and b.is_contiguous():
+        if out is None:
+            out = torch.empty(M, N, dtype=a.dtype, device=a.device)
+            accumulate = False
+        _lib.check(_lib.cuda().zc_gemm_bf16(
+            a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, int(trans_a), int(trans_b),
+            int(accumulate), _lib.stream_ptr(a.device)), "zc_gemm_bf16")
+        return out
+    A = a.t() if trans_a else a
+    B = b.t() if trans_b else b
+    if out is None:
+        return torch.matmul(A, B)
+    if accumulate:
+        return out.addmm_(A, B)
+    return torch.matmul(A, B, out=out)
+
+
+class _Linear(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w):
+        ctx.save_for_backward(x, w)
+        x2 = x.reshape(-1, x.shape[-1])
+        y = gemm(x2, w, False, True)           # [T,K] @ [N,K]^T
+        return y.view(*x.shape[:-1], w.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w = ctx.saved_tensors
+        x2 = x.reshape(-1, x.shape[-1])
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            dx = gemm(dy2, w, False, False).view(x.shape)      # [T,N] @ [N,K]
+        if ctx.needs_input_grad[1]:
+            dw = gemm(dy2, x2, True, False)                    # [T,N]^T @ [T,K]
+        return dx, dw
+
+
+def linear(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """``x [..., K] @ w[N, K]^T`` without bias."""
+    if x.dtype != w.dtype:
+        w = w.to(x.dtype)
+    return _Linear.apply(x, w)

@@ -1,0 +1,80 @@
+"""FSDP2 wrapping: the one parallelism strategy (ZeRO-3 style full-shard data parallel).
+
+``apply_fsdp`` reproduces the reference's wrapping (reference: train.py:93-123): every decoder
+layer becomes its own FSDP2 group with ``reshard_after_forward=True`` and a bf16-compute /
+fp32-reduce mixed-precision policy, then the root module is wrapped; layer i explicitly prefetches
+layers i+1..i+distance in forward; a fresh comm hook instance is installed per FSDP module.
+On top of the reference: a gradient reduce-scatter hook, a choice of reduce dtype, and
+activation checkpointing per block.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Optional
+
+import torch
+from torch.distributed.fsdp import CPUOffloadPolicy, FSDPModule, MixedPrecisionPolicy, fully_shard
+
+from ..models import decoder_layers
+from .hooks import QuantizedAllGather, ZipCCLAllGather, ZipCCLReduceScatter
+
+
+@dataclass
+class FSDPPlan:
+    quantize: bool = False            # -q: install a custom all-gather (int8 unless zip_ccl)
+    zip_ccl: bool = False             # --zip-ccl: lossless compressed all-gather
+    compress_rs: bool = False         # --compress-rs: compressed reduce-scatter with error feedback
+    cpu_offload: bool = False
+    forward_prefetch_distance: int = 1
+    param_dtype: torch.dtype = torch.bfloat16
+    reduce_dtype: torch.dtype = torch.float32
+    transport: str = "auto"
+    codec_version: str = "auto"
+    error_feedback: bool = True
+    act_ckpt: bool = False
+    mesh: Optional[object] = None
+    rs_hooks: list = field(default_factory=list)
+    ag_hooks: list = field(default_factory=list)
+
+
+def _install_hooks(m: FSDPModule, plan: FSDPPlan) -> None:
+    if plan.quantize:
+        if plan.zip_ccl:
+            hook = ZipCCLAllGather(codec_version=plan.codec_version, transport=plan.transport)
+        else:
+            hook = QuantizedAllGather(transport=plan.transport)
+        m.set_custom_all_gather(hook)
+        plan.ag_hooks.append(hook)
+    if plan.compress_rs:
+        rs = ZipCCLReduceScatter(error_feedback=plan.error_feedback, reduce_dtype=plan.reduce_dtype,
+                                 transport=plan.transport)
+        m.set_custom_reduce_scatter(rs)
+        plan.rs_hooks.append(rs)
+
+
+def apply_fsdp(model: torch.nn.Module, plan: FSDPPlan) -> torch.nn.Module:
+    cfg = dict(
+        reshard_after_forward=True,
+        offload_policy=CPUOffloadPolicy() if plan.cpu_offload else None,
+        mp_policy=MixedPrecisionPolicy(param_dtype=plan.param_dtype, reduce_dtype=plan.reduce_dtype),
+    )
+    if cfg["offload_policy"] is None:
+        del cfg["offload_policy"]
+    if plan.mesh is not None:
+        cfg["mesh"] = plan.mesh
+    layers = decoder_layers(model)
+    fsdp_layers = []
+    for layer in layers:
+        m = fully_shard(layer, **cfg)
+        fsdp_layers.append(m)
+        _install_hooks(m, plan)
+    if plan.forward_prefetch_distance > 0:
+        for i, m in enumerate(fsdp_layers):
+            nxt = fsdp_layers[i + 1: i + 1 + plan.forward_prefetch_distance]
+            if nxt:
+                m.set_modules_to_forward_prefetch(nxt)
+    root = fully_shard(model, **cfg)
+    _install_hooks(root, plan)
+    if plan.act_ckpt:
+        model.activation_checkpointing = True
+    return root

@@ -1,0 +1,234 @@
+"""FSDP2 training entry point with compressed collectives.
+
+Keeps every flag of the reference script (reference: train.py:426-448) and its loop structure
+(reference: train.py:229-311: ``model.unshard()`` -> batch to device -> forward -> backward ->
+optimizer / LR step -> zero_grad -> profiler step -> logging -> checkpoint), and adds
+
+  --synthetic / --model-shape   build a named shape locally and train on random tokens
+                                (the reference needs the HF hub for config, tokenizer and data)
+  --device {auto,cuda,cpu}      CPU runs use gloo and the scalar codec
+  --compress-rs                 compressed gradient reduce-scatter with error feedback
+  --act-ckpt                    activation checkpointing per decoder block
+  --steps N                     stop after N optimizer steps
+  --transport / --codec         symm | lib | auto,  v1 | v2 | auto
+  --master-dtype fp32           keep fp32 master weights (communication stays bf16)
+
+Launch: ``torchrun --nproc-per-node N --master-addr 127.0.0.1 train.py --synthetic ...``.
+"""
+from __future__ import annotations
+
+import argparse
+import contextlib
+import os
+from pathlib import Path
+
+import torch
+from torch import distributed as dist
+from torch.distributed.elastic.multiprocessing.errors import record
+from torch.profiler import ProfilerActivity
+from torch.utils.data import DataLoader
+from torch.utils.data.distributed import DistributedSampler
+
+from fsdp_comm_opt_b200.models import build_model, get_config
+from fsdp_comm_opt_b200.ops.adamw import FusedAdamW
+from fsdp_comm_opt_b200.parallel.fsdp import FSDPPlan, apply_fsdp
+from fsdp_comm_opt_b200.utils import checkpoint as ckpt
+from fsdp_comm_opt_b200.utils.data import SyntheticTokens, collate, load_text_dataset
+from fsdp_comm_opt_b200.utils.dist import all_reduce_max, init_distributed, rank0_first
+from fsdp_comm_opt_b200.utils.failure import Heartbeat
+from fsdp_comm_opt_b200.utils.metrics import get_mem_stats, setup_logging
+from fsdp_comm_opt_b200.utils.timing import LocalTimer
+
+
+def _get_parser() -> argparse.ArgumentParser:
+    p = argparse.ArgumentParser()
+    # reference flags
+    p.add_argument("-e", "--experiment-name", default=None)
+    p.add_argument("-d", "--dataset-name", default=None)
+    p.add_argument("--dataset-subset", default=None)
+    p.add_argument("-m", "--model-name", default=None)
+    p.add_argument("--save-dir", default="../outputs")
+    p.add_argument("--seed", default=0, type=int)
+    p.add_argument("--num-epochs", default=100, type=int)
+    p.add_argument("--lr", default=3e-5, type=float)
+    p.add_argument("-b", "--batch-size", default=1, type=int)
+    p.add_argument("--log-freq", default=10, type=int)
+    p.add_argument("--ckpt-freq", default=500, type=int)
+    p.add_argument("-s", "--seq-length", default=1024, type=int)
+    p.add_argument("--cpu-offload", default=False, action="store_true")
+    p.add_argument("-p", "--profiler", default=False, action="store_true")
+    p.add_argument("--profiler-wait", default=10, type=int)
+    p.add_argument("--profiler-warmup", default=5, type=int)
+    p.add_argument("--profiler-active", default=2, type=int)
+    p.add_argument("--forward-prefetch-distance", default=1, type=int)
+    p.add_argument("-q", "--quantize", default=False, action="store_true")
+    p.add_argument("--zip-ccl", default=False, action="store_true")
+    # additions
+    p.add_argument("--synthetic", default=False, action="store_true")
+    p.add_argument("--model-shape", default=None, help="tiny | small | llama3-8b | llama2-13b | 34b | gpt2-tiny | gpt2-xl")
+    p.add_argument("--device", default="auto", choices=["auto", "cuda", "cpu"])
+    p.add_argument("--compress-rs", default=False, action="store_true")
+    p.add_argument("--no-error-feedback", default=False, action="store_true")
+    p.add_argument("--act-ckpt", default=False, action="store_true")
+    p.add_argument("--steps", default=None, type=int)
+    p.add_argument("--transport", default="auto", choices=["auto", "symm", "lib"])
+    p.add_argument("--codec", default="auto", choices=["auto", "v1", "v2"])
+    p.add_argument("--master-dtype", default="bf16", choices=["bf16", "fp32"])
+    p.add_argument("--num-samples", default=1 << 14, type=int, help="synthetic dataset length")
+    p.add_argument("--heartbeat-timeout", default=0.0, type=float,
+                   help="> 0: ranks publish a heartbeat each step and abort when a peer is silent that long")
+    p.add_argument("--loss-log", default=None, help="rank 0 appends 'step loss' lines to this file")
+    return p
+
+
+@record
+def main(argv=None):
+    args = _get_parser().parse_args(argv)
+    if not args.synthetic and (args.dataset_name is None or args.model_name is None):
+        raise SystemExit("either --synthetic with --model-shape, or -d/--dataset-name and -m/--model-name")
+
+    rank, world_size, device = init_distributed(args.device)
+    local_rank = device.index or 0
+    LOGGER = setup_logging(rank)
+    LOGGER.debug(os.environ)
+    LOGGER.debug(args)
+
+    master_dtype = torch.bfloat16 if args.master_dtype == "bf16" else torch.float32
+    torch.manual_seed(args.seed)
+
+    # ---- model on the meta device (no memory), FSDP wrap, then materialise shards -------------
+    shape_name = args.model_shape or args.model_name
+    cfg = get_config(shape_name)
+    with torch.device("meta"):
+        model = build_model(cfg).to(master_dtype)
+    LOGGER.info(f"Training {sum(p.numel() for p in model.parameters())} model parameters")
+
+    plan = FSDPPlan(
+        quantize=args.quantize, zip_ccl=args.zip_ccl, compress_rs=args.compress_rs,
+        cpu_offload=args.cpu_offload, forward_prefetch_distance=args.forward_prefetch_distance,
+        transport=args.transport, codec_version=args.codec, error_feedback=not args.no_error_feedback,
+        act_ckpt=args.act_ckpt)
+    apply_fsdp(model, plan)
+    model.to_empty(device="cpu" if args.cpu_offload else device)
+    model.init_weights()
+    LOGGER.info(f"Initialized model uses {get_mem_stats(device)['curr_alloc_gb']}gb")
+
+    # ---- data ---------------------------------------------------------------------------------
+    if args.synthetic:
+        train_data = SyntheticTokens(cfg.vocab_size, args.seq_length, args.num_samples, args.seed)
+    else:
+        with rank0_first():
+            train_data = load_text_dataset(args.dataset_name, args.dataset_subset, args.model_name,
+                                           args.seq_length, cfg.max_seq)
+    dataloader = DataLoader(train_data, batch_size=args.batch_size, collate_fn=collate,
+                            sampler=DistributedSampler(train_data, shuffle=True, drop_last=True))
+    LOGGER.debug(f"{len(dataloader)} batches per epoch")
+
+    optimizer = FusedAdamW(model.parameters(), lr=args.lr)
+    lr_scheduler = torch.optim.lr_scheduler.CosineAnnealingLR(optimizer, T_max=1000, eta_min=args.lr * 1e-2)
+
+    # ---- experiment directory / resume --------------------------------------------------------
+    is_experiment = args.experiment_name is not None
+    exp_dir = Path(args.save_dir)
+    if is_experiment:
+        exp_dir = exp_dir / args.experiment_name
+    state = {"epoch": 0, "global_step": 0, "epoch_step": 0, "running_loss": 0}
+    resumed = False
+    if is_experiment:
+        loaded = ckpt.try_resume(exp_dir, model, optimizer, lr_scheduler, device, plan.rs_hooks)
+        if loaded is not None:
+            state, resumed = loaded, True
+        LOGGER.info(f"Resumed={resumed} | {state}")
+    dist.barrier()
+    if is_experiment and ((exp_dir.is_mount() and rank == 0) or (not exp_dir.is_mount() and local_rank == 0)):
+        exp_dir.mkdir(parents=True, exist_ok=True)
+    dist.barrier()
+    if is_experiment:
+        (exp_dir / f"rank-{rank}").mkdir(parents=True, exist_ok=True)
+
+    timers = {k: LocalTimer(device) for k in ["data", "forward", "backward", "update"]}
+    heartbeat = Heartbeat.from_default_store(rank, world_size, args.heartbeat_timeout) if args.heartbeat_timeout > 0 else None
+
+    activities = [ProfilerActivity.CPU] + ([ProfilerActivity.CUDA] if device.type == "cuda" else [])
+    prof_ctx = torch.profiler.profile(
+        activities=activities,
+        schedule=torch.profiler.schedule(wait=args.profiler_wait, warmup=args.profiler_warmup,
+                                         active=args.profiler_active, repeat=1),
+        on_trace_ready=torch.profiler.tensorboard_trace_handler(str(exp_dir / "log" / f"rank-{rank}")),
+        record_shapes=False, with_stack=False, profile_memory=False, with_modules=False,
+    ) if args.profiler else contextlib.nullcontext()
+
+    done = False
+    with prof_ctx as prof:
+        for state["epoch"] in range(state["epoch"], args.num_epochs):
+            LOGGER.info(f"Begin epoch {state['epoch']} at step {state['epoch_step']}")
+            dataloader.sampler.set_epoch(state["epoch"])
+            batches = iter(dataloader)
+            for i_step in range(len(dataloader)):
+                if heartbeat is not None:
+                    heartbeat.beat_and_check(state["global_step"])
+                model.unshard()  # prefetch the root group's parameters
+                with timers["data"], torch.no_grad():
+                    batch = next(batches)
+                    batch = {k: v.to(device=device, non_blocking=True) for k, v in batch.items()}
+                if i_step < state["epoch_step"]:
+                    continue  # fast-forward when resuming
+                with timers["forward"], torch.profiler.record_function("STEP::forward"):
+                    outputs = model(**batch)
+                    del batch
+                with timers["backward"], torch.profiler.record_function("STEP::backward"):
+                    outputs.loss.backward()
+                with timers["update"], torch.profiler.record_function("STEP::update"):
+                    optimizer.step()
+                    lr_scheduler.step()
+                    optimizer.zero_grad(set_to_none=not args.cpu_offload)
+                if prof is not None:
+                    prof.step()
+
+                state["global_step"] += 1
+                state["epoch_step"] += 1
+                loss_value = outputs.loss.item()
+                state["running_loss"] += loss_value
+                if args.loss_log and rank == 0:
+                    with open(args.loss_log, "a") as fp:
+                        fp.write(f"{state['global_step']} {loss_value:.8f}\n")
+
+                if state["global_step"] % args.log_freq == 0:
+                    tok_per_step = world_size * args.batch_size * args.seq_length
+                    ms_local = sum(t.avg_elapsed_ms() for t in timers.values())
+                    ms_per_step = all_reduce_max(ms_local, device)  # slowest rank sets the pace
+                    info = {
+                        "global_step": state["global_step"],
+                        "lr": lr_scheduler.get_last_lr()[0],
+                        "running_loss": state["running_loss"] / args.log_freq,
+                        "epoch": state["epoch"],
+                        "epoch_progress": state["epoch_step"] / len(dataloader),
+                        "num_batches_remaining": len(dataloader) - i_step,
+                        **get_mem_stats(device),
+                        "tokens_per_s": 1000 * tok_per_step / max(ms_per_step, 1e-9),
+                        "time/total": ms_per_step,
+                        **{f"time/{k}": t.avg_elapsed_ms() for k, t in timers.items()},
+                    }
+                    LOGGER.info(info)
+                    if device.type == "cuda":
+                        torch.cuda.reset_peak_memory_stats(device)
+                    state["running_loss"] = 0
+                    for t in timers.values():
+                        t.reset()
+
+                if is_experiment and state["global_step"] % args.ckpt_freq == 0:
+                    ckpt.save_checkpoint(exp_dir, model, optimizer, lr_scheduler, state, plan.rs_hooks)
+
+                if args.steps is not None and state["global_step"] >= args.steps:
+                    done = True
+                    break
+            if done:
+                break
+            state["epoch_step"] = 0
+    dist.barrier()
+    dist.destroy_process_group()
+    return state
+
+
+if __name__ == "__main__":
+    main()
