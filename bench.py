@@ -1,0 +1,315 @@
+"""Throughput benchmark: FSDP training tokens/s of a Llama-3-8B-shape model (bf16, seq 4096,
+micro-batch 1 per GPU, AdamW, synthetic uniform tokens, random N(0, 0.02) weights).
+
+    python bench.py --gpus 1 --steps 5 --warmup 3
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
+        --master-port P bench.py --gpus N --steps K --warmup W
+    python bench.py --impl reference ...      # the unmodified reference hooks from baseline/_ref
+
+Two measurements per run, both the maximum over ranks:
+  value      device-timed: K optimizer steps between CUDA events, inputs already on the device
+  e2e.value  end to end through ``TrainEngine.step``: every step copies its token batch from pinned
+             host memory and reads the loss back to the host
+Rank 0 prints one JSON line.  SM clocks and throttle reasons are sampled with nvidia-smi while the
+timed regions run.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+
+MODEL_SHAPES = {
+    # name: (vocab, d_model, layers, heads, kv_heads, ffn, rope_theta)
+    "llama3-8b": (128256, 4096, 32, 32, 8, 14336, 500000.0),
+    "llama2-13b": (32000, 5120, 40, 40, 40, 13824, 10000.0),
+    "34b": (32000, 8192, 48, 64, 8, 22016, 1000000.0),
+    "small": (32768, 1024, 4, 8, 2, 4096, 500000.0),
+}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons of one GPU every 200 ms while running."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "200"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._pump, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.rows.append((time.time(), line.strip()))
+
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=2)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self, t0: float, t1: float) -> dict:
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for t, line in self.rows:
+            if t < t0 or t > t1:
+                continue
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0])), mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--model", default="llama3-8b", choices=sorted(MODEL_SHAPES))
+    ap.add_argument("--seq", type=int, default=4096)
+    ap.add_argument("--micro-batch", type=int, default=1)
+    ap.add_argument("--ref-variant", default="zip", choices=["zip", "int8", "nccl"],
+                    help="reference arm: its shipped run uses -q --zip-ccl (zip)")
+    ap.add_argument("--transport", default="auto", choices=["auto", "symm", "lib"])
+    ap.add_argument("--no-compress", action="store_true", help="ours: stock NCCL collectives")
+    ap.add_argument("--act-ckpt", action="store_true")
+    ap.add_argument("--gemm", default=None, choices=[None, "auto", "tcgen05", "cublas"])
+    return ap.parse_args()
+
+
+def make_ours(args, device):
+    sys.path.insert(0, ROOT)
+    from fsdp_comm_opt_b200 import _lib
+    from fsdp_comm_opt_b200.engine import EngineConfig, TrainEngine
+    from fsdp_comm_opt_b200.ops import gemm
+
+    if args.gemm:
+        gemm.set_backend(args.gemm)
+    comp = not args.no_compress
+    eng = TrainEngine(EngineConfig(model=args.model, quantize=comp, zip_ccl=comp, compress_rs=comp,
+                                   transport=args.transport, act_ckpt=args.act_ckpt), device)
+    info = {"gemm_backend": gemm.get_backend(), "native_lib": str(_lib.cuda_lib_path()),
+            "comm": "zip all-gather + compressed reduce-scatter" if comp else "nccl"}
+    return eng.step_on_device, eng.step, info, _lib
+
+
+def make_reference(args, device, world):
+    """Stock FSDP2 + the reference's unmodified hook classes and extension from baseline/_ref, an HF
+    Llama model built from a local config, torch fused AdamW: the reference's train.py flow
+    (which cannot run offline because it needs the HF hub) with synthetic tokens."""
+    ref_root = os.path.join(ROOT, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref_root, "main")):
+        raise RuntimeError("baseline/_ref is missing (reference not installed)")
+    sys.path.insert(0, ref_root)
+    import torch
+    from torch.distributed.fsdp import MixedPrecisionPolicy, fully_shard
+    from transformers import AutoModelForCausalLM, LlamaConfig
+    from transformers.models.llama.modeling_llama import LlamaRMSNorm
+
+    v, d, L, H, Hkv, ffn, theta = MODEL_SHAPES[args.model]
+    cfg = LlamaConfig(vocab_size=v, hidden_size=d, intermediate_size=ffn, num_hidden_layers=L,
+                      num_attention_heads=H, num_key_value_heads=Hkv, max_position_embeddings=max(args.seq, 4096),
+                      rope_theta=theta, use_cache=False, tie_word_embeddings=False)
+    with torch.device("meta"):
+        model = AutoModelForCausalLM.from_config(cfg, dtype=torch.bfloat16)
+    fsdp_config = dict(reshard_after_forward=True,
+                       mp_policy=MixedPrecisionPolicy(param_dtype=torch.bfloat16, reduce_dtype=torch.float32))
+    hook_cls = None
+    if args.ref_variant != "nccl":
+        import main.comm as ref_comm
+        import main.zipccl_comm as ref_zip
+
+        assert ref_zip.__file__.startswith(ref_root) and ref_comm.__file__.startswith(ref_root)
+        hook_cls = ref_zip.ZipCCLAllGather if args.ref_variant == "zip" else ref_comm.QuantizedAllGather
+    layers = list(model.model.layers)
+    fl = []
+    for dec in layers:
+        m = fully_shard(dec, **fsdp_config)
+        fl.append(m)
+        if hook_cls is not None:
+            m.set_custom_all_gather(hook_cls())
+    for i, m in enumerate(fl):
+        if fl[i + 1:i + 2]:
+            m.set_modules_to_forward_prefetch(fl[i + 1:i + 2])
+    root = fully_shard(model, **fsdp_config)
+    if hook_cls is not None:
+        root.set_custom_all_gather(hook_cls())
+    model.to_empty(device=device)
+    torch.manual_seed(0)
+    with torch.no_grad():
+        for mod in model.modules():
+            if isinstance(mod, (torch.nn.Linear, torch.nn.Embedding)):
+                torch.nn.init.normal_(mod.weight, mean=0.0, std=0.02)
+            elif isinstance(mod, LlamaRMSNorm):
+                torch.nn.init.ones_(mod.weight)
+        hd = d // H
+        inv = 1.0 / (theta ** (torch.arange(0, hd, 2, dtype=torch.float32, device=device) / hd))
+        model.model.rotary_emb.inv_freq = inv
+        model.model.rotary_emb.original_inv_freq = inv.clone()
+    opt = torch.optim.AdamW(model.parameters(), lr=3e-5, fused=True)
+    sched = torch.optim.lr_scheduler.CosineAnnealingLR(opt, T_max=1000, eta_min=3e-7)
+
+    def step_on_device(ids):
+        model.unshard()
+        out = model(input_ids=ids, labels=ids)
+        out.loss.backward()
+        opt.step()
+        sched.step()
+        opt.zero_grad(set_to_none=True)
+        return out.loss.detach()
+
+    def step(host_ids):
+        return float(step_on_device(host_ids.to(device, non_blocking=True)).item())
+
+    return step_on_device, step, {"ref_variant": args.ref_variant}, None
+
+
+def main():
+    args = parse_args()
+    try:
+        import torch
+        import torch.distributed as dist
+    except Exception as e:  # pragma: no cover
+        print(json.dumps({"impl": args.impl, "unavailable": f"torch import failed: {e}"}))
+        return 0
+    if not torch.cuda.is_available():
+        print(json.dumps({"impl": args.impl, "unavailable": "no CUDA device"}))
+        return 0
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            print(json.dumps({"impl": args.impl, "unavailable":
+                              f"--gpus {args.gpus} needs torch.distributed.run with --nproc-per-node {args.gpus}"}))
+            return 0
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29541")
+    device = torch.device(f"cuda:{local_rank}")
+    torch.cuda.set_device(device)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=device)
+
+    try:
+        if args.impl == "ours":
+            step_dev, step_host, info, lib = make_ours(args, device)
+        else:
+            step_dev, step_host, info, lib = make_reference(args, device, world)
+    except Exception as e:
+        if args.impl == "reference":
+            if rank == 0:
+                print(json.dumps({"impl": "reference", "unavailable": f"{type(e).__name__}: {e}"[:300]}))
+            dist.destroy_process_group()
+            return 0
+        raise
+
+    vocab = MODEL_SHAPES[args.model][0]
+    B, S = args.micro_batch, args.seq
+    g = torch.Generator().manual_seed(1234 + rank)
+    n_batches = args.warmup + args.steps
+    host_batches = [torch.randint(0, vocab, (B, S), generator=g, dtype=torch.int64).pin_memory()
+                    for _ in range(n_batches)]
+    dev_batches = [b.to(device) for b in host_batches]
+
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+
+    def run(kind):
+        fn, batches = (step_dev, dev_batches) if kind == "device" else (step_host, host_batches)
+        for i in range(args.warmup):
+            fn(batches[i])
+        torch.cuda.synchronize(device)
+        dist.barrier()
+        torch.cuda.synchronize(device)
+        if lib is not None:
+            lib.reset_launch_count()
+        t_wall0 = time.time()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        last = None
+        for i in range(args.steps):
+            last = fn(batches[args.warmup + i])
+        e1.record()
+        torch.cuda.synchronize(device)
+        dist.barrier()
+        torch.cuda.synchronize(device)
+        t_wall1 = time.time()
+        ms = e0.elapsed_time(e1) if kind == "device" else 1000.0 * (t_wall1 - t_wall0)
+        t = torch.tensor([ms], dtype=torch.float64, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        launches = lib.launch_count() if lib is not None else None
+        return float(t.item()), float(last) if last is not None else None, launches, (t_wall0, t_wall1)
+
+    dev_ms, dev_loss, launches, (d0, d1) = run("device")
+    e2e_ms, e2e_loss, _, (x0, x1) = run("e2e")
+    if rank == 0:
+        time.sleep(0.3)
+        sampler.stop()
+    tokens = world * B * S * args.steps
+    value = tokens / (dev_ms / 1000.0)
+    e2e_value = tokens / (e2e_ms / 1000.0)
+    if rank == 0:
+        clocks = sampler.summary(d0, x1)
+        out = {
+            "metric": "FSDP training tokens/sec (max over ranks, device-timed)",
+            "impl": args.impl,
+            "value": value,
+            "unit": "tokens/s",
+            "n_gpus": world,
+            "steps": args.steps,
+            "warmup": args.warmup,
+            "ms_per_step": dev_ms / args.steps,
+            "higher_is_better": True,
+            "scaling": "weak",
+            "vs_baseline": None,
+            "dtype": "bf16",
+            "data": "synthetic uniform random tokens, random N(0,0.02) init (no datasets or checkpoints offline)",
+            "config": {"model": args.model, "global_batch": world * B, "seq_len": S,
+                       "parallelism": f"fsdp{world}" if world > 1 else "fsdp1 (single GPU, full shard of one)",
+                       "optimizer": "AdamW", "act_ckpt": args.act_ckpt,
+                       "l2": "inputs larger than L2: every step streams >16 GB of weights and activations",
+                       **info},
+            "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": e2e_ms / args.steps,
+                    "h2d_bytes_per_step": B * S * 8, "d2h_bytes_per_step": 4,
+                    "api": "TrainEngine.step(pinned host token ids) -> float loss" if args.impl == "ours"
+                    else "reference hooks + FSDP2 + HF model step, batch.to(device) then loss.item()"},
+            "gpu_launches": launches,
+            "clocks": clocks,
+            "loss": {"device_run_last": dev_loss, "e2e_run_last": e2e_loss},
+        }
+        print(json.dumps(out))
+    dist.barrier()
+    dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

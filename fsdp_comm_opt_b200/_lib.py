@@ -60,7 +60,47 @@ def cuda_lib_path() -> Path:
     return _build.LIB / "libzc_cuda.so"
 
 
-def cuda() -> ctypes.CDLL:
+# kernels launched by one call of each C launcher (for the launch counter)
+_KERNELS_PER_CALL = {
+    "zc_v1_encode_split": 3, "zc_v1_encode_fused": 3, "zc_v1_base_from_std": 2, "zc_quant_int8": 2,
+    "zc_attn_bwd": 3, "zc_attn_status_read_and_clear": 0, "zc_gemm_status_read_and_clear": 0,
+}
+_LAUNCHES = 0
+
+
+class _CountingLib:
+    """Proxy over the CDLL that counts kernel launches made through the C launchers."""
+
+    def __init__(self, lib):
+        self._lib = lib
+        self._cache = {}
+
+    def __getattr__(self, name):
+        fn = self._cache.get(name)
+        if fn is None:
+            raw = getattr(self._lib, name)
+            n = _KERNELS_PER_CALL.get(name, 1)
+
+            def fn(*args, _raw=raw, _n=n):
+                global _LAUNCHES
+                _LAUNCHES += _n
+                return _raw(*args)
+
+            self._cache[name] = fn
+        return fn
+
+
+def launch_count() -> int:
+    """Kernels of this library launched since the last ``reset_launch_count``."""
+    return _LAUNCHES
+
+
+def reset_launch_count() -> None:
+    global _LAUNCHES
+    _LAUNCHES = 0
+
+
+def cuda():
     """The CUDA kernel library.  Raises when it cannot be loaded."""
     global _CUDA
     if _CUDA is None:
@@ -77,7 +117,7 @@ def cuda() -> ctypes.CDLL:
                 from . import _cuda_sigs
 
                 _cuda_sigs.declare(lib)
-                _CUDA = lib
+                _CUDA = _CountingLib(lib)
     return _CUDA
 
 

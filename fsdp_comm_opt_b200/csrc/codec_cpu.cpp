@@ -213,25 +213,39 @@ int64_t zc_cpu_v2_encode(const uint16_t* in, int64_t n, uint8_t* records, uint32
   for (int64_t c = 0; c < nc; ++c) {
     uint8_t* rec = records + c * V2_SLOT_BYTES;
     uint8_t ex[V2_CHUNK_ELEMS];
-    int emax = 0;
+    int emax = 0, emin = 255;
     for (int i = 0; i < V2_CHUNK_ELEMS; ++i) {
       const int64_t g = c * V2_CHUNK_ELEMS + i;
       const uint16_t v = g < n ? in[g] : (uint16_t)0;
       rec[i] = bf16_sm(v);
       ex[i] = bf16_exp(v);
       if (ex[i] > emax) emax = ex[i];
+      if (ex[i] < emin) emin = ex[i];
     }
-    const int anchor = emax > 15 ? emax - 15 : 0;
-    int prefix[17] = {0};
-    int h[16] = {0};
-    for (int i = 0; i < V2_CHUNK_ELEMS; ++i) {
-      const int d = (int)ex[i] - anchor;
-      if (d >= 0) h[d]++;
+    uint32_t hdr;
+    if (emin == emax) {
+      hdr = v2_header(emax, 0, 0);
+    } else {
+      const int anchor = emax > 15 ? emax - 15 : 0;
+      int prefix[17] = {0};
+      int h[16] = {0};
+      for (int i = 0; i < V2_CHUNK_ELEMS; i += 4) {
+        const int d = (int)ex[i] - anchor;
+        if (d >= 0) h[d]++;
+      }
+      for (int k = 0; k < 16; ++k) prefix[k + 1] = prefix[k] + h[k];
+      hdr = v2_choose(prefix, anchor);
     }
-    for (int k = 0; k < 16; ++k) prefix[k + 1] = prefix[k] + h[k];
-    const uint32_t hdr = v2_choose(prefix, anchor, emax);
+    int w = v2_hdr_width(hdr);
+    const int base = v2_hdr_base(hdr);
+    if (w != V2_RAW_WIDTH && w > 0) {
+      const unsigned span = (1u << w) - 1u;
+      int n_esc = 0;
+      for (int i = 0; i < V2_CHUNK_ELEMS; ++i) n_esc += ((unsigned)((int)ex[i] - base) < span) ? 0 : 1;
+      if (128 * w + n_esc > V2_CHUNK_ELEMS) { hdr = v2_header(0, V2_RAW_WIDTH, 0); w = V2_RAW_WIDTH; }
+      else hdr = v2_header(base, w, n_esc);
+    }
     headers[c] = hdr;
-    const int w = v2_hdr_width(hdr), base = v2_hdr_base(hdr);
     if (w == V2_RAW_WIDTH) {
       std::memcpy(rec + 1024, ex, 1024);
     } else if (w > 0) {

@@ -35,11 +35,14 @@
 //            never longer than 2048 B, so a record slot has the size of the raw bf16 chunk and
 //            every chunk is encodable and decodable on its own at a fixed offset.
 //   window choice (identical on CPU and GPU, so streams are byte-identical):
-//            emax = max e; anchor a = max(emax-15, 0); h[d] = #{e - a == d}, d = 0..15;
+//            emin, emax = exact min / max exponent of the chunk; emin == emax gives width 0.
+//            anchor a = max(emax-15, 0); h[d] = #{sampled e - a == d}, d = 0..15, where the
+//            sample is every 4th element (index % 4 == 0, 256 samples);
 //            candidates (width w, first bin d0) with span s = 2^w - 1, d0 = 0..16-s:
-//            cost = 128*w + 1024 - sum(h[d0..d0+s-1]); width 0 (cost 0) when one bin holds all
-//            1024; raw costs 1024.  Smallest cost wins; ties go to the smaller width, then the
-//            smaller d0; raw only when strictly cheaper.
+//            estimated cost = 128*w + 4*(256 - sum(h[d0..d0+s-1])).  Smallest estimate wins; ties
+//            go to the smaller width, then the smaller d0; an estimate above 1024 selects raw.
+//            The escapes are then counted exactly; if 128*w + n_esc > 1024 the chunk is stored
+//            raw after all, so a record never exceeds its slot.
 #pragma once
 #include <stdint.h>
 
@@ -92,24 +95,23 @@ ZC_HD void v2_candidate(int idx, int& w, int& d0) {
   else { w = 4; d0 = idx - 40; }
 }
 
-// Given the 16-bin histogram anchored at `anchor`, pick (base, width, n_esc).
-// prefix[k] = sum of h[0..k-1], k = 0..16.  Returns the packed header.
-ZC_HD uint32_t v2_choose(const int* prefix, int anchor, int emax) {
-  const int dmax = emax - anchor;
-  if (prefix[dmax + 1] - prefix[dmax] == V2_CHUNK_ELEMS) return v2_header(emax, 0, 0);
-  int best_cost = V2_CHUNK_ELEMS;  // raw
-  int best_idx = -1;
+// Given the 16-bin sample histogram (256 samples) anchored at `anchor`, pick (base, width).
+// prefix[k] = sum of h[0..k-1], k = 0..16.  Returns the header with n_esc = 0 (the exact escape
+// count is filled in by the encoder) or a raw header.
+ZC_HD uint32_t v2_choose(const int* prefix, int anchor) {
+  int best_key = 0x7fffffff;
   for (int idx = 0; idx < V2_NUM_CAND; ++idx) {
     int w, d0;
     v2_candidate(idx, w, d0);
     const int s = (1 << w) - 1;
-    const int cost = 128 * w + V2_CHUNK_ELEMS - (prefix[d0 + s] - prefix[d0]);
-    if (cost < best_cost || (best_idx < 0 && cost == best_cost)) { best_cost = cost; best_idx = idx; }
+    const int cost = 128 * w + 4 * (256 - (prefix[d0 + s] - prefix[d0]));
+    const int key = (cost << 6) | idx;
+    if (key < best_key) best_key = key;
   }
-  if (best_idx < 0) return v2_header(0, V2_RAW_WIDTH, 0);
+  if ((best_key >> 6) > V2_CHUNK_ELEMS) return v2_header(0, V2_RAW_WIDTH, 0);
   int w, d0;
-  v2_candidate(best_idx, w, d0);
-  return v2_header(anchor + d0, w, best_cost - 128 * w);
+  v2_candidate(best_key & 63, w, d0);
+  return v2_header(anchor + d0, w, 0);
 }
 
 }  // namespace zc

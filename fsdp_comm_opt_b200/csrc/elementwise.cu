@@ -1,0 +1,537 @@
+// Memory-bound training ops for sm_100a: RMSNorm (+ residual add) forward/backward, RoPE, SwiGLU
+// forward/backward, cross-entropy with in-place gradient, int8 absmax quantise/dequantise and
+// fused AdamW.  Every kernel moves 16-byte vectors, keeps fp32 math in registers and touches each
+// HBM byte once per pass.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <math_constants.h>
+#include <stdint.h>
+
+#include "launch_util.h"
+
+namespace zc {
+
+constexpr unsigned FULLM = 0xffffffffu;
+
+struct alignas(16) BF8 {
+  __nv_bfloat162 v[4];
+};
+
+__device__ __forceinline__ void unpack8(const BF8& p, float (&f)[8]) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 t = __bfloat1622float2(p.v[i]);
+    f[2 * i] = t.x;
+    f[2 * i + 1] = t.y;
+  }
+}
+__device__ __forceinline__ BF8 pack8(const float (&f)[8]) {
+  BF8 p;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) p.v[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+  return p;
+}
+__device__ __forceinline__ BF8 ld8(const __nv_bfloat16* p) { return *reinterpret_cast<const BF8*>(p); }
+__device__ __forceinline__ void st8(__nv_bfloat16* p, const BF8& v) { *reinterpret_cast<BF8*>(p) = v; }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(FULLM, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(FULLM, v, o));
+  return v;
+}
+
+// block-wide sum for up to 1024 threads; every thread gets the result
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float t = (lane < nw) ? red[lane] : 0.f;
+  return warp_sum(t);
+}
+__device__ __forceinline__ float block_max(float v, float* red) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  v = warp_max(v);
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float t = (lane < nw) ? red[lane] : -CUDART_INF_F;
+  return warp_max(t);
+}
+
+// ---------------------------------------------------------------------------------------------
+// RMSNorm.  One CTA (256 threads) per row, row cached in registers (cols <= 8192, cols % 8 == 0).
+//   h = x (+ residual, rounded to bf16);  rstd = rsqrt(mean(h^2) + eps);  y = h * rstd * w
+// ---------------------------------------------------------------------------------------------
+constexpr int RN_THREADS = 256;
+constexpr int RN_MAXV = 4;  // vectors of 8 per thread
+
+__global__ void __launch_bounds__(RN_THREADS) rmsnorm_fwd_kernel(
+    const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ res,
+    const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ y, __nv_bfloat16* __restrict__ h_out,
+    float* __restrict__ rstd_out, int cols, float eps) {
+  __shared__ float red[32];
+  const int64_t row = blockIdx.x;
+  const int nvec = cols / 8;
+  float h[RN_MAXV][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < RN_MAXV; ++i) {
+    const int v = threadIdx.x + i * RN_THREADS;
+    if (v < nvec) {
+      unpack8(ld8(x + row * cols + v * 8), h[i]);
+      if (res) {
+        float r[8];
+        unpack8(ld8(res + row * cols + v * 8), r);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) h[i][j] += r[j];
+        const BF8 hb = pack8(h[i]);
+        st8(h_out + row * cols + v * 8, hb);
+        unpack8(hb, h[i]);  // normalise the rounded sum, as the unfused op order would
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) ss += h[i][j] * h[i][j];
+    }
+  }
+  ss = block_sum(ss, red);
+  const float rstd = rsqrtf(ss / (float)cols + eps);
+  if (threadIdx.x == 0) rstd_out[row] = rstd;
+#pragma unroll
+  for (int i = 0; i < RN_MAXV; ++i) {
+    const int v = threadIdx.x + i * RN_THREADS;
+    if (v < nvec) {
+      float wv[8], o[8];
+      unpack8(ld8(w + v * 8), wv);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = h[i][j] * rstd * wv[j];
+      st8(y + row * cols + v * 8, pack8(o));
+    }
+  }
+}
+
+// dx = rstd * (g - xhat * mean(g * xhat)) (+ dh),  g = dy * w,  xhat = h * rstd
+// dw += sum_rows dy * xhat   (fp32 atomics into dw32 once per CTA)
+__global__ void __launch_bounds__(RN_THREADS) rmsnorm_bwd_kernel(
+    const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ h,
+    const __nv_bfloat16* __restrict__ w, const float* __restrict__ rstd_in,
+    const __nv_bfloat16* __restrict__ dh, __nv_bfloat16* __restrict__ dx, float* __restrict__ dw32,
+    int64_t rows, int cols) {
+  __shared__ float red[32];
+  const int nvec = cols / 8;
+  float wv[RN_MAXV][8], dwacc[RN_MAXV][8];
+#pragma unroll
+  for (int i = 0; i < RN_MAXV; ++i) {
+    const int v = threadIdx.x + i * RN_THREADS;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) dwacc[i][j] = 0.f;
+    if (v < nvec) unpack8(ld8(w + v * 8), wv[i]);
+  }
+  for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+    const float rstd = rstd_in[row];
+    float g[RN_MAXV][8], xh[RN_MAXV][8];
+    float dot = 0.f;
+#pragma unroll
+    for (int i = 0; i < RN_MAXV; ++i) {
+      const int v = threadIdx.x + i * RN_THREADS;
+      if (v < nvec) {
+        float d[8];
+        unpack8(ld8(dy + row * cols + v * 8), d);
+        unpack8(ld8(h + row * cols + v * 8), xh[i]);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          xh[i][j] *= rstd;
+          g[i][j] = d[j] * wv[i][j];
+          dot += g[i][j] * xh[i][j];
+          dwacc[i][j] += d[j] * xh[i][j];
+        }
+      }
+    }
+    dot = block_sum(dot, red) / (float)cols;
+#pragma unroll
+    for (int i = 0; i < RN_MAXV; ++i) {
+      const int v = threadIdx.x + i * RN_THREADS;
+      if (v < nvec) {
+        float o[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = rstd * (g[i][j] - xh[i][j] * dot);
+        if (dh) {
+          float e[8];
+          unpack8(ld8(dh + row * cols + v * 8), e);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) o[j] += e[j];
+        }
+        st8(dx + row * cols + v * 8, pack8(o));
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < RN_MAXV; ++i) {
+    const int v = threadIdx.x + i * RN_THREADS;
+    if (v < nvec) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) atomicAdd(dw32 + v * 8 + j, dwacc[i][j]);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// RoPE in place on the first n_rot heads of a packed [T, total_heads * D] tensor
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) rope_kernel(__nv_bfloat16* __restrict__ qkv, const float* __restrict__ cosT,
+                                                   const float* __restrict__ sinT, int64_t T, int S, int n_rot,
+                                                   int total_heads, int D, float sign) {
+  const int vph = D / 16;  // 8-element vectors per half head
+  const int64_t total = T * n_rot * vph;
+  for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += (int64_t)gridDim.x * blockDim.x) {
+    const int v = (int)(idx % vph);
+    const int hd = (int)((idx / vph) % n_rot);
+    const int64_t t = idx / ((int64_t)vph * n_rot);
+    const int pos = (int)(t % S);
+    __nv_bfloat16* p = qkv + (t * total_heads + hd) * D + v * 8;
+    float a[8], b[8], oa[8], ob[8];
+    unpack8(ld8(p), a);
+    unpack8(ld8(p + D / 2), b);
+    const float4* c4 = reinterpret_cast<const float4*>(cosT + (int64_t)pos * (D / 2) + v * 8);
+    const float4* s4 = reinterpret_cast<const float4*>(sinT + (int64_t)pos * (D / 2) + v * 8);
+    const float4 c0 = c4[0], c1 = c4[1], s0 = s4[0], s1 = s4[1];
+    const float c[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+    const float s[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float sj = s[j] * sign;
+      oa[j] = a[j] * c[j] - b[j] * sj;
+      ob[j] = b[j] * c[j] + a[j] * sj;
+    }
+    st8(p, pack8(oa));
+    st8(p + D / 2, pack8(ob));
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// SwiGLU on packed [T, 2F] = [gate | up]
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ gu,
+                                                         __nv_bfloat16* __restrict__ out, int64_t T, int F) {
+  const int vpr = F / 8;
+  const int64_t total = T * vpr;
+  for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t t = idx / vpr;
+    const int v = (int)(idx % vpr);
+    float g[8], u[8], o[8];
+    unpack8(ld8(gu + t * 2 * F + v * 8), g);
+    unpack8(ld8(gu + t * 2 * F + F + v * 8), u);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) o[j] = g[j] / (1.f + __expf(-g[j])) * u[j];
+    st8(out + t * F + v * 8, pack8(o));
+  }
+}
+
+__global__ void __launch_bounds__(256) swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ gu,
+                                                         const __nv_bfloat16* __restrict__ dy,
+                                                         __nv_bfloat16* __restrict__ dgu, int64_t T, int F) {
+  const int vpr = F / 8;
+  const int64_t total = T * vpr;
+  for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t t = idx / vpr;
+    const int v = (int)(idx % vpr);
+    float g[8], u[8], d[8], dg[8], du[8];
+    unpack8(ld8(gu + t * 2 * F + v * 8), g);
+    unpack8(ld8(gu + t * 2 * F + F + v * 8), u);
+    unpack8(ld8(dy + t * F + v * 8), d);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float s = 1.f / (1.f + __expf(-g[j]));
+      dg[j] = d[j] * u[j] * s * (1.f + g[j] * (1.f - s));
+      du[j] = d[j] * g[j] * s;
+    }
+    st8(dgu + t * 2 * F + v * 8, pack8(dg));
+    st8(dgu + t * 2 * F + F + v * 8, pack8(du));
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Cross-entropy: one CTA per row; pass 1 online max / sum-exp, pass 2 writes the gradient over the
+// logits.  row_loss = lse - logit[label];  grad = (softmax - onehot) * inv_count
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(1024) ce_kernel(__nv_bfloat16* __restrict__ logits,
+                                                  const int64_t* __restrict__ labels,
+                                                  float* __restrict__ row_loss, const float* __restrict__ inv_count,
+                                                  int V, int ignore_index) {
+  __shared__ float red[32];
+  const int64_t row = blockIdx.x;
+  __nv_bfloat16* lr = logits + row * V;
+  const int64_t label = labels[row];
+  const bool vec = (V % 8 == 0) && ((reinterpret_cast<uintptr_t>(lr) & 15) == 0);
+  if (label == ignore_index) {
+    if (vec) {
+      BF8 z;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) z.v[i] = __floats2bfloat162_rn(0.f, 0.f);
+      for (int v = threadIdx.x; v < V / 8; v += blockDim.x) st8(lr + v * 8, z);
+    } else {
+      for (int i = threadIdx.x; i < V; i += blockDim.x) lr[i] = __float2bfloat16(0.f);
+    }
+    if (threadIdx.x == 0) row_loss[row] = 0.f;
+    return;
+  }
+  float m = -CUDART_INF_F, s = 0.f;
+  if (vec) {
+    for (int v = threadIdx.x; v < V / 8; v += blockDim.x) {
+      float f[8];
+      unpack8(ld8(lr + v * 8), f);
+      float lm = f[0];
+#pragma unroll
+      for (int j = 1; j < 8; ++j) lm = fmaxf(lm, f[j]);
+      if (lm > m) { s *= __expf(m - lm); m = lm; }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) s += __expf(f[j] - m);
+    }
+  } else {
+    for (int i = threadIdx.x; i < V; i += blockDim.x) {
+      const float f = __bfloat162float(lr[i]);
+      if (f > m) { s *= __expf(m - f); m = f; }
+      s += __expf(f - m);
+    }
+  }
+  const float gm = block_max(m, red);
+  s = (m == -CUDART_INF_F) ? 0.f : s * __expf(m - gm);
+  const float gs = block_sum(s, red);
+  const float lse = gm + __logf(gs);
+  const float scale = inv_count[0];
+  const float picked = __bfloat162float(lr[label]);
+  __syncthreads();  // everyone has read lr[label] before it is overwritten
+  if (threadIdx.x == 0) row_loss[row] = lse - picked;
+  const float inv_s = 1.f / gs;
+  if (vec) {
+    for (int v = threadIdx.x; v < V / 8; v += blockDim.x) {
+      float f[8];
+      unpack8(ld8(lr + v * 8), f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        float p = __expf(f[j] - gm) * inv_s;
+        if (v * 8 + j == label) p -= 1.f;
+        f[j] = p * scale;
+      }
+      st8(lr + v * 8, pack8(f));
+    }
+  } else {
+    for (int i = threadIdx.x; i < V; i += blockDim.x) {
+      float p = __expf(__bfloat162float(lr[i]) - gm) * inv_s;
+      if (i == label) p -= 1.f;
+      lr[i] = __float2bfloat16(p * scale);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// int8 absmax quantisation.  Packed buffer: word0 = fp32 scale, word1 = absmax bits (scratch),
+// bytes [16, 16+n) = int8 payload.
+// ---------------------------------------------------------------------------------------------
+template <typename T> __device__ __forceinline__ float to_f(T v);
+template <> __device__ __forceinline__ float to_f<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <> __device__ __forceinline__ float to_f<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f<__half>(__half v) { return __half2float(v); }
+template <typename T> __device__ __forceinline__ T from_f(float v);
+template <> __device__ __forceinline__ __nv_bfloat16 from_f<__nv_bfloat16>(float v) { return __float2bfloat16(v); }
+template <> __device__ __forceinline__ float from_f<float>(float v) { return v; }
+template <> __device__ __forceinline__ __half from_f<__half>(float v) { return __float2half(v); }
+
+template <typename T>
+__global__ void __launch_bounds__(256) absmax_kernel(const T* __restrict__ x, int64_t n, uint32_t* __restrict__ hdr) {
+  float m = 0.f;
+  for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < n; i += (int64_t)gridDim.x * 256)
+    m = fmaxf(m, fabsf(to_f<T>(x[i])));
+  m = warp_max(m);
+  __shared__ float red[8];
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = m;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int i = 1; i < 8; ++i) m = fmaxf(m, red[i]);
+    atomicMax(hdr + 1, __float_as_uint(m));  // non-negative floats order like their bit patterns
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) quant_kernel(const T* __restrict__ x, int64_t n, uint8_t* __restrict__ out) {
+  const float absmax = __uint_as_float(reinterpret_cast<const uint32_t*>(out)[1]);
+  const float scale = fmaxf(absmax / 127.f, 1e-8f);
+  if (blockIdx.x == 0 && threadIdx.x == 0) reinterpret_cast<float*>(out)[0] = scale;
+  int8_t* q = reinterpret_cast<int8_t*>(out + 16);
+  for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < n; i += (int64_t)gridDim.x * 256) {
+    const float r = rintf(to_f<T>(x[i]) / scale);
+    q[i] = (int8_t)fminf(fmaxf(r, -127.f), 127.f);
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) dequant_kernel(const uint8_t* __restrict__ gathered, int64_t stride,
+                                                      int world, int64_t n, T* __restrict__ out) {
+  const int64_t total = (int64_t)world * n;
+  for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < total; i += (int64_t)gridDim.x * 256) {
+    const int r = (int)(i / n);
+    const int64_t k = i - (int64_t)r * n;
+    const uint8_t* slot = gathered + r * stride;
+    const float scale = reinterpret_cast<const float*>(slot)[0];
+    out[i] = from_f<T>((float)reinterpret_cast<const int8_t*>(slot + 16)[k] * scale);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// AdamW (decoupled weight decay), one launch per shard
+// ---------------------------------------------------------------------------------------------
+template <typename TP, typename TG, typename TS>
+__global__ void __launch_bounds__(256) adamw_kernel(TP* __restrict__ p, TG* __restrict__ g, TS* __restrict__ m,
+                                                    TS* __restrict__ v, int64_t n, float lr, float b1, float b2,
+                                                    float eps, float wd, float bc1, float rsqrt_bc2, int zero_grad) {
+  for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < n; i += (int64_t)gridDim.x * 256) {
+    const float gf = to_f<TG>(g[i]);
+    float pf = to_f<TP>(p[i]);
+    float mf = to_f<TS>(m[i]) * b1 + (1.f - b1) * gf;
+    float vf = to_f<TS>(v[i]) * b2 + (1.f - b2) * gf * gf;
+    pf *= 1.f - lr * wd;
+    const float denom = sqrtf(vf) * rsqrt_bc2 + eps;
+    pf -= (lr / bc1) * mf / denom;
+    p[i] = from_f<TP>(pf);
+    m[i] = from_f<TS>(mf);
+    v[i] = from_f<TS>(vf);
+    if (zero_grad) g[i] = from_f<TG>(0.f);
+  }
+}
+
+template <typename TP, typename TG>
+int adamw_dispatch_s(void* p, void* g, void* m, void* v, int64_t n, int sdt, float lr, float b1, float b2, float eps,
+                     float wd, float bc1, float bc2, int zg, cudaStream_t st) {
+  const int grid = (int)std::min<int64_t>((n + 255) / 256, (int64_t)sm_count() * 16);
+  const float rs = 1.f / sqrtf(bc2);
+  if (sdt == 0)
+    adamw_kernel<TP, TG, __nv_bfloat16><<<grid, 256, 0, st>>>((TP*)p, (TG*)g, (__nv_bfloat16*)m, (__nv_bfloat16*)v, n,
+                                                              lr, b1, b2, eps, wd, bc1, rs, zg);
+  else if (sdt == 1)
+    adamw_kernel<TP, TG, float><<<grid, 256, 0, st>>>((TP*)p, (TG*)g, (float*)m, (float*)v, n, lr, b1, b2, eps, wd,
+                                                      bc1, rs, zg);
+  else
+    return ERR_UNSUPPORTED;
+  return launch_status();
+}
+
+}  // namespace zc
+
+extern "C" {
+
+using zc::ERR_BAD_ARG;
+using zc::ERR_UNSUPPORTED;
+typedef __nv_bfloat16 bf16;
+
+int zc_rmsnorm_fwd(const void* x, const void* res, const void* w, void* y, void* h_out, float* rstd, int64_t rows,
+                   int cols, float eps, cudaStream_t st) {
+  if (cols % 8 || cols > zc::RN_THREADS * zc::RN_MAXV * 8) return ERR_UNSUPPORTED;
+  if (rows == 0) return 0;
+  zc::rmsnorm_fwd_kernel<<<(unsigned)rows, zc::RN_THREADS, 0, st>>>((const bf16*)x, (const bf16*)res, (const bf16*)w,
+                                                                   (bf16*)y, (bf16*)h_out, rstd, cols, eps);
+  return zc::launch_status();
+}
+
+int zc_rmsnorm_bwd(const void* dy, const void* h, const void* w, const float* rstd, const void* dh, void* dx,
+                   float* dw32, int64_t rows, int cols, cudaStream_t st) {
+  if (cols % 8 || cols > zc::RN_THREADS * zc::RN_MAXV * 8) return ERR_UNSUPPORTED;
+  if (rows == 0) return 0;
+  const int grid = (int)std::min<int64_t>(rows, (int64_t)zc::sm_count() * 4);
+  zc::rmsnorm_bwd_kernel<<<grid, zc::RN_THREADS, 0, st>>>((const bf16*)dy, (const bf16*)h, (const bf16*)w, rstd,
+                                                          (const bf16*)dh, (bf16*)dx, dw32, rows, cols);
+  return zc::launch_status();
+}
+
+int zc_rope_inplace(void* qkv, const float* cosT, const float* sinT, int64_t T, int S, int n_rot, int total_heads,
+                    int D, float sign, cudaStream_t st) {
+  if (D % 16 || n_rot > total_heads) return ERR_UNSUPPORTED;
+  const int64_t total = T * n_rot * (D / 16);
+  if (total == 0) return 0;
+  const int grid = (int)std::min<int64_t>((total + 255) / 256, (int64_t)zc::sm_count() * 16);
+  zc::rope_kernel<<<grid, 256, 0, st>>>((bf16*)qkv, cosT, sinT, T, S, n_rot, total_heads, D, sign);
+  return zc::launch_status();
+}
+
+int zc_swiglu_fwd(const void* gu, void* out, int64_t T, int F, cudaStream_t st) {
+  if (F % 8) return ERR_UNSUPPORTED;
+  const int64_t total = T * (F / 8);
+  if (total == 0) return 0;
+  const int grid = (int)std::min<int64_t>((total + 255) / 256, (int64_t)zc::sm_count() * 16);
+  zc::swiglu_fwd_kernel<<<grid, 256, 0, st>>>((const bf16*)gu, (bf16*)out, T, F);
+  return zc::launch_status();
+}
+
+int zc_swiglu_bwd(const void* gu, const void* dy, void* dgu, int64_t T, int F, cudaStream_t st) {
+  if (F % 8) return ERR_UNSUPPORTED;
+  const int64_t total = T * (F / 8);
+  if (total == 0) return 0;
+  const int grid = (int)std::min<int64_t>((total + 255) / 256, (int64_t)zc::sm_count() * 16);
+  zc::swiglu_bwd_kernel<<<grid, 256, 0, st>>>((const bf16*)gu, (const bf16*)dy, (bf16*)dgu, T, F);
+  return zc::launch_status();
+}
+
+int zc_ce_fwd_bwd(void* logits, const int64_t* labels, float* row_loss, const float* inv_count, int64_t T, int V,
+                  int ignore_index, cudaStream_t st) {
+  if (T == 0) return 0;
+  zc::ce_kernel<<<(unsigned)T, 1024, 0, st>>>((bf16*)logits, labels, row_loss, inv_count, V, ignore_index);
+  return zc::launch_status();
+}
+
+int zc_quant_int8(const void* x, int64_t n, int dtype, void* out, cudaStream_t st) {
+  cudaMemsetAsync(out, 0, 16, st);
+  if (n == 0) return zc::launch_status();
+  const int grid = (int)std::min<int64_t>((n + 255) / 256, (int64_t)zc::sm_count() * 16);
+  if (dtype == 0) {
+    zc::absmax_kernel<bf16><<<grid, 256, 0, st>>>((const bf16*)x, n, (uint32_t*)out);
+    zc::quant_kernel<bf16><<<grid, 256, 0, st>>>((const bf16*)x, n, (uint8_t*)out);
+  } else if (dtype == 1) {
+    zc::absmax_kernel<float><<<grid, 256, 0, st>>>((const float*)x, n, (uint32_t*)out);
+    zc::quant_kernel<float><<<grid, 256, 0, st>>>((const float*)x, n, (uint8_t*)out);
+  } else if (dtype == 2) {
+    zc::absmax_kernel<__half><<<grid, 256, 0, st>>>((const __half*)x, n, (uint32_t*)out);
+    zc::quant_kernel<__half><<<grid, 256, 0, st>>>((const __half*)x, n, (uint8_t*)out);
+  } else {
+    return ERR_UNSUPPORTED;
+  }
+  return zc::launch_status();
+}
+
+int zc_dequant_int8(const void* gathered, int64_t stride, int world, int64_t n, int dtype, void* out,
+                    cudaStream_t st) {
+  const int64_t total = (int64_t)world * n;
+  if (total == 0) return 0;
+  const int grid = (int)std::min<int64_t>((total + 255) / 256, (int64_t)zc::sm_count() * 16);
+  if (dtype == 0)
+    zc::dequant_kernel<bf16><<<grid, 256, 0, st>>>((const uint8_t*)gathered, stride, world, n, (bf16*)out);
+  else if (dtype == 1)
+    zc::dequant_kernel<float><<<grid, 256, 0, st>>>((const uint8_t*)gathered, stride, world, n, (float*)out);
+  else if (dtype == 2)
+    zc::dequant_kernel<__half><<<grid, 256, 0, st>>>((const uint8_t*)gathered, stride, world, n, (__half*)out);
+  else
+    return ERR_UNSUPPORTED;
+  return zc::launch_status();
+}
+
+int zc_adamw(void* p, void* g, void* m, void* v, int64_t n, int pdt, int gdt, int sdt, float lr, float b1, float b2,
+             float eps, float wd, float bc1, float bc2, int zero_grad, cudaStream_t st) {
+  if (n == 0) return 0;
+  if (pdt == 0 && gdt == 0)
+    return zc::adamw_dispatch_s<bf16, bf16>(p, g, m, v, n, sdt, lr, b1, b2, eps, wd, bc1, bc2, zero_grad, st);
+  if (pdt == 1 && gdt == 1)
+    return zc::adamw_dispatch_s<float, float>(p, g, m, v, n, sdt, lr, b1, b2, eps, wd, bc1, bc2, zero_grad, st);
+  if (pdt == 0 && gdt == 1)
+    return zc::adamw_dispatch_s<bf16, float>(p, g, m, v, n, sdt, lr, b1, b2, eps, wd, bc1, bc2, zero_grad, st);
+  if (pdt == 1 && gdt == 0)
+    return zc::adamw_dispatch_s<float, bf16>(p, g, m, v, n, sdt, lr, b1, b2, eps, wd, bc1, bc2, zero_grad, st);
+  return ERR_UNSUPPORTED;
+}
+
+}  // extern "C"
