@@ -43,5 +43,7 @@ def declare(lib) -> None:
     _sig(lib, "zc_gemm_bf16", P, P, P, L, L, L, I, I, I, P)
     _sig(lib, "zc_gemm_status_read_and_clear")
     # fused collectives
-    _sig(lib, "zc_symm_all_gather", *([P] * 8), L, I, I, I, L, L, P)
-    _sig(lib, "zc_symm_reduce_scatter", *([P] * 9), L, I, I, I, I, F, L, L, P)
+    from ctypes import c_double, c_uint
+
+    _sig(lib, "zc_symm_all_gather", P, P, P, P, L, I, I, L, c_uint, I, I, c_double, P)
+    _sig(lib, "zc_symm_reduce_scatter", P, P, P, P, P, L, I, I, L, c_uint, I, I, F, I, I, c_double, P)

@@ -34,12 +34,20 @@ template <int D>
 __device__ __forceinline__ void stage_tile(uint8_t* dst, const __nv_bfloat16* src, int64_t ld, int rows_valid,
                                            int tid) {
   constexpr int CPR = D / 8;  // 16-byte chunks per row
-#pragma unroll 4
-  for (int i = tid; i < 128 * CPR; i += 128) {
+  // all of this thread's loads are issued before the first store, so a whole tile is in flight
+  uint4 v[CPR];
+#pragma unroll
+  for (int it = 0; it < CPR; ++it) {
+    const int i = tid + it * 128;
     const int row = i / CPR, chunk = i % CPR;
-    uint4 v = make_uint4(0, 0, 0, 0);
-    if (row < rows_valid) v = __ldg(reinterpret_cast<const uint4*>(src + (int64_t)row * ld + chunk * 8));
-    *reinterpret_cast<uint4*>(dst + (chunk >> 3) * 16384 + sw128_off(row, chunk & 7)) = v;
+    v[it] = make_uint4(0, 0, 0, 0);
+    if (row < rows_valid) v[it] = __ldg(reinterpret_cast<const uint4*>(src + (int64_t)row * ld + chunk * 8));
+  }
+#pragma unroll
+  for (int it = 0; it < CPR; ++it) {
+    const int i = tid + it * 128;
+    const int row = i / CPR, chunk = i % CPR;
+    *reinterpret_cast<uint4*>(dst + (chunk >> 3) * 16384 + sw128_off(row, chunk & 7)) = v[it];
   }
 }
 

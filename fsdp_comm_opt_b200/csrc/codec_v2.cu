@@ -4,142 +4,11 @@
 // SM count.  No shared memory, no atomics, no cross-chunk dependency: chunk c lives at the fixed
 // offset c*2048 of the record buffer, so encode and decode are embarrassingly parallel and the
 // same device functions are reused inside the fused collective kernels.
-#include "codec_dev.cuh"
+#include "codec_v2_dev.cuh"
 #include "launch_util.h"
 
 namespace zc {
 
-// Window choice for one chunk.  Every lane passes its 8 exponent words; the result (header with
-// n_esc = 0, or a raw header) is uniform across the warp.
-__device__ __forceinline__ uint32_t v2_choose_warp(const LaneSplit& s, int lane) {
-  // exact min / max of the 1024 exponents
-  uint32_t mx = s.ex[0], mn = s.ex[0];
-#pragma unroll
-  for (int k = 1; k < 8; ++k) {
-    mx = __vmaxu4(mx, s.ex[k]);
-    mn = __vminu4(mn, s.ex[k]);
-  }
-  uint32_t mxb = max(max(mx & 0xFF, (mx >> 8) & 0xFF), max((mx >> 16) & 0xFF, mx >> 24));
-  uint32_t mnb = min(min(mn & 0xFF, (mn >> 8) & 0xFF), min((mn >> 16) & 0xFF, mn >> 24));
-  const int emax = (int)__reduce_max_sync(FULL, mxb);
-  const int emin = (int)__reduce_min_sync(FULL, mnb);
-  if (emin == emax) return v2_header(emax, 0, 0);
-  const int anchor = emax > 15 ? emax - 15 : 0;
-  // sample histogram: byte 0 of every word (elements with index % 4 == 0), 16 bins x 4 bit
-  unsigned long long h = 0;
-#pragma unroll
-  for (int k = 0; k < 8; ++k) {
-    const int d = (int)(s.ex[k] & 0xFFu) - anchor;
-    if (d >= 0) h += 1ull << (4 * d);
-  }
-  // widen to 16-bit fields (two bins per word) and sum over the warp
-  int tot[16];
-#pragma unroll
-  for (int q = 0; q < 8; ++q) {
-    const uint32_t pair = (uint32_t)((h >> (8 * q)) & 0xFull) | ((uint32_t)((h >> (8 * q + 4)) & 0xFull) << 16);
-    const uint32_t sum = __reduce_add_sync(FULL, pair);
-    tot[2 * q] = (int)(sum & 0xFFFFu);
-    tot[2 * q + 1] = (int)(sum >> 16);
-  }
-  // lane k keeps prefix[k] (k = 0..16); candidates fetch their two prefixes by shuffle
-  int mine = 0;
-#pragma unroll
-  for (int d = 0; d < 16; ++d) mine += (d < lane) ? tot[d] : 0;
-  int best = 0x7fffffff;
-#pragma unroll
-  for (int r = 0; r < 2; ++r) {
-    const int idx = lane + 32 * r;
-    int w = 1, d0 = 0;
-    if (idx < V2_NUM_CAND) v2_candidate(idx, w, d0);
-    const int sp = (1 << w) - 1;
-    const int hi = __shfl_sync(FULL, mine, d0 + sp);
-    const int lo = __shfl_sync(FULL, mine, d0);
-    const int cost = 128 * w + 4 * (256 - (hi - lo));
-    if (idx < V2_NUM_CAND) best = min(best, (cost << 6) | idx);
-  }
-  best = __reduce_min_sync(FULL, best);
-  if ((best >> 6) > V2_CHUNK_ELEMS) return v2_header(0, V2_RAW_WIDTH, 0);
-  int w, d0;
-  v2_candidate(best & 63, w, d0);
-  return v2_header(anchor + d0, w, 0);
-}
-
-// Encode the chunk whose split fields are in `s` into `rec`; returns the final header.
-__device__ __forceinline__ uint32_t v2_encode_chunk(const LaneSplit& s, uint8_t* rec, int lane) {
-  uint32_t hdr = v2_choose_warp(s, lane);
-  int w = v2_hdr_width(hdr);
-  const int base = v2_hdr_base(hdr);
-  uint4* smp = reinterpret_cast<uint4*>(rec + lane * 32);
-  smp[0] = make_uint4(s.sm[0], s.sm[1], s.sm[2], s.sm[3]);
-  smp[1] = make_uint4(s.sm[4], s.sm[5], s.sm[6], s.sm[7]);
-  if (w != V2_RAW_WIDTH && w > 0) {
-    uint32_t code[8];
-    codes_lane(s, base, (1u << w) - 1u, code);
-    const uint32_t zm = zero_mask(code);
-    int n_esc;
-    const int pos = warp_excl_scan(__popc(zm), lane, n_esc);
-    if (128 * w + n_esc > V2_CHUNK_ELEMS) {
-      w = V2_RAW_WIDTH;
-      hdr = v2_header(0, V2_RAW_WIDTH, 0);
-    } else {
-      hdr = v2_header(base, w, n_esc);
-      uint32_t* pl = reinterpret_cast<uint32_t*>(rec + 1024) + lane;
-      pl[0] = plane_word<0>(code);
-      if (w > 1) pl[32] = plane_word<1>(code);
-      if (w > 2) pl[64] = plane_word<2>(code);
-      if (w > 3) pl[96] = plane_word<3>(code);
-      scatter_escapes(rec + 1024 + 128 * w + pos, s, zm);
-    }
-  }
-  if (w == V2_RAW_WIDTH) {
-    uint4* ep = reinterpret_cast<uint4*>(rec + 1024 + lane * 32);
-    ep[0] = make_uint4(s.ex[0], s.ex[1], s.ex[2], s.ex[3]);
-    ep[1] = make_uint4(s.ex[4], s.ex[5], s.ex[6], s.ex[7]);
-  }
-  return hdr;
-}
-
-// Decode one chunk record into split fields.
-__device__ __forceinline__ void v2_decode_chunk(const uint8_t* rec, uint32_t hdr, int lane, LaneSplit& s) {
-  const int w = v2_hdr_width(hdr);
-  const int base = v2_hdr_base(hdr);
-  const uint4* smp = reinterpret_cast<const uint4*>(rec + lane * 32);
-  const uint4 a = smp[0], b = smp[1];
-  s.sm[0] = a.x; s.sm[1] = a.y; s.sm[2] = a.z; s.sm[3] = a.w;
-  s.sm[4] = b.x; s.sm[5] = b.y; s.sm[6] = b.z; s.sm[7] = b.w;
-  if (w == V2_RAW_WIDTH) {
-    const uint4* ep = reinterpret_cast<const uint4*>(rec + 1024 + lane * 32);
-    const uint4 c = ep[0], d = ep[1];
-    s.ex[0] = c.x; s.ex[1] = c.y; s.ex[2] = c.z; s.ex[3] = c.w;
-    s.ex[4] = d.x; s.ex[5] = d.y; s.ex[6] = d.z; s.ex[7] = d.w;
-    return;
-  }
-  if (w == 0) {
-    const uint32_t e4 = rep4((uint32_t)base);
-#pragma unroll
-    for (int k = 0; k < 8; ++k) s.ex[k] = e4;
-    return;
-  }
-  uint32_t planes[4] = {0, 0, 0, 0};
-  const uint32_t* pl = reinterpret_cast<const uint32_t*>(rec + 1024) + lane;
-  planes[0] = pl[0];
-  if (w > 1) planes[1] = pl[32];
-  if (w > 2) planes[2] = pl[64];
-  if (w > 3) planes[3] = pl[96];
-  uint32_t zm = ~planes[0];
-  if (w > 1) zm &= ~planes[1];
-  if (w > 2) zm &= ~planes[2];
-  if (w > 3) zm &= ~planes[3];
-  int total;
-  const int pos = warp_excl_scan(__popc(zm), lane, total);
-  const uint8_t* esc = rec + 1024 + 128 * w + pos;
-  switch (w) {
-    case 1: decode_lane<1>(planes, base, esc, s.ex); break;
-    case 2: decode_lane<2>(planes, base, esc, s.ex); break;
-    case 3: decode_lane<3>(planes, base, esc, s.ex); break;
-    default: decode_lane<4>(planes, base, esc, s.ex); break;
-  }
-}
 
 __global__ void __launch_bounds__(256) v2_encode_kernel(const uint16_t* __restrict__ in, int64_t n,
                                                         uint8_t* __restrict__ records,

@@ -1,0 +1,457 @@
+// Fused compressed collectives over NVLink peer memory (sm_100a): one kernel per collective does
+// encode -> push into the peers' symmetric staging buffers -> signal -> bounded wait -> decode
+// (-> fp32 reduce).  No NCCL call, no host sync, no allocation; sizes travel in band (one uint32
+// header per chunk), so only the used bytes of each v2 record cross the wire.
+//
+// Symmetric buffer layout (identical on every rank; `peers[q]` is rank q's buffer in this rank's
+// address space, obtained from the symmetric-memory rendezvous):
+//   [0, 4096)                 control: done[world] (uint32), local counters
+//   [4096, 4096 + flag_bytes) flags[2 parities][world sources][max_groups] (uint32)
+//   data                      2 parities x world source slots; slot = header table + records
+// A "group" is 64 chunks (65536 elements).  The pusher CTAs encode group after group and, after a
+// system-scope fence, release-store flag[parity][me][group] = seq on the receivers.  The decoder
+// CTAs acquire-load their local flags and decode as groups arrive, so push, transfer and decode
+// overlap inside one launch.  Buffers alternate by call parity; before pushing call `seq` a rank
+// waits until every peer has reported done >= seq - 2 (it finished reading that parity).
+// Waits are bounded by wall time; on expiry the kernel records {code, peer, group} in the status
+// words of its own control block and returns normally, leaving the context usable.
+//
+// Peer memory is only touched with plain ld/st (st.release.sys for flags); no bulk-tensor copies.
+#include <cuda_bf16.h>
+
+#include "codec_v2_dev.cuh"
+#include "launch_util.h"
+
+namespace zc {
+
+constexpr int GROUP_CHUNKS = 64;
+constexpr int CTRL_BYTES = 4096;
+// control block word indices (uint32)
+constexpr int CW_DONE = 0;        // done[q], q < 64
+constexpr int CW_COUNTER = 64;    // decoder CTAs finished in this call
+constexpr int CW_STATUS = 65;     // 0 ok, else code
+constexpr int CW_STATUS_PEER = 66;
+constexpr int CW_STATUS_GROUP = 67;
+constexpr int CW_WIRE_LO = 68;    // 64-bit count of record bytes pushed (all calls)
+
+struct SymmLayout {
+  int world, rank;
+  long long nc_max;      // chunks per source slot
+  int max_groups;
+  long long flag_bytes, hdr_bytes, slot_bytes, parity_bytes;
+};
+
+__device__ __forceinline__ uint32_t* ctrl(uint8_t* buf) { return reinterpret_cast<uint32_t*>(buf); }
+__device__ __forceinline__ uint32_t* flag_ptr(uint8_t* buf, const SymmLayout& L, int parity, int src, long long g) {
+  return reinterpret_cast<uint32_t*>(buf + CTRL_BYTES) + ((long long)parity * L.world + src) * L.max_groups + g;
+}
+__device__ __forceinline__ uint8_t* slot_ptr(uint8_t* buf, const SymmLayout& L, int parity, int src) {
+  return buf + CTRL_BYTES + L.flag_bytes + parity * L.parity_bytes + src * L.slot_bytes;
+}
+
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ unsigned long long now_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+// spin until *p >= want (sequence numbers only grow); false on timeout
+__device__ __forceinline__ bool wait_ge(const uint32_t* p, uint32_t want, unsigned long long limit_ns) {
+  if ((int)(ld_acquire_sys(p) - want) >= 0) return true;
+  const unsigned long long t0 = now_ns();
+  for (uint32_t it = 0;; ++it) {
+    if ((int)(ld_acquire_sys(p) - want) >= 0) return true;
+    if ((it & 31u) == 31u && now_ns() - t0 > limit_ns) return false;
+    __nanosleep(64);
+  }
+}
+__device__ __forceinline__ void set_status(uint8_t* local, int code, int peer, long long group) {
+  uint32_t* c = ctrl(local);
+  if (atomicCAS(c + CW_STATUS, 0u, (uint32_t)code) == 0u) {
+    c[CW_STATUS_PEER] = (uint32_t)peer;
+    c[CW_STATUS_GROUP] = (uint32_t)group;
+  }
+}
+
+// copy `bytes` (rounded up to 16) from shared memory to global/peer memory, warp-cooperative
+__device__ __forceinline__ void warp_copy16(uint8_t* dst, const uint8_t* src, int bytes, int lane) {
+  const int nv = (bytes + 15) >> 4;
+  for (int i = lane; i < nv; i += 32)
+    reinterpret_cast<uint4*>(dst)[i] = reinterpret_cast<const uint4*>(src)[i];
+}
+
+struct AgArgs {
+  const uint16_t* in;     // this rank's shard, n elements
+  uint16_t* out;          // world * n elements
+  uint8_t* const* peers;  // device array of world buffer pointers
+  uint8_t* local;         // == peers[rank]
+  long long n;
+  uint32_t seq;
+  int push_ctas;
+  unsigned long long timeout_ns;
+  SymmLayout L;
+};
+
+__global__ void __launch_bounds__(256) symm_all_gather_kernel(const AgArgs a) {
+  __shared__ __align__(16) uint8_t srec[8][V2_SLOT_BYTES];
+  __shared__ int s_ok;
+  const SymmLayout& L = a.L;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int parity = a.seq & 1;
+  const long long nc = (a.n + V2_CHUNK_ELEMS - 1) / V2_CHUNK_ELEMS;
+  const long long ngroups = (nc + GROUP_CHUNKS - 1) / GROUP_CHUNKS;
+  if (tid == 0) s_ok = 1;
+  __syncthreads();
+
+  if ((int)blockIdx.x < a.push_ctas) {
+    // ---- pusher --------------------------------------------------------------------------------
+    if (tid < L.world && tid != L.rank && a.seq >= 3) {
+      if (!wait_ge(ctrl(a.local) + CW_DONE + tid, a.seq - 2, a.timeout_ns)) {
+        set_status(a.local, 1, tid, -1);
+        s_ok = 0;
+      }
+    }
+    __syncthreads();
+    if (!s_ok) return;
+    const bool in_al = (reinterpret_cast<uintptr_t>(a.in) & 15) == 0;
+    uint16_t* own = a.out + (long long)L.rank * a.n;
+    const bool copy_own = own != a.in;
+    const bool own_al = (reinterpret_cast<uintptr_t>(own) & 15) == 0;
+    unsigned long long pushed = 0;
+    for (long long g = blockIdx.x; g < ngroups; g += a.push_ctas) {
+      for (int it = 0; it < GROUP_CHUNKS / 8; ++it) {
+        const long long c = g * GROUP_CHUNKS + it * 8 + warp;
+        if (c >= nc) break;
+        const long long e0 = c * V2_CHUNK_ELEMS + lane * 32;
+        LaneIn li;
+        load_lane(a.in + e0, a.n - e0, in_al, li);
+        if (copy_own) store_lane(own + e0, a.n - e0, own_al, li);
+        LaneSplit s;
+        split_lane(li, s);
+        const uint32_t hdr = v2_encode_chunk(s, srec[warp], lane);
+        __syncwarp();
+        const int used = v2_record_bytes(hdr);
+        for (int q = 0; q < L.world; ++q) {
+          if (q == L.rank) continue;
+          uint8_t* slot = slot_ptr(a.peers[q], L, parity, L.rank);
+          warp_copy16(slot + L.hdr_bytes + c * V2_SLOT_BYTES, srec[warp], used, lane);
+          if (lane == 0) reinterpret_cast<uint32_t*>(slot)[c] = hdr;
+        }
+        if (lane == 0) pushed += (unsigned long long)(used + 4) * (L.world - 1);
+        __syncwarp();
+      }
+      __threadfence_system();
+      __syncthreads();
+      if (tid < L.world && tid != L.rank) st_release_sys(flag_ptr(a.peers[tid], L, parity, L.rank, g), a.seq);
+    }
+    if (lane == 0 && pushed) atomicAdd(reinterpret_cast<unsigned long long*>(ctrl(a.local) + CW_WIRE_LO), pushed);
+    return;
+  }
+  // ---- decoder ---------------------------------------------------------------------------------
+  const int dec_ctas = gridDim.x - a.push_ctas;
+  const long long items = ngroups * (L.world - 1);
+  for (long long i = (long long)blockIdx.x - a.push_ctas; i < items; i += dec_ctas) {
+    const long long g = i / (L.world - 1);
+    int src = (int)(i % (L.world - 1));
+    if (src >= L.rank) ++src;
+    uint32_t* fl = flag_ptr(a.local, L, parity, src, g);
+    if (tid == 0 && !wait_ge(fl, a.seq, a.timeout_ns)) {
+      set_status(a.local, 2, src, g);
+      s_ok = 0;
+    }
+    __syncthreads();
+    if (!s_ok) break;
+    (void)ld_acquire_sys(fl);  // every thread orders its own reads of the staged bytes after the flag
+    const uint8_t* slot = slot_ptr(a.local, L, parity, src);
+    uint16_t* dst = a.out + (long long)src * a.n;
+    const bool al = (reinterpret_cast<uintptr_t>(dst) & 15) == 0;
+    for (int it = 0; it < GROUP_CHUNKS / 8; ++it) {
+      const long long c = g * GROUP_CHUNKS + it * 8 + warp;
+      if (c >= nc) break;
+      const uint32_t hdr = __ldcg(reinterpret_cast<const uint32_t*>(slot) + c);
+      LaneSplit s;
+      v2_decode_chunk(slot + L.hdr_bytes + c * V2_SLOT_BYTES, hdr, lane, s);
+      LaneIn o;
+      join_lane(s, o);
+      const long long e0 = c * V2_CHUNK_ELEMS + lane * 32;
+      store_lane(dst + e0, a.n - e0, al, o);
+    }
+  }
+  // last decoder CTA of this call tells every peer that this rank is done with the parity buffer
+  __syncthreads();
+  if (tid == 0) {
+    uint32_t* c = ctrl(a.local);
+    __threadfence();
+    const uint32_t prev = atomicAdd(c + CW_COUNTER, 1u);
+    if (prev + 1 == (uint32_t)dec_ctas) {
+      c[CW_COUNTER] = 0;
+      __threadfence_system();
+      for (int q = 0; q < L.world; ++q)
+        if (q != L.rank) st_release_sys(ctrl(a.peers[q]) + CW_DONE + L.rank, a.seq);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// reduce-scatter
+// ---------------------------------------------------------------------------------------------
+struct RsArgs {
+  const void* in;         // [world, shard] fp32 or bf16
+  void* out;              // [shard] fp32 or bf16
+  uint16_t* residual;     // [world * shard] bf16 or null
+  uint8_t* const* peers;
+  uint8_t* local;
+  long long shard;
+  uint32_t seq;
+  int push_ctas, in_fp32, out_fp32;
+  float scale;
+  unsigned long long timeout_ns;
+  SymmLayout L;
+};
+
+__device__ __forceinline__ float bf16_bits_to_f(uint32_t b) { return __uint_as_float(b << 16); }
+__device__ __forceinline__ uint32_t f_to_bf16_bits(float f) {
+  return (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(f));
+}
+
+// load 32 values of one lane as fp32 (zero past `valid`)
+__device__ __forceinline__ void load_lane_f32(const void* base, bool fp32, long long e0, long long valid, float (&v)[32]) {
+  if (fp32) {
+    const float* p = reinterpret_cast<const float*>(base) + e0;
+    if (valid >= 32 && (reinterpret_cast<uintptr_t>(p) & 15) == 0) {
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        const float4 f = __ldg(reinterpret_cast<const float4*>(p) + k);
+        v[4 * k] = f.x; v[4 * k + 1] = f.y; v[4 * k + 2] = f.z; v[4 * k + 3] = f.w;
+      }
+    } else {
+#pragma unroll
+      for (int k = 0; k < 32; ++k) v[k] = k < valid ? __ldg(p + k) : 0.f;
+    }
+  } else {
+    LaneIn li;
+    const uint16_t* p = reinterpret_cast<const uint16_t*>(base) + e0;
+    load_lane(p, valid, (reinterpret_cast<uintptr_t>(p) & 15) == 0, li);
+#pragma unroll
+    for (int k = 0; k < 16; ++k) {
+      v[2 * k] = bf16_bits_to_f(li.w[k] & 0xFFFFu);
+      v[2 * k + 1] = bf16_bits_to_f(li.w[k] >> 16);
+    }
+  }
+}
+
+__global__ void __launch_bounds__(256) symm_reduce_scatter_kernel(const RsArgs a) {
+  __shared__ __align__(16) uint8_t srec[8][V2_SLOT_BYTES];
+  __shared__ int s_ok;
+  const SymmLayout& L = a.L;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int parity = a.seq & 1;
+  const long long nc = (a.shard + V2_CHUNK_ELEMS - 1) / V2_CHUNK_ELEMS;
+  const long long ngroups = (nc + GROUP_CHUNKS - 1) / GROUP_CHUNKS;
+  if (tid == 0) s_ok = 1;
+  __syncthreads();
+
+  if ((int)blockIdx.x < a.push_ctas) {
+    if (tid < L.world && tid != L.rank && a.seq >= 3) {
+      if (!wait_ge(ctrl(a.local) + CW_DONE + tid, a.seq - 2, a.timeout_ns)) {
+        set_status(a.local, 1, tid, -1);
+        s_ok = 0;
+      }
+    }
+    __syncthreads();
+    if (!s_ok) return;
+    unsigned long long pushed = 0;
+    // work item = (destination, group); destinations interleaved so all links are busy
+    const long long items = ngroups * (L.world - 1);
+    for (long long i = blockIdx.x; i < items; i += a.push_ctas) {
+      const long long g = i / (L.world - 1);
+      int q = (int)(i % (L.world - 1));
+      q = (L.rank + 1 + q) % L.world;  // start with the next rank: spreads traffic over peers
+      uint8_t* slot = slot_ptr(a.peers[q], L, parity, L.rank);
+      for (int it = 0; it < GROUP_CHUNKS / 8; ++it) {
+        const long long c = g * GROUP_CHUNKS + it * 8 + warp;
+        if (c >= nc) break;
+        const long long e0 = c * V2_CHUNK_ELEMS + lane * 32;
+        const long long valid = a.shard - e0;
+        float v[32];
+        load_lane_f32(a.in, a.in_fp32, (long long)q * a.shard + e0, valid, v);
+        LaneIn li;
+        if (a.residual && a.in_fp32) {
+          uint16_t* rp = a.residual + (long long)q * a.shard + e0;
+          LaneIn r;
+          const bool ral = (reinterpret_cast<uintptr_t>(rp) & 15) == 0;
+          load_lane(rp, valid, ral, r);
+#pragma unroll
+          for (int k = 0; k < 16; ++k) {
+            const float x0 = v[2 * k] + bf16_bits_to_f(r.w[k] & 0xFFFFu);
+            const float x1 = v[2 * k + 1] + bf16_bits_to_f(r.w[k] >> 16);
+            const uint32_t b0 = f_to_bf16_bits(x0), b1 = f_to_bf16_bits(x1);
+            li.w[k] = b0 | (b1 << 16);
+            r.w[k] = f_to_bf16_bits(x0 - bf16_bits_to_f(b0)) | (f_to_bf16_bits(x1 - bf16_bits_to_f(b1)) << 16);
+          }
+          store_lane(rp, valid, ral, r);
+        } else {
+#pragma unroll
+          for (int k = 0; k < 16; ++k) li.w[k] = f_to_bf16_bits(v[2 * k]) | (f_to_bf16_bits(v[2 * k + 1]) << 16);
+        }
+        LaneSplit s;
+        split_lane(li, s);
+        const uint32_t hdr = v2_encode_chunk(s, srec[warp], lane);
+        __syncwarp();
+        const int used = v2_record_bytes(hdr);
+        warp_copy16(slot + L.hdr_bytes + c * V2_SLOT_BYTES, srec[warp], used, lane);
+        if (lane == 0) {
+          reinterpret_cast<uint32_t*>(slot)[c] = hdr;
+          pushed += (unsigned long long)(used + 4);
+        }
+        __syncwarp();
+      }
+      __threadfence_system();
+      __syncthreads();
+      if (tid == 0) st_release_sys(flag_ptr(a.peers[q], L, parity, L.rank, g), a.seq);
+    }
+    if (lane == 0 && pushed) atomicAdd(reinterpret_cast<unsigned long long*>(ctrl(a.local) + CW_WIRE_LO), pushed);
+    return;
+  }
+  // ---- decoder + reduce ------------------------------------------------------------------------
+  const int dec_ctas = gridDim.x - a.push_ctas;
+  for (long long g = (long long)blockIdx.x - a.push_ctas; g < ngroups; g += dec_ctas) {
+    if (tid < L.world && tid != L.rank) {
+      if (!wait_ge(flag_ptr(a.local, L, parity, tid, g), a.seq, a.timeout_ns)) {
+        set_status(a.local, 2, tid, g);
+        s_ok = 0;
+      }
+    }
+    __syncthreads();
+    if (!s_ok) break;
+    for (int q = 0; q < L.world; ++q)
+      if (q != L.rank) (void)ld_acquire_sys(flag_ptr(a.local, L, parity, q, g));
+    for (int it = 0; it < GROUP_CHUNKS / 8; ++it) {
+      const long long c = g * GROUP_CHUNKS + it * 8 + warp;
+      if (c >= nc) break;
+      const long long e0 = c * V2_CHUNK_ELEMS + lane * 32;
+      const long long valid = a.shard - e0;
+      float acc[32];
+#pragma unroll
+      for (int k = 0; k < 32; ++k) acc[k] = 0.f;
+      for (int p = 0; p < L.world; ++p) {  // fixed rank order: deterministic sum
+        if (p == L.rank) {
+          float v[32];
+          load_lane_f32(a.in, a.in_fp32, (long long)p * a.shard + e0, valid, v);
+#pragma unroll
+          for (int k = 0; k < 32; ++k) acc[k] += v[k];
+        } else {
+          const uint8_t* slot = slot_ptr(a.local, L, parity, p);
+          const uint32_t hdr = __ldcg(reinterpret_cast<const uint32_t*>(slot) + c);
+          LaneSplit s;
+          v2_decode_chunk(slot + L.hdr_bytes + c * V2_SLOT_BYTES, hdr, lane, s);
+          LaneIn o;
+          join_lane(s, o);
+#pragma unroll
+          for (int k = 0; k < 16; ++k) {
+            acc[2 * k] += bf16_bits_to_f(o.w[k] & 0xFFFFu);
+            acc[2 * k + 1] += bf16_bits_to_f(o.w[k] >> 16);
+          }
+        }
+      }
+      if (valid <= 0) continue;
+      if (a.out_fp32) {
+        float* dst = reinterpret_cast<float*>(a.out) + e0;
+        if (valid >= 32 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+#pragma unroll
+          for (int k = 0; k < 8; ++k)
+            reinterpret_cast<float4*>(dst)[k] = make_float4(acc[4 * k] * a.scale, acc[4 * k + 1] * a.scale,
+                                                            acc[4 * k + 2] * a.scale, acc[4 * k + 3] * a.scale);
+        } else {
+#pragma unroll
+          for (int k = 0; k < 32; ++k)
+            if (k < valid) dst[k] = acc[k] * a.scale;
+        }
+      } else {
+        LaneIn o;
+#pragma unroll
+        for (int k = 0; k < 16; ++k)
+          o.w[k] = f_to_bf16_bits(acc[2 * k] * a.scale) | (f_to_bf16_bits(acc[2 * k + 1] * a.scale) << 16);
+        uint16_t* dst = reinterpret_cast<uint16_t*>(a.out) + e0;
+        store_lane(dst, valid, (reinterpret_cast<uintptr_t>(dst) & 15) == 0, o);
+      }
+    }
+  }
+  __syncthreads();
+  if (tid == 0) {
+    uint32_t* c = ctrl(a.local);
+    __threadfence();
+    const uint32_t prev = atomicAdd(c + CW_COUNTER, 1u);
+    if (prev + 1 == (uint32_t)dec_ctas) {
+      c[CW_COUNTER] = 0;
+      __threadfence_system();
+      for (int q = 0; q < L.world; ++q)
+        if (q != L.rank) st_release_sys(ctrl(a.peers[q]) + CW_DONE + L.rank, a.seq);
+    }
+  }
+}
+
+static SymmLayout make_layout(int world, int rank, long long nc_max) {
+  SymmLayout L;
+  L.world = world;
+  L.rank = rank;
+  L.nc_max = nc_max;
+  L.max_groups = (int)((nc_max + GROUP_CHUNKS - 1) / GROUP_CHUNKS);
+  L.flag_bytes = align128(2LL * world * L.max_groups * 4);
+  L.hdr_bytes = align128(nc_max * 4);
+  L.slot_bytes = L.hdr_bytes + nc_max * V2_SLOT_BYTES;
+  L.parity_bytes = (long long)world * L.slot_bytes;
+  return L;
+}
+
+}  // namespace zc
+
+extern "C" {
+
+// bytes of symmetric memory a channel needs for messages of up to nc_max chunks per source
+long long zc_symm_buffer_bytes(int world, long long nc_max) {
+  const zc::SymmLayout L = zc::make_layout(world, 0, nc_max);
+  return zc::CTRL_BYTES + L.flag_bytes + 2 * L.parity_bytes;
+}
+
+// in: n bf16 elements; out: world*n; peers: device array of `world` buffer pointers
+int zc_symm_all_gather(const void* in, void* out, void* const* peers, void* local, long long n, int rank, int world,
+                       long long nc_max, unsigned seq, int push_ctas, int dec_ctas, double timeout_s,
+                       cudaStream_t st) {
+  using namespace zc;
+  const long long nc = (n + V2_CHUNK_ELEMS - 1) / V2_CHUNK_ELEMS;
+  if (world < 2 || world > 64 || nc > nc_max || nc == 0 || push_ctas < 1 || dec_ctas < 1) return ERR_BAD_ARG;
+  AgArgs a;
+  a.in = (const uint16_t*)in; a.out = (uint16_t*)out; a.peers = (uint8_t* const*)peers; a.local = (uint8_t*)local;
+  a.n = n; a.seq = seq; a.push_ctas = push_ctas;
+  a.timeout_ns = (unsigned long long)(timeout_s * 1e9);
+  a.L = make_layout(world, rank, nc_max);
+  symm_all_gather_kernel<<<push_ctas + dec_ctas, 256, 0, st>>>(a);
+  return launch_status();
+}
+
+int zc_symm_reduce_scatter(const void* in, void* out, void* residual, void* const* peers, void* local,
+                           long long shard, int rank, int world, long long nc_max, unsigned seq, int in_fp32,
+                           int out_fp32, float scale, int push_ctas, int dec_ctas, double timeout_s,
+                           cudaStream_t st) {
+  using namespace zc;
+  const long long nc = (shard + V2_CHUNK_ELEMS - 1) / V2_CHUNK_ELEMS;
+  if (world < 2 || world > 64 || nc > nc_max || nc == 0 || push_ctas < 1 || dec_ctas < 1) return ERR_BAD_ARG;
+  RsArgs a;
+  a.in = in; a.out = out; a.residual = (uint16_t*)residual; a.peers = (uint8_t* const*)peers;
+  a.local = (uint8_t*)local; a.shard = shard; a.seq = seq; a.push_ctas = push_ctas; a.in_fp32 = in_fp32;
+  a.out_fp32 = out_fp32; a.scale = scale;
+  a.timeout_ns = (unsigned long long)(timeout_s * 1e9);
+  a.L = make_layout(world, rank, nc_max);
+  symm_reduce_scatter_kernel<<<push_ctas + dec_ctas, 256, 0, st>>>(a);
+  return launch_status();
+}
+
+}  // extern "C"

@@ -68,10 +68,11 @@ class LlamaBlock(nn.Module):
         self.attn_norm = RMSNorm(d, cfg.norm_eps)
         self.mlp_norm = RMSNorm(d, cfg.norm_eps)
 
-    def forward(self, x, cos, sin):
+    def forward(self, x):
         cfg = self.cfg
         B, S, d = x.shape
         hd, Hq, Hkv = cfg.head_dim, cfg.n_heads, cfg.n_kv_heads
+        cos, sin = rope.cached_tables(S, hd, cfg.rope_theta, x.device)
         h = self.attn_norm(x)
         qkv = self.wqkv(h).view(B, S, Hq + 2 * Hkv, hd)
         o = attn_ops.causal_attention(qkv, Hq, Hkv, None, cos, sin)
@@ -101,10 +102,8 @@ class LlamaForCausalLM(nn.Module):
         self.model = LlamaBackbone(cfg)
         self.lm_head = Linear(cfg.d_model, cfg.vocab_size, cfg.init_std)
         self.activation_checkpointing = False
-        self._rope_cache: dict = {}
 
     def reset_parameters(self):
-        self._rope_cache.clear()
         if self.config.tie_embeddings:
             self.lm_head.weight = self.model.embed_tokens.weight
 
@@ -113,22 +112,15 @@ class LlamaForCausalLM(nn.Module):
         ``to_empty`` (train.py:125-128)."""
         self.apply(lambda m: m.reset_parameters() if hasattr(m, "reset_parameters") else None)
 
-    def _rope(self, S: int, device):
-        key = (S, str(device))
-        if key not in self._rope_cache:
-            self._rope_cache[key] = rope.rope_tables(S, self.config.head_dim, self.config.rope_theta, device)
-        return self._rope_cache[key]
-
     def forward(self, input_ids: torch.Tensor, labels: Optional[torch.Tensor] = None,
                 return_logits: bool = False, **_ignored) -> CausalLMOutput:
         B, S = input_ids.shape
-        cos, sin = self._rope(S, input_ids.device)
         x = self.model.embed_tokens(input_ids)
         for layer in self.model.layers:
             if self.activation_checkpointing and torch.is_grad_enabled():
-                x = checkpoint(layer, x, cos, sin, use_reentrant=False)
+                x = checkpoint(layer, x, use_reentrant=False)
             else:
-                x = layer(x, cos, sin)
+                x = layer(x)
         x = self.model.norm(x)
         logits = self.lm_head(x)
         loss = None

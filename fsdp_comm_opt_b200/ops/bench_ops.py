@@ -1,0 +1,143 @@
+"""Device-timed micro-benchmarks of the hot kernels against their roofline denominators.
+
+    python -m fsdp_comm_opt_b200.ops.bench_ops [--peaks MEASURED_PEAKS.json] [--only gemm,attn,codec,elt]
+
+Every number: >= 3 warm-up launches, CUDA events on the launching stream around ``iters`` launches,
+inputs larger than the 126 MB L2 or an L2 flush between launches (stated per line).  Fractions are
+"of measured" peaks when the peaks file exists, else "of fallback" (6.65 TB/s, 1.59 PFLOP/s).
+Prints one JSON object per line.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+import torch
+
+from . import attention, codec, gemm, loss, norm, swiglu
+from .. import _lib
+
+
+def _time(fn, iters=10, warmup=3, flush=None):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    total = 0.0
+    for _ in range(iters):
+        if flush is not None:
+            flush.add_(1)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        total += e0.elapsed_time(e1)
+    return total / iters
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--peaks", default="MEASURED_PEAKS.json")
+    ap.add_argument("--only", default="gemm,attn,codec,elt")
+    ap.add_argument("--iters", type=int, default=10)
+    args = ap.parse_args()
+    if os.path.exists(args.peaks):
+        pk = json.load(open(args.peaks))
+        hbm, tf, tag = pk["hbm_gbs"], pk["bf16_tflops"], "of measured"
+    else:
+        hbm, tf, tag = 6650.0, 1590.0, "of fallback"
+    dev = torch.device("cuda")
+    flush = torch.zeros(256 << 20, dtype=torch.uint8, device=dev)  # 256 MB > L2
+    only = set(args.only.split(","))
+
+    def emit(**kw):
+        print(json.dumps(kw), flush=True)
+
+    if "gemm" in only:
+        shapes = [("fwd wgu", 4096, 28672, 4096, False, True), ("fwd wd", 4096, 4096, 14336, False, True),
+                  ("fwd qkv", 4096, 6144, 4096, False, True), ("dgrad wgu", 4096, 4096, 28672, False, False),
+                  ("wgrad wgu", 28672, 4096, 4096, True, False), ("lm_head", 4096, 128256, 4096, False, True),
+                  ("square 8192", 8192, 8192, 8192, False, True)]
+        for name, M, N, K, ta, tb in shapes:
+            a = torch.randn((K, M) if ta else (M, K), device=dev).bfloat16()
+            b = torch.randn((N, K) if tb else (K, N), device=dev).bfloat16()
+            out = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+            res = {}
+            for be in ("tcgen05", "cublas"):
+                gemm.set_backend(be)
+                ms = _time(lambda: gemm.gemm(a, b, ta, tb, out=out), args.iters, flush=flush)
+                res[be] = 2.0 * M * N * K / ms / 1e9
+            gemm.set_backend("auto")
+            emit(kernel="gemm_bf16", case=name, M=M, N=N, K=K, tflops_tcgen05=round(res["tcgen05"], 1),
+                 tflops_cublas=round(res["cublas"], 1), frac=round(res["tcgen05"] / tf, 3), frac_of=tag,
+                 l2="flushed between launches")
+    if "attn" in only:
+        for B, S, Hq, Hkv, D in [(1, 4096, 32, 8, 128), (2, 4096, 40, 40, 128), (1, 8192, 32, 8, 128)]:
+            qkv = (torch.randn(B, S, Hq + 2 * Hkv, D, device=dev) * 0.5).bfloat16().requires_grad_()
+            o = attention.causal_attention(qkv, Hq, Hkv)
+            g = torch.randn_like(o)
+            fl = 4.0 * B * Hq * S * S * D / 2
+            ms_f = _time(lambda: attention.causal_attention(qkv.detach(), Hq, Hkv), args.iters, flush=flush)
+            ms_b = _time(lambda: torch.autograd.grad(attention.causal_attention(qkv, Hq, Hkv), qkv, g), args.iters,
+                         flush=flush) - ms_f
+            q, k, v = (t.transpose(1, 2) for t in qkv.detach().split([Hq, Hkv, Hkv], dim=2))
+            ms_sdpa = _time(lambda: torch.nn.functional.scaled_dot_product_attention(q, k, v, is_causal=True,
+                                                                                     enable_gqa=True),
+                            args.iters, flush=flush)
+            emit(kernel="attn", B=B, S=S, Hq=Hq, Hkv=Hkv, D=D, fwd_tflops=round(fl / ms_f / 1e9, 1),
+                 bwd_tflops=round(2.5 * fl / max(ms_b, 1e-6) / 1e9, 1), sdpa_fwd_tflops=round(fl / ms_sdpa / 1e9, 1),
+                 frac_fwd=round(fl / ms_f / 1e9 / tf, 3), frac_of=tag, l2="flushed between launches")
+    if "codec" in only:
+        n = 1 << 28  # 512 MB of bf16 > L2
+        x = (torch.randn(n, device=dev) * 0.02).bfloat16()
+        rec, hdr = codec.v2_encode(x)
+        out = torch.empty_like(x)
+        used = int(codec.v2_record_bytes(hdr).sum().item()) + 4 * hdr.numel()
+        ms_e = _time(lambda: codec.v2_encode(x, rec, hdr), args.iters)
+        ms_d = _time(lambda: codec.v2_decode(rec, hdr, n, out), args.iters)
+        emit(kernel="v2_encode", elems=n, gbs=round((2 * n + used) / ms_e / 1e6, 1),
+             frac=round((2 * n + used) / ms_e / 1e6 / hbm, 3), frac_of=tag, bytes_per_elem=round(used / n, 4),
+             l2="input larger than L2")
+        emit(kernel="v2_decode", elems=n, gbs=round((2 * n + used) / ms_d / 1e6, 1),
+             frac=round((2 * n + used) / ms_d / 1e6 / hbm, 3), frac_of=tag, l2="input larger than L2")
+        per = codec.pad_to_block(n)
+        n_8 = torch.tensor([per], dtype=torch.int32, device=dev)
+        bases = torch.full((256,), 116, dtype=torch.int32, device=dev)
+        det = torch.empty(codec.v1_det_bytes(per), dtype=torch.uint8, device=dev)
+        scr = torch.empty(per, dtype=torch.uint8, device=dev)
+        esc = torch.empty(per, dtype=torch.uint8, device=dev)
+        gc = torch.zeros(1, dtype=torch.int32, device=dev)
+        ms_e1 = _time(lambda: codec.v1_compress_split_store(x, n_8, bases, det, scr, esc, gc, 1), args.iters)
+        cnt = int(gc[0])
+        ms_d1 = _time(lambda: codec.v1_decompress_split_store(det, esc, n_8, gc, out, 1), args.iters)
+        b1 = det.numel() + cnt
+        emit(kernel="v1_encode_split", elems=n, gbs=round((2 * n + b1 + 2 * cnt) / ms_e1 / 1e6, 1),
+             frac=round((2 * n + b1 + 2 * cnt) / ms_e1 / 1e6 / hbm, 3), frac_of=tag, bytes_per_elem=round(b1 / n, 4))
+        emit(kernel="v1_decode_split", elems=n, gbs=round((2 * n + b1) / ms_d1 / 1e6, 1),
+             frac=round((2 * n + b1) / ms_d1 / 1e6 / hbm, 3), frac_of=tag)
+    if "elt" in only:
+        T, d, F_, V = 16384, 4096, 14336, 128256
+        x = torch.randn(T, d, device=dev).bfloat16()
+        w = torch.ones(d, device=dev).bfloat16()
+        ms = _time(lambda: norm.rms_norm(x, w, 1e-5), args.iters)
+        emit(kernel="rmsnorm_fwd", rows=T, cols=d, gbs=round(4 * T * d / ms / 1e6, 1), frac=round(4 * T * d / ms / 1e6 / hbm, 3), frac_of=tag)
+        gu = torch.randn(T, 2 * F_, device=dev).bfloat16()
+        ms = _time(lambda: swiglu.swiglu(gu), args.iters)
+        emit(kernel="swiglu_fwd", rows=T, F=F_, gbs=round(6 * T * F_ / ms / 1e6, 1), frac=round(6 * T * F_ / ms / 1e6 / hbm, 3), frac_of=tag)
+        lg = torch.randn(4096, V, device=dev).bfloat16()
+        lab = torch.randint(0, V, (4096,), device=dev)
+        ms = _time(lambda: loss.cross_entropy(lg, lab), args.iters)
+        emit(kernel="ce_fwd_bwd", rows=4096, V=V, gbs=round(4 * 4096 * V / ms / 1e6, 1), frac=round(4 * 4096 * V / ms / 1e6 / hbm, 3), frac_of=tag,
+             note="algorithmic bytes: one read + one write of the logits")
+        n = 1 << 28
+        p = torch.randn(n, device=dev).bfloat16(); g = torch.randn(n, device=dev).bfloat16()
+        m = torch.zeros_like(p); v = torch.zeros_like(p)
+        lib = _lib.cuda()
+        ms = _time(lambda: lib.zc_adamw(p.data_ptr(), g.data_ptr(), m.data_ptr(), v.data_ptr(), n, 0, 0, 0, 1e-4, 0.9, 0.999,
+                                        1e-8, 0.01, 0.1, 0.001, 0, _lib.stream_ptr()), args.iters)
+        emit(kernel="adamw_bf16", elems=n, gbs=round(14 * n / ms / 1e6, 1), frac=round(14 * n / ms / 1e6 / hbm, 3), frac_of=tag)
+
+
+if __name__ == "__main__":
+    main()

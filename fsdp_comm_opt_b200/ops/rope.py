@@ -11,6 +11,22 @@ import torch
 from .. import _lib
 
 
+_TABLES: dict = {}
+
+
+def cached_tables(seq_len: int, head_dim: int, theta: float, device) -> tuple[torch.Tensor, torch.Tensor]:
+    """fp32 cos/sin tables, cached per (seq_len, head_dim, theta, device).  Modules fetch them here
+    instead of receiving them as forward arguments: FSDP2's mixed-precision policy casts floating
+    point forward inputs to the parameter dtype, which would silently turn the tables into bf16."""
+    key = (int(seq_len), int(head_dim), float(theta), str(device))
+    t = _TABLES.get(key)
+    if t is None:
+        if len(_TABLES) > 16:
+            _TABLES.clear()
+        t = _TABLES[key] = rope_tables(seq_len, head_dim, theta, device)
+    return t
+
+
 def rope_tables(seq_len: int, head_dim: int, theta: float, device) -> tuple[torch.Tensor, torch.Tensor]:
     inv = 1.0 / (theta ** (torch.arange(0, head_dim, 2, dtype=torch.float32, device=device) / head_dim))
     t = torch.arange(seq_len, dtype=torch.float32, device=device)
@@ -22,9 +38,12 @@ def _rotate(qkv: torch.Tensor, cos, sin, n_rot_heads: int, head_dim: int, seq_le
     """qkv: [T, H_total*D] contiguous, token t sits at position t % seq_len."""
     T = qkv.shape[0]
     total_heads = qkv.shape[1] // head_dim
+    if cos.dtype != torch.float32 or sin.dtype != torch.float32 or cos.shape != (seq_len, head_dim // 2):
+        raise TypeError("rope tables must be fp32 [seq_len, head_dim/2]")
     if qkv.is_cuda:
         if qkv.dtype != torch.bfloat16 or not qkv.is_contiguous():
             raise TypeError("CUDA rope expects contiguous bf16")
+        cos, sin = cos.contiguous(), sin.contiguous()
         _lib.check(_lib.cuda().zc_rope_inplace(
             qkv.data_ptr(), cos.data_ptr(), sin.data_ptr(), T, seq_len, n_rot_heads, total_heads,
             head_dim, float(sign), _lib.stream_ptr(qkv.device)), "zc_rope_inplace")

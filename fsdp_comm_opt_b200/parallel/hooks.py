@@ -86,12 +86,8 @@ class QuantizedAllGather(_CommBase):
         rank = dist.get_rank(group)
         n = x.numel()
         stride = quant_ops.packed_bytes(n)
-        transport = _resolve_transport(self.transport, x.device, group)
-        if transport == "symm":
-            from . import symm
-
-            return symm.channel_for(group, x.device, "ag").all_gather(
-                output_tensor, x, mode="int8", async_op=async_op)
+        # the int8 payload travels through the collective library (NCCL / gloo); the fused
+        # symmetric-memory kernels carry the lossless codec only
         gathered = torch.empty(world, stride, dtype=torch.uint8, device=x.device)
         quant_ops.quantize_pack(x, gathered[rank])
         work = dist.all_gather_into_tensor(gathered.view(-1), gathered[rank], group=group,

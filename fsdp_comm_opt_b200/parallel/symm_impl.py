@@ -1,0 +1,182 @@
+"""Symmetric-memory channels that drive the fused collective kernels (``csrc/symm_collectives.cu``).
+
+A ``Channel`` owns one symmetric buffer per (process group, device, role): control words, arrival
+flags and two parities of staging slots.  The buffer is allocated with
+``torch.distributed._symmetric_memory`` and exchanged once by rendezvous (a collective, so every
+rank must create and grow channels in the same order -- FSDP2 calls its hooks in the same order on
+every rank).  After that a collective is ONE kernel launch on the current stream: no NCCL call, no
+host sync, no allocation.  The reference has no counterpart: all of its traffic goes through
+``dist.all_gather_into_tensor`` (reference: main/zipccl_comm.py:106-132).
+
+Sequence numbers: every call on a channel increments ``seq``; the kernels use ``seq & 1`` as the
+staging parity and wait (bounded) for the peers' ``done >= seq - 2`` before reusing a parity.
+
+Failure reporting: a device wait that runs out sets status words in the control block;
+``check_status()`` (synchronising) turns them into ``SymmTimeout``.  It is called from
+``AggregatedWork.wait`` on the async path and can be called by the training loop between steps.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+import torch
+import torch.distributed as dist
+
+from .. import _lib
+from ..ops import codec
+from .work import AggregatedWork
+
+_CHANNELS: dict = {}
+_AVAILABLE: dict = {}
+
+CTRL_WORDS = 1024
+CW_STATUS, CW_STATUS_PEER, CW_STATUS_GROUP, CW_WIRE_LO = 65, 66, 67, 68
+
+
+class SymmTimeout(RuntimeError):
+    """A bounded device-side wait expired (peer did not arrive in time)."""
+
+    def __init__(self, code: int, peer: int, group: int):
+        what = {1: "waiting for a peer to release the staging buffer", 2: "waiting for a peer's data"}.get(code, "?")
+        super().__init__(f"fused collective timed out {what}: peer rank {peer}, group {group}")
+        self.code, self.peer, self.group = code, peer, group
+
+
+def _symm_mod():
+    import torch.distributed._symmetric_memory as symm_mem
+
+    return symm_mem
+
+
+def available(group) -> bool:
+    """True when symmetric memory can be rendezvoused for ``group`` (probed once, collectively)."""
+    key = group.group_name if hasattr(group, "group_name") else str(group)
+    if key in _AVAILABLE:
+        return _AVAILABLE[key]
+    ok = False
+    try:
+        if dist.get_backend(group) == "nccl" and dist.get_world_size(group) > 1 and hasattr(
+                _lib.cuda()._lib, "zc_symm_all_gather"):
+            symm_mem = _symm_mod()
+            t = symm_mem.empty(4096, dtype=torch.uint8, device=torch.device("cuda", torch.cuda.current_device()))
+            hdl = symm_mem.rendezvous(t, group)
+            ok = hdl is not None and len(hdl.buffer_ptrs) == dist.get_world_size(group)
+    except Exception:
+        ok = False
+    # every rank must agree, otherwise some would wait in a kernel for peers that use NCCL
+    flag = torch.tensor([1 if ok else 0], device=torch.device("cuda", torch.cuda.current_device()))
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=group)
+    ok = bool(flag.item())
+    _AVAILABLE[key] = ok
+    return ok
+
+
+class Channel:
+    def __init__(self, group, device: torch.device, kind: str):
+        self.group, self.device, self.kind = group, device, kind
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.seq = 0
+        self.nc_max = 0
+        self.buf = None
+        self.hdl = None
+        self.timeout_s = float(os.environ.get("ZC_SYMM_TIMEOUT_S", "5"))
+        sm = torch.cuda.get_device_properties(device).multi_processor_count
+        self.push_ctas = int(os.environ.get("ZC_SYMM_PUSH_CTAS", str(max(8, sm // 6))))
+        self.dec_ctas = int(os.environ.get("ZC_SYMM_DEC_CTAS", str(max(8, sm // 4))))
+        self._lib = _lib.cuda()
+        self._lib._lib.zc_symm_buffer_bytes.restype = ctypes.c_int64
+        self._lib._lib.zc_symm_buffer_bytes.argtypes = [ctypes.c_int, ctypes.c_int64]
+
+    # -- buffer management -----------------------------------------------------------------------
+    def reserve(self, numel_per_source: int) -> None:
+        """Make sure messages of ``numel_per_source`` elements per source fit (collective when it
+        has to grow: allocates a new symmetric buffer and rendezvouses it)."""
+        nc = codec.v2_num_chunks(numel_per_source)
+        if nc <= self.nc_max:
+            return
+        symm_mem = _symm_mod()
+        if self.buf is not None:
+            torch.cuda.synchronize(self.device)
+            dist.barrier(group=self.group)  # nobody may still be pushing into the old buffer
+        nc_max = max(nc, 1024)
+        nbytes = int(self._lib._lib.zc_symm_buffer_bytes(self.world, nc_max))
+        buf = symm_mem.empty(nbytes, dtype=torch.uint8, device=self.device)
+        buf[: CTRL_WORDS * 4 + 0].zero_()
+        # flags must start below any sequence number; zero the control block and the flag area
+        flag_bytes = (2 * self.world * ((nc_max + 63) // 64) * 4 + 127) // 128 * 128
+        buf[: CTRL_WORDS * 4 + flag_bytes].zero_()
+        torch.cuda.synchronize(self.device)
+        hdl = symm_mem.rendezvous(buf, self.group)
+        dist.barrier(group=self.group)
+        self.buf, self.hdl, self.nc_max, self.seq = buf, hdl, nc_max, 0
+        self.peers_dev = hdl.buffer_ptrs_dev
+        self.local_ptr = hdl.buffer_ptrs[self.rank]
+
+    def _next_seq(self) -> int:
+        self.seq += 1
+        return self.seq
+
+    # -- status ----------------------------------------------------------------------------------
+    def _ctrl(self) -> torch.Tensor:
+        return self.buf[: CTRL_WORDS * 4].view(torch.int32)
+
+    def check_status(self) -> None:
+        """Synchronises the device and raises ``SymmTimeout`` when a bounded wait expired."""
+        if self.buf is None:
+            return
+        c = self._ctrl()[CW_STATUS:CW_STATUS + 3].tolist()
+        if c[0] != 0:
+            self._ctrl()[CW_STATUS:CW_STATUS + 3].zero_()
+            raise SymmTimeout(c[0], c[1], c[2])
+
+    def wire_bytes(self) -> int:
+        """Bytes this rank has pushed over NVLink on this channel so far (synchronises)."""
+        if self.buf is None:
+            return 0
+        return int(self._ctrl()[CW_WIRE_LO:CW_WIRE_LO + 2].view(torch.int64).item())
+
+    # -- collectives -----------------------------------------------------------------------------
+    def all_gather(self, output_tensor: torch.Tensor, x: torch.Tensor, mode: str = "zip", async_op: bool = False):
+        if mode != "zip":
+            raise NotImplementedError("the fused all-gather carries the lossless v2 codec only")
+        n = x.numel()
+        self.reserve(n)
+        seq = self._next_seq()
+        _lib.check(self._lib.zc_symm_all_gather(
+            x.data_ptr(), output_tensor.data_ptr(), self.peers_dev, self.local_ptr, n, self.rank, self.world,
+            self.nc_max, seq, self.push_ctas, self.dec_ctas, self.timeout_s, _lib.stream_ptr(self.device)),
+            "zc_symm_all_gather")
+        if not async_op:
+            return None
+        return AggregatedWork([], status_fn=None)
+
+    def reduce_scatter(self, output_tensor: torch.Tensor, x: torch.Tensor, scale: float, residual, async_op=False):
+        shard = x.numel() // self.world
+        if output_tensor.numel() != shard or output_tensor.dtype not in (torch.float32, torch.bfloat16):
+            raise ValueError("output must hold numel/world fp32 or bf16 elements")
+        if residual is not None and residual.dtype != torch.bfloat16:
+            raise TypeError("the fused reduce-scatter keeps its residual in bf16")
+        self.reserve(shard)
+        seq = self._next_seq()
+        _lib.check(self._lib.zc_symm_reduce_scatter(
+            x.data_ptr(), output_tensor.data_ptr(), _lib.ptr(residual), self.peers_dev, self.local_ptr, shard,
+            self.rank, self.world, self.nc_max, seq, int(x.dtype == torch.float32),
+            int(output_tensor.dtype == torch.float32), float(scale), self.push_ctas, self.dec_ctas,
+            self.timeout_s, _lib.stream_ptr(self.device)), "zc_symm_reduce_scatter")
+        if not async_op:
+            return None
+        return AggregatedWork([], status_fn=None)
+
+
+def channel_for(group, device: torch.device, kind: str) -> Channel:
+    key = (group.group_name if hasattr(group, "group_name") else str(group), str(device), kind)
+    ch = _CHANNELS.get(key)
+    if ch is None:
+        ch = _CHANNELS[key] = Channel(group, device, kind)
+    return ch
+
+
+def all_channels():
+    return list(_CHANNELS.values())

@@ -1,0 +1,155 @@
+"""Multi-GPU tests (2 ranks, NCCL, NVLS off): fused symmetric-memory collectives against the
+uncompressed NCCL collectives, the NCCL-transport hooks, bounded-wait failure reporting, and a
+short FSDP run.  Skipped with fewer than 2 GPUs."""
+import os
+
+import pytest
+import torch
+
+from mp_util import run_ranks
+
+pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
+
+
+def _bits(t):
+    return t.view(torch.int16)
+
+
+def _ag_case(rank, world, transport):
+    import torch.distributed as dist
+    from fsdp_comm_opt_b200.parallel.hooks import ZipCCLAllGather
+
+    dev = torch.device("cuda", rank)
+    hook = ZipCCLAllGather(transport=transport)
+    sizes = [1 << 20, 777, 65536 * 3 + 5, 1 << 22, 4096, 1 << 20, (1 << 20) + 8]
+    for it, n in enumerate(sizes):
+        g = torch.Generator().manual_seed(100 * it + rank)
+        x = (torch.randn(n, generator=g) * 0.02).to(torch.bfloat16).to(dev)
+        ref = torch.zeros(world * n, dtype=torch.bfloat16, device=dev)
+        dist.all_gather_into_tensor(ref, x)
+        out = torch.zeros(world * n, dtype=torch.bfloat16, device=dev)
+        if it % 2 == 0:                      # FSDP2 style: input is a view of the output
+            inp = out.narrow(0, n * rank, n)
+            inp.copy_(x)
+        else:
+            inp = x
+        w = hook(out, inp, dist.group.WORLD, async_op=(it % 3 == 0))
+        if w is not None:
+            w.wait()
+        torch.cuda.synchronize()
+        assert torch.equal(_bits(out), _bits(ref)), (transport, it, n)
+    if transport == "symm":
+        from fsdp_comm_opt_b200.parallel import symm_impl
+
+        for ch in symm_impl.all_channels():
+            ch.check_status()
+            pushed = ch.wire_bytes()
+            raw = 2 * sum(sizes) * (world - 1)
+            assert 0.6 * raw < pushed < 0.8 * raw, (pushed, raw)   # ~1.4 of 2 bytes per element
+
+
+@pytest.mark.parametrize("transport", ["symm", "lib"])
+def test_zip_all_gather_nccl_ranks(transport):
+    run_ranks(_ag_case, 2, (transport,), backend="nccl")
+
+
+def _rs_case(rank, world, transport):
+    import torch.distributed as dist
+    from fsdp_comm_opt_b200.parallel.hooks import ZipCCLReduceScatter
+
+    dev = torch.device("cuda", rank)
+    hook = ZipCCLReduceScatter(transport=transport)
+    for it, shard in enumerate([1 << 20, 5000, 65536 * 2 + 3, 1 << 21, 1 << 20]):
+        g = torch.Generator().manual_seed(7 * it + rank)
+        x = (torch.randn(world * shard, generator=g) * 1e-3).to(torch.bfloat16).float().to(dev)
+        ref = torch.zeros(shard, device=dev)
+        dist.reduce_scatter_tensor(ref, x.clone(), op=dist.ReduceOp.AVG)
+        out = torch.zeros(shard, device=dev)
+        hook(out, x, dist.group.WORLD, dist.ReduceOp.AVG)
+        torch.cuda.synchronize()
+        assert torch.allclose(out, ref, rtol=1e-6, atol=1e-9), (transport, it, (out - ref).abs().max().item())
+        # bf16 input and output
+        xb = x.to(torch.bfloat16)
+        outb = torch.zeros(shard, dtype=torch.bfloat16, device=dev)
+        hook(outb, xb, dist.group.WORLD, dist.ReduceOp.SUM)
+        refb = torch.zeros(shard, device=dev)
+        dist.reduce_scatter_tensor(refb, x.clone(), op=dist.ReduceOp.SUM)
+        torch.cuda.synchronize()
+        assert torch.allclose(outb.float(), refb, rtol=1e-2, atol=1e-6)
+    # true fp32 gradients: error feedback keeps the running sum closer than plain rounding
+    shard = 1 << 18
+    ef, no = ZipCCLReduceScatter(transport=transport), ZipCCLReduceScatter(error_feedback=False, transport=transport)
+    const = (torch.randn(world * shard, generator=torch.Generator().manual_seed(rank)) * 1e-3).to(dev)
+    acc_ref, acc_ef, acc_no = (torch.zeros(shard, device=dev) for _ in range(3))
+    for _ in range(24):
+        r, a, b = (torch.zeros(shard, device=dev) for _ in range(3))
+        dist.reduce_scatter_tensor(r, const.clone(), op=dist.ReduceOp.SUM)
+        ef(a, const.clone(), dist.group.WORLD, dist.ReduceOp.SUM)
+        no(b, const.clone(), dist.group.WORLD, dist.ReduceOp.SUM)
+        acc_ref += r; acc_ef += a; acc_no += b
+    torch.cuda.synchronize()
+    e1, e2 = (acc_ef - acc_ref).abs().max().item(), (acc_no - acc_ref).abs().max().item()
+    assert e1 < e2 / 3, (e1, e2)
+    if transport == "symm":
+        from fsdp_comm_opt_b200.parallel import symm_impl
+
+        for ch in symm_impl.all_channels():
+            ch.check_status()
+
+
+@pytest.mark.parametrize("transport", ["symm", "lib"])
+def test_compressed_reduce_scatter_nccl_ranks(transport):
+    run_ranks(_rs_case, 2, (transport,), backend="nccl")
+
+
+def _timeout_case(rank, world):
+    """Rank 1 never joins one collective; rank 0's bounded wait must expire into a status word,
+    surface as SymmTimeout on the host, and leave the context usable."""
+    import torch.distributed as dist
+    from fsdp_comm_opt_b200.parallel import symm_impl
+
+    dev = torch.device("cuda", rank)
+    assert symm_impl.available(dist.group.WORLD)
+    ch = symm_impl.channel_for(dist.group.WORLD, dev, "timeout-test")
+    ch.timeout_s = 1.0
+    n = 1 << 16
+    ch.reserve(n)
+    x = torch.ones(n, dtype=torch.bfloat16, device=dev)
+    out = torch.zeros(world * n, dtype=torch.bfloat16, device=dev)
+    if rank == 0:
+        ch.all_gather(out, x)
+        with pytest.raises(symm_impl.SymmTimeout) as ei:
+            ch.check_status()
+        assert ei.value.code == 2 and ei.value.peer == 1
+        ch.check_status()                       # cleared
+        y = torch.arange(10, device=dev).sum()  # the context still works
+        assert int(y) == 45
+    torch.cuda.synchronize()
+    dist.barrier()
+
+
+def test_bounded_wait_reports_missing_peer():
+    run_ranks(_timeout_case, 2, backend="nccl")
+
+
+def _train(rank, world, extra, loss_log):
+    import train
+
+    train.main(["--synthetic", "--model-shape", "small", "--device", "cuda", "-b", "1", "-s", "512", "--lr", "1e-4",
+                "--log-freq", "100", "--num-samples", "64", "--steps", "4", "--loss-log", loss_log] + extra)
+
+
+def _losses(path):
+    return [float(l.split()[1]) for l in open(path).read().split("\n") if l]
+
+
+def test_fsdp_two_gpus_symm_vs_lib_vs_uncompressed(tmp_path):
+    logs = {k: str(tmp_path / f"{k}.log") for k in ("none", "lib", "symm")}
+    run_ranks(_train, 2, init_pg=False, backend="nccl", args=([], logs["none"]))
+    run_ranks(_train, 2, init_pg=False, backend="nccl", args=(["-q", "--zip-ccl", "--transport", "lib"], logs["lib"]))
+    run_ranks(_train, 2, init_pg=False, backend="nccl",
+              args=(["-q", "--zip-ccl", "--compress-rs", "--transport", "symm"], logs["symm"]))
+    a, b, c = (_losses(logs[k]) for k in ("none", "lib", "symm"))
+    assert len(a) == len(b) == len(c) == 4
+    assert a == b, "lossless all-gather: identical loss curve"
+    assert all(abs(x - y) / x < 0.01 for x, y in zip(a, c)), (a, c)
