@@ -22,6 +22,12 @@ def _ag_case(rank, world, transport):
     dev = torch.device("cuda", rank)
     hook = ZipCCLAllGather(transport=transport)
     sizes = [1 << 20, 777, 65536 * 3 + 5, 1 << 22, 4096, 1 << 20, (1 << 20) + 8]
+    if transport == "symm":
+        from fsdp_comm_opt_b200.parallel import symm_impl
+
+        # size the channel once: growing it later would start a new buffer and a new byte counter
+        assert symm_impl.available(dist.group.WORLD)
+        symm_impl.channel_for(dist.group.WORLD, dev, "ag").reserve(max(sizes))
     for it, n in enumerate(sizes):
         g = torch.Generator().manual_seed(100 * it + rank)
         x = (torch.randn(n, generator=g) * 0.02).to(torch.bfloat16).to(dev)
