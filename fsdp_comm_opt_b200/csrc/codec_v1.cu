@@ -428,3 +428,61 @@ int zc_v1_base_from_std(const void* x, long long n, int* bases, cudaStream_t st)
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------------------------
+// Allocation-free variant (see zc_noalloc.h): the outlier staging area is a static device array.
+// ---------------------------------------------------------------------------------------------
+#include <cstdio>
+#include <mutex>
+
+#include "zc_noalloc.h"
+
+static __device__ __align__(256) unsigned char g_noalloc_scratch[ZC_NOALLOC_MAX_ELEMS];
+
+namespace {
+std::mutex g_noalloc_mutex;
+unsigned char* g_noalloc_ptr[64] = {nullptr};  // device address of the array, per device
+
+// In host code `g_noalloc_scratch` is only a handle for the runtime, not a device address; the
+// address is looked up once per device, with that device current.
+int noalloc_scratch(unsigned char** out) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return ZC_ERR_SYMBOL;
+  std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+  if (!g_noalloc_ptr[dev]) {
+    unsigned char* p = nullptr;
+    const cudaError_t e = cudaGetSymbolAddress((void**)&p, g_noalloc_scratch);
+    if (e != cudaSuccess || p == nullptr) {
+      fprintf(stderr, "[zc_noalloc] cudaGetSymbolAddress failed on device %d: %s\n", dev, cudaGetErrorString(e));
+      return ZC_ERR_SYMBOL;
+    }
+    g_noalloc_ptr[dev] = p;
+  }
+  *out = g_noalloc_ptr[dev];
+  return 0;
+}
+}  // namespace
+
+extern "C" int zc_v1_encode_split_noalloc(const void* in, long long total_n, const int* n_8, const int* orig_n,
+                                          int n_works, const int* bases, void* det, void* esc_final, int* counts,
+                                          long long total_blocks, cudaStream_t st) {
+  using namespace zc;
+  if (total_blocks <= 0) return 0;
+  if (n_works <= 0) return ERR_BAD_ARG;
+  if (total_blocks * V1_BLOCK_ELEMS > ZC_NOALLOC_MAX_ELEMS) {
+    fprintf(stderr,
+            "[zc_noalloc] request of %lld padded elements exceeds the built-in scratch of %lld; "
+            "use zc_v1_encode_split with your own scratch buffer\n",
+            total_blocks * V1_BLOCK_ELEMS, (long long)ZC_NOALLOC_MAX_ELEMS);
+    return ZC_ERR_TOO_LARGE;
+  }
+  unsigned char* scratch = nullptr;
+  const int rc = noalloc_scratch(&scratch);
+  if (rc != 0) return rc;
+  v1_encode_kernel<<<(unsigned)total_blocks, 128, 0, st>>>((const uint16_t*)in, total_n, n_8, orig_n, n_works,
+                                                           bases, LAYOUT_SPLIT, (uint8_t*)det, scratch);
+  v1_scan_kernel<<<n_works, 1024, 0, st>>>(n_8, n_works, LAYOUT_SPLIT, (uint8_t*)det, counts, nullptr);
+  v1_compact_kernel<<<(unsigned)total_blocks, 128, 0, st>>>(n_8, n_works, LAYOUT_SPLIT, counts, nullptr,
+                                                            (uint8_t*)det, scratch, (uint8_t*)esc_final);
+  return launch_status();
+}
