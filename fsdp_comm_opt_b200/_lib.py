@@ -63,7 +63,7 @@ def cuda_lib_path() -> Path:
 # kernels launched by one call of each C launcher (for the launch counter)
 _KERNELS_PER_CALL = {
     "zc_v1_encode_split": 3, "zc_v1_encode_fused": 3, "zc_v1_base_from_std": 2, "zc_quant_int8": 2,
-    "zc_attn_bwd": 3, "zc_attn_status_read_and_clear": 0, "zc_gemm_status_read_and_clear": 0,
+    "zc_attn_bwd": 3, "zc_attn_bwd_ws": 3, "zc_attn_bwd_ws_status_read_and_clear": 0, "zc_attn_status_read_and_clear": 0, "zc_attn_ws_status_read_and_clear": 0, "zc_gemm_status_read_and_clear": 0,
 }
 _LAUNCHES = 0
 

@@ -1,0 +1,423 @@
+// Warp-specialised causal GQA attention backward for sm_100a (the default backward path).
+//
+// One CTA (320 threads) per (128-key block, kv head, batch); it loops over the query heads of the
+// group and over the query blocks at or below the diagonal, with dK and dV accumulating in TMEM.
+//   warp 0      TMA producer: K, V once; then Q_i and dO_i per iteration (4-D tensor maps,
+//               SWIZZLE_128B, zero fill past S).  The next iteration's loads start as soon as the
+//               MMAs that read the buffers have completed, and overlap the dQ reduction below.
+//   warp 1      MMA issuer: S = Q K^T and dP = dO V^T, then dV += P^T dO, dK += dS^T Q and
+//               dQ_i = dS K (P / dS are read through MN-major descriptors: no transposes)
+//   warps 2-9   256 compute threads: two threads share a query row and take 64 columns each;
+//               P = exp2(S*c - lse), dS = P (dP - delta) scale, written to smem as bf16; then the
+//               dQ_i tile is read from TMEM and reduced into the fp32 accumulator with red.add
+// TMEM (512 columns): dK | dV | R0 (S, later dQ_i) | R1 (dP).  Shared memory: K V Q dO P dS, 32 KB
+// each.  Every wait is bounded; a timed-out role raises a CTA-wide abort flag.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <math_constants.h>
+
+#include <cstdio>
+
+#include "launch_util.h"
+#include "umma.cuh"
+
+namespace zc {
+namespace bws {
+using namespace umma;
+
+constexpr float LOG2E = 1.4426950408889634f;
+
+__device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1, int c2,
+                                            int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+__device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
+__device__ __forceinline__ uint64_t desc_k(uint32_t base, int k) {
+  return smem_desc(base + (k >> 2) * 16384 + (k & 3) * 32, 16, 1024);
+}
+__device__ __forceinline__ uint64_t desc_mn(uint32_t base, int k) { return smem_desc(base + k * 2048, 16384, 1024); }
+
+__device__ __forceinline__ void store_chunk32(uint8_t* tile, int row, int col0, const float (&v)[32]) {
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    const int col = col0 + q * 8;
+    __nv_bfloat162 a = __floats2bfloat162_rn(v[q * 8 + 0], v[q * 8 + 1]);
+    __nv_bfloat162 b = __floats2bfloat162_rn(v[q * 8 + 2], v[q * 8 + 3]);
+    __nv_bfloat162 c = __floats2bfloat162_rn(v[q * 8 + 4], v[q * 8 + 5]);
+    __nv_bfloat162 d = __floats2bfloat162_rn(v[q * 8 + 6], v[q * 8 + 7]);
+    uint4 u;
+    u.x = *reinterpret_cast<uint32_t*>(&a);
+    u.y = *reinterpret_cast<uint32_t*>(&b);
+    u.z = *reinterpret_cast<uint32_t*>(&c);
+    u.w = *reinterpret_cast<uint32_t*>(&d);
+    *reinterpret_cast<uint4*>(tile + (col >> 6) * 16384 + sw128_off(row, (col >> 3) & 7)) = u;
+  }
+}
+
+struct BwdParams {
+  const float *lse, *delta;
+  float* dq_acc;
+  __nv_bfloat16 *dk, *dv;
+  int B, S, Hq, Hkv;
+  int64_t dks0, dks1, dks2, dvs0, dvs1, dvs2;
+  float scale;
+  int* status;
+};
+
+template <int D>
+__global__ void __launch_bounds__(320, 1) attn_bwd_ws_kernel(const __grid_constant__ CUtensorMap mapQ,
+                                                             const __grid_constant__ CUtensorMap mapK,
+                                                             const __grid_constant__ CUtensorMap mapV,
+                                                             const __grid_constant__ CUtensorMap mapdO,
+                                                             const BwdParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  constexpr int TILE = 128 * D * 2;
+  constexpr int SLABS = D / 64;
+  uint8_t* sK = smem;
+  uint8_t* sV = smem + 1 * 32768;
+  uint8_t* sQ = smem + 2 * 32768;
+  uint8_t* sdO = smem + 3 * 32768;
+  uint8_t* sP = smem + 4 * 32768;
+  uint8_t* sdS = smem + 5 * 32768;
+  __shared__ uint64_t kv_full, qdo_full, qdo_empty, sdp_full, pds_full, dq_full, dq_empty;
+  __shared__ uint32_t tmem_base;
+  __shared__ volatile int s_abort;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int nkb = gridDim.x;
+  const int jb = blockIdx.x;
+  const int hk = blockIdx.y, b = blockIdx.z;
+  const int group = p.Hq / p.Hkv;
+  const int k0 = jb * 128;
+  const int iters = group * (nkb - jb);
+  if (tid == 0) {
+    mbar_init(&kv_full, 1);
+    mbar_init(&qdo_full, 1);
+    mbar_init(&qdo_empty, 1);
+    mbar_init(&sdp_full, 1);
+    mbar_init(&pds_full, 1);
+    mbar_init(&dq_full, 1);
+    mbar_init(&dq_empty, 1);
+    mbar_fence_init();
+    s_abort = 0;
+  }
+  if (warp == 1) {
+    tmem_alloc(&tmem_base, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tm_dk = tmem_base, tm_dv = tmem_base + 128, tm_r0 = tmem_base + 256, tm_r1 = tmem_base + 384;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_expect_tx(&kv_full, 2 * TILE);
+#pragma unroll
+      for (int sl = 0; sl < SLABS; ++sl) {
+        tma_load_4d(sK + sl * 16384, &mapK, &kv_full, sl * 64, hk, k0, b);
+        tma_load_4d(sV + sl * 16384, &mapV, &kv_full, sl * 64, hk, k0, b);
+      }
+      for (int it = 0; it < iters; ++it) {
+        const int h = hk * group + it / (nkb - jb);
+        const int q0 = (jb + it % (nkb - jb)) * 128;
+        if (!mbar_wait(&qdo_empty, (it & 1) ^ 1)) { s_abort = 1; break; }
+        mbar_expect_tx(&qdo_full, 2 * TILE);
+#pragma unroll
+        for (int sl = 0; sl < SLABS; ++sl) {
+          tma_load_4d(sQ + sl * 16384, &mapQ, &qdo_full, sl * 64, h, q0, b);
+          tma_load_4d(sdO + sl * 16384, &mapdO, &qdo_full, sl * 64, h, q0, b);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t id_s = idesc_bf16(128, 128, MAJOR_K, MAJOR_K);
+      const uint32_t id_kv = idesc_bf16(128, D, MAJOR_MN, MAJOR_MN);
+      const uint32_t id_dq = idesc_bf16(128, D, MAJOR_K, MAJOR_MN);
+      const uint32_t aK = smem_u32(sK), aV = smem_u32(sV), aQ = smem_u32(sQ), adO = smem_u32(sdO), aP = smem_u32(sP),
+                     adS = smem_u32(sdS);
+      bool ok = mbar_wait(&kv_full, 0);
+      for (int it = 0; it < iters && ok; ++it) {
+        if (!(ok = mbar_wait(&qdo_full, it & 1))) break;
+        if (!(ok = mbar_wait(&dq_empty, (it & 1) ^ 1))) break;
+        tc_fence_after_sync();
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) mma_bf16(tm_r0, desc_k(aQ, k), desc_k(aK, k), id_s, k != 0);
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) mma_bf16(tm_r1, desc_k(adO, k), desc_k(aV, k), id_s, k != 0);
+        mma_commit(&sdp_full);
+        if (!(ok = mbar_wait(&pds_full, it & 1))) break;
+        tc_fence_after_sync();
+#pragma unroll
+        for (int k = 0; k < 8; ++k) mma_bf16(tm_dv, desc_mn(aP, k), desc_mn(adO, k), id_kv, (it | k) != 0);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) mma_bf16(tm_dk, desc_mn(adS, k), desc_mn(aQ, k), id_kv, (it | k) != 0);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) mma_bf16(tm_r0, desc_k(adS, k), desc_mn(aK, k), id_dq, k != 0);
+        mma_commit(&dq_full);
+        mma_commit(&qdo_empty);
+      }
+      if (!ok) s_abort = 1;
+    }
+  } else {
+    const int cw = warp - 2;
+    const int quarter = warp & 3;
+    const int half = cw >> 2;
+    const int r = quarter * 32 + lane;
+    const uint32_t lane_base = (uint32_t)(quarter * 32);
+    const float sl2 = p.scale * LOG2E;
+    for (int it = 0; it < iters; ++it) {
+      const int h = hk * group + it / (nkb - jb);
+      const int ib = jb + it % (nkb - jb);
+      const int q0 = ib * 128;
+      const int row = q0 + r;
+      float lse2 = 0.f, dl = 0.f;
+      if (row < p.S) {
+        lse2 = __ldg(p.lse + ((int64_t)b * p.Hq + h) * p.S + row) * LOG2E;
+        dl = __ldg(p.delta + ((int64_t)b * p.Hq + h) * p.S + row);
+      }
+      if (!mbar_wait(&sdp_full, it & 1)) s_abort = 1;
+      tc_fence_after_sync();
+      const bool diag = (ib == jb) || (q0 + 128 > p.S) || (k0 + 128 > p.S);
+#pragma unroll 1
+      for (int c = half * 64; c < half * 64 + 64; c += 32) {
+        uint32_t rs[32], rp[32];
+        tmem_ld32(tmem_addr(tm_r0, lane_base, c), rs);
+        tmem_ld32(tmem_addr(tm_r1, lane_base, c), rp);
+        tmem_ld_wait();
+        float pv[32], ds[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          float e = exp2f(__uint_as_float(rs[i]) * sl2 - lse2);
+          if (diag && (k0 + c + i > row || k0 + c + i >= p.S || row >= p.S)) e = 0.f;
+          pv[i] = e;
+          ds[i] = e * (__uint_as_float(rp[i]) - dl) * p.scale;
+        }
+        store_chunk32(sP, r, c, pv);
+        store_chunk32(sdS, r, c, ds);
+      }
+      fence_proxy_async_smem();
+      tc_fence_before_sync();
+      named_bar_sync(1, 256);
+      if (s_abort) break;
+      if (tid == 64) mbar_arrive(&pds_full);
+      // ---- dQ_i partial: this thread reduces its row's columns [half*D/2, half*D/2 + D/2) ---------
+      if (!mbar_wait(&dq_full, it & 1)) s_abort = 1;
+      tc_fence_after_sync();
+      float* dqrow = p.dq_acc + ((int64_t)(b * p.S + row) * p.Hq + h) * D;
+#pragma unroll 1
+      for (int c = half * (D / 2); c < half * (D / 2) + D / 2; c += 32) {
+        uint32_t rr[32];
+        tmem_ld32(tmem_addr(tm_r0, lane_base, c), rr);
+        tmem_ld_wait();
+        if (row < p.S) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 4)
+            atomicAdd(reinterpret_cast<float4*>(dqrow + c + i),
+                      make_float4(__uint_as_float(rr[i]), __uint_as_float(rr[i + 1]), __uint_as_float(rr[i + 2]),
+                                  __uint_as_float(rr[i + 3])));
+        }
+      }
+      tc_fence_before_sync();
+      named_bar_sync(1, 256);
+      if (s_abort) break;
+      if (tid == 64) mbar_arrive(&dq_empty);
+    }
+    if (!s_abort) {
+      // all MMAs into dK / dV have completed (dq_full of the last iteration covers them)
+      const int krow = k0 + r;
+#pragma unroll 1
+      for (int which = 0; which < 2; ++which) {
+        const uint32_t tmx = which ? tm_dv : tm_dk;
+        __nv_bfloat16* dst = which ? p.dv + b * p.dvs0 + (int64_t)krow * p.dvs1 + hk * p.dvs2
+                                   : p.dk + b * p.dks0 + (int64_t)krow * p.dks1 + hk * p.dks2;
+#pragma unroll 1
+        for (int c = half * (D / 2); c < half * (D / 2) + D / 2; c += 32) {
+          uint32_t rr[32];
+          tmem_ld32(tmem_addr(tmx, lane_base, c), rr);
+          tmem_ld_wait();
+          if (krow < p.S) {
+#pragma unroll
+            for (int i = 0; i < 32; i += 8) {
+              __nv_bfloat162 a0 = __floats2bfloat162_rn(__uint_as_float(rr[i]), __uint_as_float(rr[i + 1]));
+              __nv_bfloat162 a1 = __floats2bfloat162_rn(__uint_as_float(rr[i + 2]), __uint_as_float(rr[i + 3]));
+              __nv_bfloat162 a2 = __floats2bfloat162_rn(__uint_as_float(rr[i + 4]), __uint_as_float(rr[i + 5]));
+              __nv_bfloat162 a3 = __floats2bfloat162_rn(__uint_as_float(rr[i + 6]), __uint_as_float(rr[i + 7]));
+              uint4 u;
+              u.x = *reinterpret_cast<uint32_t*>(&a0);
+              u.y = *reinterpret_cast<uint32_t*>(&a1);
+              u.z = *reinterpret_cast<uint32_t*>(&a2);
+              u.w = *reinterpret_cast<uint32_t*>(&a3);
+              *reinterpret_cast<uint4*>(dst + c + i) = u;
+            }
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (tid == 0 && s_abort) atomicExch(p.status, 5);
+  if (warp == 1) tmem_dealloc(tmem_base, 512);
+}
+
+typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                             const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                             CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeFn encode_fn() {
+  static EncodeFn fn = nullptr;
+  if (!fn) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeFn>(ptr);
+  }
+  return fn;
+}
+static bool make_map4(CUtensorMap* m, const void* base, int D, int H, int S, int B, int64_t s_b, int64_t s_s,
+                      int64_t s_h) {
+  EncodeFn fn = encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)H, (cuuint64_t)S, (cuuint64_t)B};
+  cuuint64_t strides[3] = {(cuuint64_t)s_h * 2, (cuuint64_t)s_s * 2, (cuuint64_t)s_b * 2};
+  cuuint32_t box[4] = {64, 1, 128, 1};
+  cuuint32_t el[4] = {1, 1, 1, 1};
+  const CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, el,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    fprintf(stderr, "[zc_attn_bwd] cuTensorMapEncodeTiled failed (%d): base=%p D=%d H=%d S=%d B=%d\n", (int)r, base, D,
+            H, S, B);
+  return r == CUDA_SUCCESS;
+}
+
+struct Scratch {
+  int* status = nullptr;
+  float* dq_acc = nullptr;
+  size_t dq_bytes = 0;
+};
+static Scratch g_scratch[64];
+
+__global__ void __launch_bounds__(256) delta_kernel(const __nv_bfloat16* __restrict__ o,
+                                                    const __nv_bfloat16* __restrict__ dout, float* __restrict__ delta,
+                                                    int B, int S, int Hq, int D) {
+  const int64_t wid = ((int64_t)blockIdx.x * 256 + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  const int64_t total = (int64_t)B * S * Hq;
+  if (wid >= total) return;
+  const __nv_bfloat16* po = o + wid * D;
+  const __nv_bfloat16* pd = dout + wid * D;
+  float acc = 0.f;
+  for (int i = lane * 2; i < D; i += 64) {
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(po + i));
+    const float2 g = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(pd + i));
+    acc += a.x * g.x + a.y * g.y;
+  }
+#pragma unroll
+  for (int s = 16; s > 0; s >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, s);
+  if (lane == 0) {
+    const int64_t bs = wid / Hq;
+    const int hh = (int)(wid % Hq);
+    delta[((bs / S) * Hq + hh) * S + bs % S] = acc;
+  }
+}
+
+__global__ void __launch_bounds__(256) dq_convert_kernel(const float* __restrict__ acc, __nv_bfloat16* __restrict__ dq,
+                                                         int64_t rows, int Hq, int D, int64_t s_bs, int64_t s_h) {
+  const int vpr = D / 4;
+  const int64_t total = rows * Hq * vpr;
+  for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < total; i += (int64_t)gridDim.x * 256) {
+    const int v = (int)(i % vpr);
+    const int h = (int)((i / vpr) % Hq);
+    const int64_t r = i / ((int64_t)vpr * Hq);
+    const float4 f = *reinterpret_cast<const float4*>(acc + (r * Hq + h) * D + v * 4);
+    __nv_bfloat162 a = __floats2bfloat162_rn(f.x, f.y), c = __floats2bfloat162_rn(f.z, f.w);
+    uint2 u;
+    u.x = *reinterpret_cast<uint32_t*>(&a);
+    u.y = *reinterpret_cast<uint32_t*>(&c);
+    *reinterpret_cast<uint2*>(dq + r * s_bs + h * s_h + v * 4) = u;
+  }
+}
+
+}  // namespace bws
+}  // namespace zc
+
+extern "C" {
+
+int zc_attn_bwd_ws_status_read_and_clear() {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  zc::bws::Scratch& sc = zc::bws::g_scratch[dev];
+  if (!sc.status) return 0;
+  int v = 0;
+  cudaMemcpy(&v, sc.status, sizeof(int), cudaMemcpyDeviceToHost);
+  if (v) cudaMemset(sc.status, 0, sizeof(int));
+  return v;
+}
+
+// Same argument list as zc_attn_bwd.
+int zc_attn_bwd_ws(const void* q, const void* k, const void* v, const void* o, const void* dout, const float* lse,
+                   float* delta, void* dq, void* dk, void* dv, int B, int S, int Hq, int Hkv, int D, int64_t qs0,
+                   int64_t qs1, int64_t qs2, int64_t ks0, int64_t ks1, int64_t ks2, int64_t vs0, int64_t vs1,
+                   int64_t vs2, int64_t dqs0, int64_t dqs1, int64_t dqs2, int64_t dks0, int64_t dks1, int64_t dks2,
+                   int64_t dvs0, int64_t dvs1, int64_t dvs2, float scale, cudaStream_t st) {
+  using namespace zc;
+  using namespace zc::bws;
+  if ((D != 64 && D != 128) || Hq % Hkv) return ERR_UNSUPPORTED;
+  if ((qs1 | qs2 | ks1 | ks2 | vs1 | vs2 | qs0 | ks0 | vs0 | dqs1 | dqs2 | dks1 | dks2 | dvs1 | dvs2 | dqs0 | dks0 | dvs0) % 8)
+    return ERR_UNSUPPORTED;
+  if (dqs0 != (int64_t)S * dqs1) return ERR_UNSUPPORTED;
+  if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) |
+       reinterpret_cast<uintptr_t>(dout)) & 15)
+    return ERR_UNSUPPORTED;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  cudaSetDevice(dev);
+  Scratch& sc = g_scratch[dev];
+  if (!sc.status) {
+    if (cudaMalloc(&sc.status, sizeof(int)) != cudaSuccess) return ERR_BAD_ARG;
+    cudaMemset(sc.status, 0, sizeof(int));
+  }
+  const size_t need = (size_t)B * S * Hq * D * sizeof(float);
+  if (sc.dq_bytes < need) {
+    if (sc.dq_acc) cudaFreeAsync(sc.dq_acc, st);
+    if (cudaMallocAsync(&sc.dq_acc, need, st) != cudaSuccess) { sc.dq_acc = nullptr; sc.dq_bytes = 0; return (int)cudaGetLastError(); }
+    sc.dq_bytes = need;
+  }
+  cudaMemsetAsync(sc.dq_acc, 0, need, st);
+  CUtensorMap mq, mk, mv, mdo;
+  if (!make_map4(&mq, q, D, Hq, S, B, qs0, qs1, qs2) || !make_map4(&mk, k, D, Hkv, S, B, ks0, ks1, ks2) ||
+      !make_map4(&mv, v, D, Hkv, S, B, vs0, vs1, vs2) ||
+      !make_map4(&mdo, dout, D, Hq, S, B, (int64_t)S * Hq * D, (int64_t)Hq * D, D))
+    return ERR_BAD_ARG;
+  BwdParams p;
+  p.lse = lse; p.delta = delta; p.dq_acc = sc.dq_acc; p.dk = (__nv_bfloat16*)dk; p.dv = (__nv_bfloat16*)dv;
+  p.B = B; p.S = S; p.Hq = Hq; p.Hkv = Hkv;
+  p.dks0 = dks0; p.dks1 = dks1; p.dks2 = dks2; p.dvs0 = dvs0; p.dvs1 = dvs1; p.dvs2 = dvs2;
+  p.scale = scale; p.status = sc.status;
+  const int64_t rows = (int64_t)B * S * Hq;
+  delta_kernel<<<(unsigned)((rows * 32 + 255) / 256), 256, 0, st>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)dout,
+                                                                   delta, B, S, Hq, D);
+  const int smem = 6 * 32768 + 1024;
+  static bool attr[2] = {false, false};
+  const dim3 grid((S + 127) / 128, Hkv, B);
+  if (D == 128) {
+    if (!attr[0]) { cudaFuncSetAttribute(attn_bwd_ws_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); attr[0] = true; }
+    attn_bwd_ws_kernel<128><<<grid, 320, smem, st>>>(mq, mk, mv, mdo, p);
+  } else {
+    if (!attr[1]) { cudaFuncSetAttribute(attn_bwd_ws_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); attr[1] = true; }
+    attn_bwd_ws_kernel<64><<<grid, 320, smem, st>>>(mq, mk, mv, mdo, p);
+  }
+  const int cgrid = (int)std::min<int64_t>((rows * (D / 4) + 255) / 256, (int64_t)sm_count() * 16);
+  dq_convert_kernel<<<cgrid, 256, 0, st>>>(sc.dq_acc, (__nv_bfloat16*)dq, (int64_t)B * S, Hq, D, dqs1, dqs2);
+  return launch_status();
+}
+
+}  // extern "C"

@@ -407,20 +407,77 @@ __global__ void __launch_bounds__(256) adamw_kernel(TP* __restrict__ p, TG* __re
   }
 }
 
+// eight elements per thread, 16-byte accesses (pointers 16-byte aligned, n % 8 == 0)
+template <typename T> __device__ __forceinline__ void load8(const T* p, float (&f)[8]);
+template <> __device__ __forceinline__ void load8<__nv_bfloat16>(const __nv_bfloat16* p, float (&f)[8]) {
+  unpack8(ld8(p), f);
+}
+template <> __device__ __forceinline__ void load8<float>(const float* p, float (&f)[8]) {
+  const float4 a = reinterpret_cast<const float4*>(p)[0], b = reinterpret_cast<const float4*>(p)[1];
+  f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+}
+template <typename T> __device__ __forceinline__ void store8(T* p, const float (&f)[8]);
+template <> __device__ __forceinline__ void store8<__nv_bfloat16>(__nv_bfloat16* p, const float (&f)[8]) {
+  st8(p, pack8(f));
+}
+template <> __device__ __forceinline__ void store8<float>(float* p, const float (&f)[8]) {
+  reinterpret_cast<float4*>(p)[0] = make_float4(f[0], f[1], f[2], f[3]);
+  reinterpret_cast<float4*>(p)[1] = make_float4(f[4], f[5], f[6], f[7]);
+}
+
+template <typename TP, typename TG, typename TS>
+__global__ void __launch_bounds__(256) adamw_vec_kernel(TP* __restrict__ p, TG* __restrict__ g, TS* __restrict__ m,
+                                                        TS* __restrict__ v, int64_t nvec, float lr, float b1, float b2,
+                                                        float eps, float wd, float bc1, float rsqrt_bc2,
+                                                        int zero_grad) {
+  const float decay = 1.f - lr * wd, step = lr / bc1;
+  for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < nvec; i += (int64_t)gridDim.x * 256) {
+    float pf[8], gf[8], mf[8], vf[8];
+    load8<TP>(p + i * 8, pf);
+    load8<TG>(g + i * 8, gf);
+    load8<TS>(m + i * 8, mf);
+    load8<TS>(v + i * 8, vf);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      mf[j] = mf[j] * b1 + (1.f - b1) * gf[j];
+      vf[j] = vf[j] * b2 + (1.f - b2) * gf[j] * gf[j];
+      pf[j] = pf[j] * decay - step * mf[j] / (sqrtf(vf[j]) * rsqrt_bc2 + eps);
+    }
+    store8<TP>(p + i * 8, pf);
+    store8<TS>(m + i * 8, mf);
+    store8<TS>(v + i * 8, vf);
+    if (zero_grad) {
+      const float z[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      store8<TG>(g + i * 8, z);
+    }
+  }
+}
+
+template <typename TP, typename TG, typename TS>
+int adamw_launch(void* p, void* g, void* m, void* v, int64_t n, float lr, float b1, float b2, float eps, float wd,
+                 float bc1, float rs, int zg, cudaStream_t st) {
+  const bool vec = (n % 8 == 0) && (((reinterpret_cast<uintptr_t>(p) | reinterpret_cast<uintptr_t>(g) |
+                                      reinterpret_cast<uintptr_t>(m) | reinterpret_cast<uintptr_t>(v)) & 15) == 0);
+  if (vec) {
+    const int64_t nvec = n / 8;
+    const int grid = (int)std::min<int64_t>((nvec + 255) / 256, (int64_t)sm_count() * 8);
+    adamw_vec_kernel<TP, TG, TS><<<grid, 256, 0, st>>>((TP*)p, (TG*)g, (TS*)m, (TS*)v, nvec, lr, b1, b2, eps, wd,
+                                                        bc1, rs, zg);
+  } else {
+    const int grid = (int)std::min<int64_t>((n + 255) / 256, (int64_t)sm_count() * 16);
+    adamw_kernel<TP, TG, TS><<<grid, 256, 0, st>>>((TP*)p, (TG*)g, (TS*)m, (TS*)v, n, lr, b1, b2, eps, wd, bc1, rs,
+                                                    zg);
+  }
+  return launch_status();
+}
+
 template <typename TP, typename TG>
 int adamw_dispatch_s(void* p, void* g, void* m, void* v, int64_t n, int sdt, float lr, float b1, float b2, float eps,
                      float wd, float bc1, float bc2, int zg, cudaStream_t st) {
-  const int grid = (int)std::min<int64_t>((n + 255) / 256, (int64_t)sm_count() * 16);
   const float rs = 1.f / sqrtf(bc2);
-  if (sdt == 0)
-    adamw_kernel<TP, TG, __nv_bfloat16><<<grid, 256, 0, st>>>((TP*)p, (TG*)g, (__nv_bfloat16*)m, (__nv_bfloat16*)v, n,
-                                                              lr, b1, b2, eps, wd, bc1, rs, zg);
-  else if (sdt == 1)
-    adamw_kernel<TP, TG, float><<<grid, 256, 0, st>>>((TP*)p, (TG*)g, (float*)m, (float*)v, n, lr, b1, b2, eps, wd,
-                                                      bc1, rs, zg);
-  else
-    return ERR_UNSUPPORTED;
-  return launch_status();
+  if (sdt == 0) return adamw_launch<TP, TG, __nv_bfloat16>(p, g, m, v, n, lr, b1, b2, eps, wd, bc1, rs, zg, st);
+  if (sdt == 1) return adamw_launch<TP, TG, float>(p, g, m, v, n, lr, b1, b2, eps, wd, bc1, rs, zg, st);
+  return ERR_UNSUPPORTED;
 }
 
 }  // namespace zc

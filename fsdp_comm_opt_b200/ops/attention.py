@@ -10,10 +10,23 @@ matmul/softmax.  The reference reaches PyTorch SDPA through HF attention modules
 from __future__ import annotations
 
 import math
+import os
 
 import torch
 
 from .. import _lib
+
+
+_FWD_IMPL = os.environ.get("ZC_ATTN_FWD", "ws")
+_BWD_IMPL = os.environ.get("ZC_ATTN_BWD", "ws")
+
+
+def status_read_and_clear() -> int:
+    """Non-zero when a bounded wait inside an attention kernel expired since the last call
+    (synchronises the device)."""
+    lib = _lib.cuda()
+    return (int(lib.zc_attn_status_read_and_clear()) | int(lib.zc_attn_ws_status_read_and_clear())
+            | int(lib.zc_attn_bwd_ws_status_read_and_clear()))
 
 
 def _strides(t):
@@ -62,7 +75,10 @@ class _Attention(torch.autograd.Function):
             raise TypeError("CUDA attention expects bf16, head_dim 64 or 128, contiguous heads")
         o = torch.empty(B, S, Hq, D, dtype=qkv.dtype, device=qkv.device)
         lse = torch.empty(B, Hq, S, dtype=torch.float32, device=qkv.device)
-        _lib.check(_lib.cuda().zc_attn_fwd(
+        lib = _lib.cuda()
+        # default: warp-specialised TMA-fed kernel; ZC_ATTN_FWD=simple selects the single-role kernel
+        fwd = lib.zc_attn_fwd if _FWD_IMPL == "simple" else lib.zc_attn_fwd_ws
+        _lib.check(fwd(
             q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(), B, S, Hq, Hkv, D,
             *_strides(q), *_strides(k), *_strides(v), float(scale), _lib.stream_ptr(qkv.device)),
             "zc_attn_fwd")
@@ -85,7 +101,9 @@ class _Attention(torch.autograd.Function):
         dqkv = torch.empty_like(qkv)
         dq, dk, dv = dqkv[:, :, :Hq], dqkv[:, :, Hq:Hq + Hkv], dqkv[:, :, Hq + Hkv:]
         delta = torch.empty(B, Hq, S, dtype=torch.float32, device=qkv.device)
-        _lib.check(_lib.cuda().zc_attn_bwd(
+        lib = _lib.cuda()
+        bwd = lib.zc_attn_bwd if _BWD_IMPL == "simple" else lib.zc_attn_bwd_ws
+        _lib.check(bwd(
             q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), do.data_ptr(), lse.data_ptr(),
             delta.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), B, S, Hq, Hkv, D,
             *_strides(q), *_strides(k), *_strides(v), *_strides(dq), *_strides(dk), *_strides(dv),

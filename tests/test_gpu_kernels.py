@@ -302,7 +302,7 @@ def test_attention_fwd_bwd(B, S, Hq, Hkv, D):
     g = (torch.randn_like(o) * 0.5)
     o.backward(g)
     torch.cuda.synchronize()
-    assert _lib.cuda().zc_attn_status_read_and_clear() == 0
+    assert attention.status_read_and_clear() == 0
     qf = qkv.detach().float().requires_grad_()
     ref = _attn_ref(qf, Hq, Hkv)
     ref.backward(g.float())
