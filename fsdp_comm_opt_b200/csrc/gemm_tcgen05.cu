@@ -18,6 +18,7 @@
 #include <cuda_bf16.h>
 
 #include <cstdio>
+#include <cstdlib>
 
 #include "launch_util.h"
 #include "umma.cuh"
@@ -44,6 +45,7 @@ struct GemmParams {
   __nv_bfloat16* C;
   int64_t M, N, K;
   int a_major, b_major, accumulate;
+  int m_fast;  // 1: consecutive tiles walk m (B tile shared), 0: walk n (A tile shared)
   int* status;
 };
 
@@ -88,7 +90,8 @@ __global__ void __launch_bounds__(G_THREADS, 1) gemm_kernel(const __grid_constan
     if (lane == 0) {
       uint32_t it = 0;
       for (int64_t t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
-        const int m0 = (int)(t % m_tiles) * G_BM, n0 = (int)(t / m_tiles) * BN;
+        const int m0 = (int)(p.m_fast ? t % m_tiles : t / n_tiles) * G_BM;
+        const int n0 = (int)(p.m_fast ? t / m_tiles : t % n_tiles) * BN;
         for (int64_t kb = 0; kb < k_blocks; ++kb, ++it) {
           const int s = it % G_STAGES;
           const uint32_t ph = (it / G_STAGES) & 1;
@@ -148,7 +151,8 @@ __global__ void __launch_bounds__(G_THREADS, 1) gemm_kernel(const __grid_constan
     for (int64_t t = blockIdx.x; t < tiles && ok; t += gridDim.x, ++tile_it) {
       const int acc = tile_it & 1;
       const uint32_t acc_ph = (tile_it >> 1) & 1;
-      const int64_t m0 = (t % m_tiles) * G_BM, n0 = (t / m_tiles) * BN;
+      const int64_t m0 = (p.m_fast ? t % m_tiles : t / n_tiles) * G_BM;
+      const int64_t n0 = (p.m_fast ? t / m_tiles : t % n_tiles) * BN;
       if (!(ok = mbar_wait(&acc_full[acc], acc_ph))) break;
       tc_fence_after_sync();
       const int64_t row = m0 + quarter * 32 + lane;
@@ -267,7 +271,16 @@ int zc_gemm_bf16(const void* A, const void* B, void* C, int64_t M, int64_t N, in
   cudaSetDevice(dev);
   const int a_major = trans_a ? MAJOR_MN : MAJOR_K;   // A stored [K,M] -> M contiguous
   const int b_major = trans_b ? MAJOR_K : MAJOR_MN;   // B stored [N,K] -> K contiguous
-  const int BN = (N % 256 == 0) ? 256 : 128;
+  // tile width: 256 unless the last wave of 128x256 tiles would leave too many SMs idle
+  int BN = (N % 256 == 0) ? 256 : 128;
+  if (BN == 256) {
+    static const int force = getenv("ZC_GEMM_BN") ? atoi(getenv("ZC_GEMM_BN")) : 0;
+    const int sms = sm_count();
+    const int64_t t256 = (M / G_BM) * (N / 256), t128 = 2 * t256;
+    const double e256 = (double)t256 / (double)(((t256 + sms - 1) / sms) * sms);
+    const double e128 = 0.93 * (double)t128 / (double)(((t128 + sms - 1) / sms) * sms);
+    if (force == 128 || (force == 0 && e128 > e256)) BN = 128;
+  }
   CUtensorMap mapA, mapB;
   bool ok;
   if (a_major == MAJOR_K) ok = make_map(&mapA, A, M, K, G_BK, G_BM);
@@ -278,6 +291,7 @@ int zc_gemm_bf16(const void* A, const void* B, void* C, int64_t M, int64_t N, in
   GemmParams p;
   p.C = (__nv_bfloat16*)C; p.M = M; p.N = N; p.K = K;
   p.a_major = a_major; p.b_major = b_major; p.accumulate = accumulate;
+  p.m_fast = (M <= N) ? 1 : 0;  // re-stream the smaller operand, keep the larger one's tile resident
   p.status = gemm_status(dev);
   if (!p.status) {
     fprintf(stderr, "[zc_gemm] could not allocate the status word on device %d\n", dev);

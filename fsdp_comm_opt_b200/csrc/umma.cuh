@@ -64,6 +64,18 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity,
     if ((it & 63u) == 63u && globaltimer_ns() - t0 > limit_ns) return false;
   }
 }
+// Same, for single-thread roles (TMA producer, MMA issuer) that share a scheduler with compute
+// warps: sleeps between polls so the spin does not take issue slots from them.
+__device__ __forceinline__ bool mbar_wait_relaxed(uint64_t* bar, uint32_t parity,
+                                                  unsigned long long limit_ns = 2000000000ull) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const unsigned long long t0 = globaltimer_ns();
+  for (uint32_t it = 0;; ++it) {
+    __nanosleep(32);
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((it & 63u) == 63u && globaltimer_ns() - t0 > limit_ns) return false;
+  }
+}
 
 // ---- proxies and fences ---------------------------------------------------------------------
 // generic-proxy writes to shared memory -> visible to the async proxy (tcgen05.mma operand reads)

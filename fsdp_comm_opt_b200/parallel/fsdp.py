@@ -53,6 +53,15 @@ def _install_hooks(m: FSDPModule, plan: FSDPPlan) -> None:
 
 
 def apply_fsdp(model: torch.nn.Module, plan: FSDPPlan) -> torch.nn.Module:
+    # With bf16 parameters the gradients entering the reduce-scatter are bf16 values and FSDP2
+    # casts the reduced result back to bf16.  The compressed reduce-scatter hook accumulates in
+    # fp32 internally whatever its input dtype, so handing it bf16 rows is numerically the same as
+    # the fp32 hand-off and removes FSDP2's bf16->fp32 copy-in and fp32->bf16 cast (two passes over
+    # every gradient).  Without the hook the reference policy (fp32 reduce) is kept.
+    first = next(model.parameters(), None)
+    if (plan.compress_rs and plan.reduce_dtype == torch.float32 and first is not None
+            and first.dtype == torch.bfloat16 and plan.param_dtype == torch.bfloat16):
+        plan.reduce_dtype = torch.bfloat16
     cfg = dict(
         reshard_after_forward=True,
         offload_policy=CPUOffloadPolicy() if plan.cpu_offload else None,

@@ -10,6 +10,9 @@ from mp_util import run_ranks
 
 pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
 
+# number of ranks for the collective tests (2 by default; ZC_TEST_WORLD=8 on a full box)
+WORLD = int(os.environ.get("ZC_TEST_WORLD", "2"))
+
 
 def _bits(t):
     return t.view(torch.int16)
@@ -56,7 +59,7 @@ def _ag_case(rank, world, transport):
 
 @pytest.mark.parametrize("transport", ["symm", "lib"])
 def test_zip_all_gather_nccl_ranks(transport):
-    run_ranks(_ag_case, 2, (transport,), backend="nccl")
+    run_ranks(_ag_case, WORLD, (transport,), backend="nccl")
 
 
 def _rs_case(rank, world, transport):
@@ -105,7 +108,7 @@ def _rs_case(rank, world, transport):
 
 @pytest.mark.parametrize("transport", ["symm", "lib"])
 def test_compressed_reduce_scatter_nccl_ranks(transport):
-    run_ranks(_rs_case, 2, (transport,), backend="nccl")
+    run_ranks(_rs_case, WORLD, (transport,), backend="nccl")
 
 
 def _timeout_case(rank, world):
