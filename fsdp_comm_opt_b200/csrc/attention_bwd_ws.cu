@@ -37,6 +37,19 @@ __device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* map, u
 __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
+// global[tile at (c0..c3)] += smem tile  (element-wise fp32 add done by the TMA unit; rows past the
+// tensor's extent are clipped)
+__device__ __forceinline__ void tma_reduce_add_4d(const CUtensorMap* map, const void* src, int c0, int c1, int c2,
+                                                  int c3) {
+  asm volatile(
+      "cp.reduce.async.bulk.tensor.4d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
+      ::"l"(map), "r"(smem_u32(src)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+__device__ __forceinline__ void bulk_commit_and_wait_read() {
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+  asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+}
 __device__ __forceinline__ uint64_t desc_k(uint32_t base, int k) {
   return smem_desc(base + (k >> 2) * 16384 + (k & 3) * 32, 16, 1024);
 }
@@ -74,6 +87,7 @@ __global__ void __launch_bounds__(320, 1) attn_bwd_ws_kernel(const __grid_consta
                                                              const __grid_constant__ CUtensorMap mapK,
                                                              const __grid_constant__ CUtensorMap mapV,
                                                              const __grid_constant__ CUtensorMap mapdO,
+                                                             const __grid_constant__ CUtensorMap mapdQ,
                                                              const BwdParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -126,7 +140,7 @@ __global__ void __launch_bounds__(320, 1) attn_bwd_ws_kernel(const __grid_consta
       for (int it = 0; it < iters; ++it) {
         const int h = hk * group + it / (nkb - jb);
         const int q0 = (jb + it % (nkb - jb)) * 128;
-        if (!mbar_wait(&qdo_empty, (it & 1) ^ 1)) { s_abort = 1; break; }
+        if (!mbar_wait_relaxed(&qdo_empty, (it & 1) ^ 1)) { s_abort = 1; break; }
         mbar_expect_tx(&qdo_full, 2 * TILE);
 #pragma unroll
         for (int sl = 0; sl < SLABS; ++sl) {
@@ -142,17 +156,17 @@ __global__ void __launch_bounds__(320, 1) attn_bwd_ws_kernel(const __grid_consta
       const uint32_t id_dq = idesc_bf16(128, D, MAJOR_K, MAJOR_MN);
       const uint32_t aK = smem_u32(sK), aV = smem_u32(sV), aQ = smem_u32(sQ), adO = smem_u32(sdO), aP = smem_u32(sP),
                      adS = smem_u32(sdS);
-      bool ok = mbar_wait(&kv_full, 0);
+      bool ok = mbar_wait_relaxed(&kv_full, 0);
       for (int it = 0; it < iters && ok; ++it) {
-        if (!(ok = mbar_wait(&qdo_full, it & 1))) break;
-        if (!(ok = mbar_wait(&dq_empty, (it & 1) ^ 1))) break;
+        if (!(ok = mbar_wait_relaxed(&qdo_full, it & 1))) break;
+        if (!(ok = mbar_wait_relaxed(&dq_empty, (it & 1) ^ 1))) break;
         tc_fence_after_sync();
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) mma_bf16(tm_r0, desc_k(aQ, k), desc_k(aK, k), id_s, k != 0);
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) mma_bf16(tm_r1, desc_k(adO, k), desc_k(aV, k), id_s, k != 0);
         mma_commit(&sdp_full);
-        if (!(ok = mbar_wait(&pds_full, it & 1))) break;
+        if (!(ok = mbar_wait_relaxed(&pds_full, it & 1))) break;
         tc_fence_after_sync();
 #pragma unroll
         for (int k = 0; k < 8; ++k) mma_bf16(tm_dv, desc_mn(aP, k), desc_mn(adO, k), id_kv, (it | k) != 0);
@@ -210,24 +224,30 @@ __global__ void __launch_bounds__(320, 1) attn_bwd_ws_kernel(const __grid_consta
       // ---- dQ_i partial: this thread reduces its row's columns [half*D/2, half*D/2 + D/2) ---------
       if (!mbar_wait(&dq_full, it & 1)) s_abort = 1;
       tc_fence_after_sync();
-      float* dqrow = p.dq_acc + ((int64_t)(b * p.S + row) * p.Hq + h) * D;
+      // The dV/dK/dQ MMAs have finished reading P and dS, so their 64 KB of shared memory are
+      // free: stage the fp32 dQ_i tile there (32-column slabs, 128B swizzle) and let one thread add
+      // it into the global accumulator with bulk tensor reductions instead of 4096 red.add per CTA.
 #pragma unroll 1
       for (int c = half * (D / 2); c < half * (D / 2) + D / 2; c += 32) {
         uint32_t rr[32];
         tmem_ld32(tmem_addr(tm_r0, lane_base, c), rr);
         tmem_ld_wait();
-        if (row < p.S) {
+        uint8_t* slab = sP + (c >> 5) * 16384;
 #pragma unroll
-          for (int i = 0; i < 32; i += 4)
-            atomicAdd(reinterpret_cast<float4*>(dqrow + c + i),
-                      make_float4(__uint_as_float(rr[i]), __uint_as_float(rr[i + 1]), __uint_as_float(rr[i + 2]),
-                                  __uint_as_float(rr[i + 3])));
-        }
+        for (int i = 0; i < 8; ++i)
+          *reinterpret_cast<uint4*>(slab + sw128_off(r, i)) =
+              make_uint4(rr[4 * i], rr[4 * i + 1], rr[4 * i + 2], rr[4 * i + 3]);
       }
+      fence_proxy_async_smem();
       tc_fence_before_sync();
       named_bar_sync(1, 256);
       if (s_abort) break;
-      if (tid == 64) mbar_arrive(&dq_empty);
+      if (tid == 64) {
+#pragma unroll
+        for (int t = 0; t < D / 32; ++t) tma_reduce_add_4d(&mapdQ, sP + t * 16384, t * 32, h, q0, b);
+        bulk_commit_and_wait_read();
+        mbar_arrive(&dq_empty);
+      }
     }
     if (!s_abort) {
       // all MMAs into dK / dV have completed (dq_full of the last iteration covers them)
@@ -295,6 +315,21 @@ static bool make_map4(CUtensorMap* m, const void* base, int D, int H, int S, int
   if (r != CUDA_SUCCESS)
     fprintf(stderr, "[zc_attn_bwd] cuTensorMapEncodeTiled failed (%d): base=%p D=%d H=%d S=%d B=%d\n", (int)r, base, D,
             H, S, B);
+  return r == CUDA_SUCCESS;
+}
+
+// fp32 accumulator [B, S, Hq, D] viewed as (D, Hq, S, B); box = 32 columns x 128 rows of one head
+static bool make_map4_f32(CUtensorMap* m, const void* base, int D, int H, int S, int B) {
+  EncodeFn fn = encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)H, (cuuint64_t)S, (cuuint64_t)B};
+  cuuint64_t strides[3] = {(cuuint64_t)D * 4, (cuuint64_t)H * D * 4, (cuuint64_t)S * H * D * 4};
+  cuuint32_t box[4] = {32, 1, 128, 1};
+  cuuint32_t el[4] = {1, 1, 1, 1};
+  const CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<void*>(base), dims, strides, box, el,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) fprintf(stderr, "[zc_attn_bwd] fp32 tensor map failed (%d)\n", (int)r);
   return r == CUDA_SUCCESS;
 }
 
@@ -392,10 +427,11 @@ int zc_attn_bwd_ws(const void* q, const void* k, const void* v, const void* o, c
     sc.dq_bytes = need;
   }
   cudaMemsetAsync(sc.dq_acc, 0, need, st);
-  CUtensorMap mq, mk, mv, mdo;
+  CUtensorMap mq, mk, mv, mdo, mdq;
   if (!make_map4(&mq, q, D, Hq, S, B, qs0, qs1, qs2) || !make_map4(&mk, k, D, Hkv, S, B, ks0, ks1, ks2) ||
       !make_map4(&mv, v, D, Hkv, S, B, vs0, vs1, vs2) ||
-      !make_map4(&mdo, dout, D, Hq, S, B, (int64_t)S * Hq * D, (int64_t)Hq * D, D))
+      !make_map4(&mdo, dout, D, Hq, S, B, (int64_t)S * Hq * D, (int64_t)Hq * D, D) ||
+      !make_map4_f32(&mdq, sc.dq_acc, D, Hq, S, B))
     return ERR_BAD_ARG;
   BwdParams p;
   p.lse = lse; p.delta = delta; p.dq_acc = sc.dq_acc; p.dk = (__nv_bfloat16*)dk; p.dv = (__nv_bfloat16*)dv;
@@ -410,10 +446,10 @@ int zc_attn_bwd_ws(const void* q, const void* k, const void* v, const void* o, c
   const dim3 grid((S + 127) / 128, Hkv, B);
   if (D == 128) {
     if (!attr[0]) { cudaFuncSetAttribute(attn_bwd_ws_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); attr[0] = true; }
-    attn_bwd_ws_kernel<128><<<grid, 320, smem, st>>>(mq, mk, mv, mdo, p);
+    attn_bwd_ws_kernel<128><<<grid, 320, smem, st>>>(mq, mk, mv, mdo, mdq, p);
   } else {
     if (!attr[1]) { cudaFuncSetAttribute(attn_bwd_ws_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); attr[1] = true; }
-    attn_bwd_ws_kernel<64><<<grid, 320, smem, st>>>(mq, mk, mv, mdo, p);
+    attn_bwd_ws_kernel<64><<<grid, 320, smem, st>>>(mq, mk, mv, mdo, mdq, p);
   }
   const int cgrid = (int)std::min<int64_t>((rows * (D / 4) + 255) / 256, (int64_t)sm_count() * 16);
   dq_convert_kernel<<<cgrid, 256, 0, st>>>(sc.dq_acc, (__nv_bfloat16*)dq, (int64_t)B * S, Hq, D, dqs1, dqs2);

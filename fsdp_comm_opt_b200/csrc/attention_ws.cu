@@ -1,14 +1,16 @@
 // Warp-specialised causal GQA attention forward for sm_100a (the default forward path).
 //
-// One CTA (192 threads) per (128-query block, query head, batch):
+// One CTA (320 threads) per (128-query block, query head, batch):
 //   warp 0      TMA producer: Q once, then K/V tiles of 128 keys into a two-stage ring (4-D tensor
 //               maps over the packed [B, S, H, D] projection, SWIZZLE_128B, zero fill past S)
 //   warp 1      MMA issuer: S_j = Q K_j^T into one of two TMEM S buffers, issued one block ahead so
 //               the tensor core works on S_{j+1} while the softmax warps are busy with S_j;
 //               then O_j = P_j V_j (V read as an MN-major operand, no transpose)
-//   warps 2-5   softmax: thread t owns query row t; reads its S row from TMEM, keeps the running
-//               max / sum, writes P_j (bf16) to shared memory, and accumulates
-//               O = O * alpha + P_j V_j in registers once that MMA has completed
+//   warps 2-9   softmax: two threads per query row, 64 score columns and D/2 output columns each.
+//               A thread reads its half row of S from TMEM once (kept in registers), the pair
+//               exchanges its partial row maximum through shared memory, each thread writes its
+//               half of P_j (bf16) to shared memory and accumulates its half of
+//               O = O * alpha + P_j V_j in registers once that MMA has completed.
 // Hand-offs are mbarriers (TMA complete_tx, tcgen05.commit, thread arrivals); every wait is
 // bounded and a timed-out role raises a CTA-wide abort flag that all roles honour at their next
 // synchronisation point, so the CTA always reaches its teardown and frees its TMEM.
@@ -27,6 +29,8 @@ using namespace umma;
 
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float LN2 = 0.6931471805599453f;
+constexpr int THREADS = 320;
+constexpr int SM_THREADS = 256;  // softmax threads
 
 __device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1, int c2,
                                             int c3) {
@@ -44,7 +48,8 @@ __device__ __forceinline__ uint64_t desc_k(uint32_t base, int k) {   // K-major 
 __device__ __forceinline__ uint64_t desc_mn(uint32_t base, int k) {  // MN-major tile, K step k
   return smem_desc(base + k * 2048, 16384, 1024);
 }
-__device__ __forceinline__ void store_p_chunk(uint8_t* tile, int row, int col0, const float (&v)[32]) {
+// 32 consecutive P values of row `row`, columns col0..col0+31, into the K-major [128 x 128] tile
+__device__ __forceinline__ void store_p32(uint8_t* tile, int row, int col0, const float* v) {
 #pragma unroll
   for (int q = 0; q < 4; ++q) {
     const int col = col0 + q * 8;
@@ -70,26 +75,28 @@ struct FwdParams {
 };
 
 template <int D>
-__global__ void __launch_bounds__(192, 1) attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap mapQ,
-                                                             const __grid_constant__ CUtensorMap mapK,
-                                                             const __grid_constant__ CUtensorMap mapV,
-                                                             const FwdParams p) {
+__global__ void __maxnreg__(200) attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap mapQ,
+                                                                 const __grid_constant__ CUtensorMap mapK,
+                                                                 const __grid_constant__ CUtensorMap mapV,
+                                                                 const FwdParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   constexpr int TILE = 128 * D * 2;  // bytes of one [128 x D] tile
   constexpr int SLABS = D / 64;
+  constexpr int DH = D / 2;          // output columns per softmax thread
   uint8_t* sQ = smem;
   uint8_t* sP = smem + 32768;
   uint8_t* sKV = smem + 65536;  // stage s: K at s*65536, V at s*65536 + 32768
   __shared__ uint64_t q_full, kv_full[2], kv_empty[2], s_full[2], s_empty[2], p_full, o_full;
   __shared__ uint32_t tmem_base;
   __shared__ volatile int s_abort;
+  __shared__ float s_xchg[2][128];  // partial row max (per block) / partial row sum (at the end)
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int qb = gridDim.x - 1 - blockIdx.x;
   const int h = blockIdx.y, b = blockIdx.z;
   const int hk = h / (p.Hq / p.Hkv);
   const int q0 = qb * 128;
-  const int nb = min(qb + 1, (p.S + 127) / 128);
+  const int nb = qb + 1;
   if (tid == 0) {
     mbar_init(&q_full, 1);
     for (int i = 0; i < 2; ++i) {
@@ -119,7 +126,7 @@ __global__ void __launch_bounds__(192, 1) attn_fwd_ws_kernel(const __grid_consta
       for (int sl = 0; sl < SLABS; ++sl) tma_load_4d(sQ + sl * 16384, &mapQ, &q_full, sl * 64, h, q0, b);
       for (int j = 0; j < nb; ++j) {
         const int s = j & 1;
-        if (!mbar_wait(&kv_empty[s], ((j >> 1) & 1) ^ 1)) { s_abort = 1; break; }
+        if (!mbar_wait_relaxed(&kv_empty[s], ((j >> 1) & 1) ^ 1)) { s_abort = 1; break; }
         uint8_t* sk = sKV + s * 65536;
         mbar_expect_tx(&kv_full[s], 2 * TILE);
 #pragma unroll
@@ -133,11 +140,11 @@ __global__ void __launch_bounds__(192, 1) attn_fwd_ws_kernel(const __grid_consta
     if (lane == 0) {
       const uint32_t id_s = idesc_bf16(128, 128, MAJOR_K, MAJOR_K);
       const uint32_t id_o = idesc_bf16(128, D, MAJOR_K, MAJOR_MN);
-      bool ok = mbar_wait(&q_full, 0);
+      bool ok = mbar_wait_relaxed(&q_full, 0);
       auto issue_s = [&](int i) -> bool {
         const int s = i & 1;
-        if (!mbar_wait(&kv_full[s], (i >> 1) & 1)) return false;
-        if (!mbar_wait(&s_empty[s], ((i >> 1) & 1) ^ 1)) return false;
+        if (!mbar_wait_relaxed(&kv_full[s], (i >> 1) & 1)) return false;
+        if (!mbar_wait_relaxed(&s_empty[s], ((i >> 1) & 1) ^ 1)) return false;
         tc_fence_after_sync();
         const uint32_t kq = smem_u32(sQ), kk = smem_u32(sKV + s * 65536);
 #pragma unroll
@@ -149,7 +156,7 @@ __global__ void __launch_bounds__(192, 1) attn_fwd_ws_kernel(const __grid_consta
       for (int j = 0; j < nb && ok; ++j) {
         if (j + 1 < nb) ok = issue_s(j + 1);
         if (!ok) break;
-        if (!(ok = mbar_wait(&p_full, j & 1))) break;
+        if (!(ok = mbar_wait_relaxed(&p_full, j & 1))) break;
         tc_fence_after_sync();
         const uint32_t pp = smem_u32(sP), vv = smem_u32(sKV + (j & 1) * 65536 + 32768);
 #pragma unroll
@@ -160,96 +167,104 @@ __global__ void __launch_bounds__(192, 1) attn_fwd_ws_kernel(const __grid_consta
       if (!ok) s_abort = 1;
     }
   } else {
-    const int quarter = warp & 3;
-    const int r = quarter * 32 + lane;  // query row inside the tile == TMEM lane
+    const int cw = warp - 2;
+    const int quarter = warp & 3;          // TMEM lane quarter this warp may access
+    const int half = cw >> 2;              // which 64 score columns / D/2 output columns
+    const int r = quarter * 32 + lane;     // query row inside the tile == TMEM lane
     const int row = q0 + r;
     const uint32_t lane_base = (uint32_t)(quarter * 32);
+    const int sc0 = half * 64;             // first score column of this thread
+    const int oc0 = half * DH;             // first output column of this thread
     const float sl2 = p.scale * LOG2E;
     float m = -CUDART_INF_F, l = 0.f, alpha_prev = 1.f;
-    float o[D];
+    float o[DH];
 #pragma unroll
-    for (int i = 0; i < D; ++i) o[i] = 0.f;
-    int j = 0;
-    for (; j < nb; ++j) {
+    for (int i = 0; i < DH; ++i) o[i] = 0.f;
+    for (int j = 0; j < nb; ++j) {
       const int sb = j & 1;
       if (!mbar_wait(&s_full[sb], (j >> 1) & 1)) s_abort = 1;
       tc_fence_after_sync();
       const int k0 = j * 128;
       const bool diag = (j == qb) || (k0 + 128 > p.S);
-      float mx = -CUDART_INF_F;
-#pragma unroll 1
-      for (int c = 0; c < 128; c += 32) {
-        uint32_t rr[32];
-        tmem_ld32(tmem_addr(tm + sb * 128, lane_base, c), rr);
-        tmem_ld_wait();
+      uint32_t sa[32], sbv[32];
+      tmem_ld32(tmem_addr(tm + sb * 128, lane_base, sc0), sa);
+      tmem_ld32(tmem_addr(tm + sb * 128, lane_base, sc0 + 32), sbv);
+      tmem_ld_wait();
+      float sv[64];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float s = __uint_as_float(rr[i]);
-          if (diag && (k0 + c + i > row || k0 + c + i >= p.S)) s = -CUDART_INF_F;
-          mx = fmaxf(mx, s);
-        }
+      for (int i = 0; i < 32; ++i) {
+        sv[i] = __uint_as_float(sa[i]);
+        sv[32 + i] = __uint_as_float(sbv[i]);
       }
+      if (diag) {
+#pragma unroll
+        for (int i = 0; i < 64; ++i)
+          if (k0 + sc0 + i > row || k0 + sc0 + i >= p.S) sv[i] = -CUDART_INF_F;
+      }
+      float mx = sv[0];
+#pragma unroll
+      for (int i = 1; i < 64; ++i) mx = fmaxf(mx, sv[i]);
+      s_xchg[half][r] = mx;
+      named_bar_sync(1, SM_THREADS);
+      mx = fmaxf(mx, s_xchg[half ^ 1][r]);
       const float m_new = fmaxf(m, mx * sl2);
       const float m_use = (m_new == -CUDART_INF_F) ? 0.f : m_new;
       const float alpha = exp2f(m - m_use);
       if (j > 0) {
-        // fold in the previous block's P V (its MMA has had the whole max pass to finish)
+        // fold in the previous block's P V (its MMA ran while this block's scores were read)
         if (!mbar_wait(&o_full, (j - 1) & 1)) s_abort = 1;
         tc_fence_after_sync();
 #pragma unroll
-        for (int c = 0; c < D; c += 32) {
+        for (int c = 0; c < DH; c += 32) {
           uint32_t rr[32];
-          tmem_ld32(tmem_addr(tm + 256, lane_base, c), rr);
+          tmem_ld32(tmem_addr(tm + 256, lane_base, oc0 + c), rr);
           tmem_ld_wait();
 #pragma unroll
           for (int i = 0; i < 32; ++i) o[c + i] = o[c + i] * alpha_prev + __uint_as_float(rr[i]);
         }
       }
       float rs = 0.f;
-#pragma unroll 1
-      for (int c = 0; c < 128; c += 32) {
-        uint32_t rr[32];
-        tmem_ld32(tmem_addr(tm + sb * 128, lane_base, c), rr);
-        tmem_ld_wait();
-        float pv[32];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float e = exp2f(__uint_as_float(rr[i]) * sl2 - m_use);
-          if (diag && (k0 + c + i > row || k0 + c + i >= p.S)) e = 0.f;
-          pv[i] = e;
-          rs += e;
-        }
-        store_p_chunk(sP, r, c, pv);
+      for (int i = 0; i < 64; ++i) {
+        const float e = exp2f(sv[i] * sl2 - m_use);  // exp2(-inf) = 0 for masked entries
+        sv[i] = e;
+        rs += e;
       }
+      store_p32(sP, r, sc0, sv);
+      store_p32(sP, r, sc0 + 32, sv + 32);
       l = l * alpha + rs;
       m = m_new;
       alpha_prev = alpha;
       fence_proxy_async_smem();
       tc_fence_before_sync();
-      named_bar_sync(1, 128);
+      named_bar_sync(2, SM_THREADS);
       if (s_abort) break;
-      if (r == 0) {
+      if (tid == 64) {
         mbar_arrive(&p_full);
         mbar_arrive(&s_empty[sb]);
       }
     }
-    if (!s_abort && nb > 0) {
+    if (!s_abort) {
       if (!mbar_wait(&o_full, (nb - 1) & 1)) s_abort = 1;
       tc_fence_after_sync();
 #pragma unroll
-      for (int c = 0; c < D; c += 32) {
+      for (int c = 0; c < DH; c += 32) {
         uint32_t rr[32];
-        tmem_ld32(tmem_addr(tm + 256, lane_base, c), rr);
+        tmem_ld32(tmem_addr(tm + 256, lane_base, oc0 + c), rr);
         tmem_ld_wait();
 #pragma unroll
         for (int i = 0; i < 32; ++i) o[c + i] = o[c + i] * alpha_prev + __uint_as_float(rr[i]);
       }
     }
+    // combine the two partial row sums
+    s_xchg[half][r] = l;
+    named_bar_sync(1, SM_THREADS);
+    l += s_xchg[half ^ 1][r];
     if (!s_abort && row < p.S) {
       const float inv = l > 0.f ? 1.f / l : 0.f;
-      __nv_bfloat16* dst = p.o + ((int64_t)(b * p.S + row) * p.Hq + h) * D;
+      __nv_bfloat16* dst = p.o + ((int64_t)(b * p.S + row) * p.Hq + h) * D + oc0;
 #pragma unroll
-      for (int c = 0; c < D; c += 8) {
+      for (int c = 0; c < DH; c += 8) {
         __nv_bfloat162 a0 = __floats2bfloat162_rn(o[c] * inv, o[c + 1] * inv);
         __nv_bfloat162 a1 = __floats2bfloat162_rn(o[c + 2] * inv, o[c + 3] * inv);
         __nv_bfloat162 a2 = __floats2bfloat162_rn(o[c + 4] * inv, o[c + 5] * inv);
@@ -261,7 +276,8 @@ __global__ void __launch_bounds__(192, 1) attn_fwd_ws_kernel(const __grid_consta
         u.w = *reinterpret_cast<uint32_t*>(&a3);
         *reinterpret_cast<uint4*>(dst + c) = u;
       }
-      p.lse[((int64_t)b * p.Hq + h) * p.S + row] = (l > 0.f) ? (m + log2f(l)) * LN2 : -CUDART_INF_F;
+      if (half == 0)
+        p.lse[((int64_t)b * p.Hq + h) * p.S + row] = (l > 0.f) ? (m + log2f(l)) * LN2 : -CUDART_INF_F;
     }
   }
   tc_fence_before_sync();
@@ -356,10 +372,10 @@ int zc_attn_fwd_ws(const void* q, const void* k, const void* v, void* o, float* 
   const dim3 grid((S + 127) / 128, Hq, B);
   if (D == 128) {
     if (!attr[0]) { cudaFuncSetAttribute(attn_fwd_ws_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); attr[0] = true; }
-    attn_fwd_ws_kernel<128><<<grid, 192, smem, st>>>(mq, mk, mv, p);
+    attn_fwd_ws_kernel<128><<<grid, THREADS, smem, st>>>(mq, mk, mv, p);
   } else {
     if (!attr[1]) { cudaFuncSetAttribute(attn_fwd_ws_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); attr[1] = true; }
-    attn_fwd_ws_kernel<64><<<grid, 192, smem, st>>>(mq, mk, mv, p);
+    attn_fwd_ws_kernel<64><<<grid, THREADS, smem, st>>>(mq, mk, mv, p);
   }
   return launch_status();
 }

@@ -97,6 +97,44 @@ __device__ __forceinline__ uint32_t v2_encode_chunk(const LaneSplit& s, uint8_t*
   return hdr;
 }
 
+// Encode with a window carried over from the previous chunk of the same stream ("hint", a header
+// with width 1..4, or 0xFFFFFFFF for none).  The hint is kept while its exact escape count stays
+// close to the count it had when it was chosen; otherwise the window is chosen afresh.  Any valid
+// choice decodes correctly, so this only trades a little compression for skipping the histogram.
+// Returns the header; `hint` / `hint_esc` are updated for the next chunk.
+__device__ __forceinline__ uint32_t v2_encode_chunk_hint(const LaneSplit& s, uint8_t* rec, int lane, uint32_t& hint,
+                                                         int& hint_esc) {
+  if (hint != 0xFFFFFFFFu) {
+    const int w = v2_hdr_width(hint), base = v2_hdr_base(hint);
+    uint32_t code[8];
+    codes_lane(s, base, (1u << w) - 1u, code);
+    const uint32_t zm = zero_mask(code);
+    int n_esc;
+    const int pos = warp_excl_scan(__popc(zm), lane, n_esc);
+    if (n_esc <= hint_esc + (hint_esc >> 1) + 16 && 128 * w + n_esc <= V2_CHUNK_ELEMS) {
+      uint4* smp = reinterpret_cast<uint4*>(rec + lane * 32);
+      smp[0] = make_uint4(s.sm[0], s.sm[1], s.sm[2], s.sm[3]);
+      smp[1] = make_uint4(s.sm[4], s.sm[5], s.sm[6], s.sm[7]);
+      uint32_t* pl = reinterpret_cast<uint32_t*>(rec + 1024) + lane;
+      pl[0] = plane_word<0>(code);
+      if (w > 1) pl[32] = plane_word<1>(code);
+      if (w > 2) pl[64] = plane_word<2>(code);
+      if (w > 3) pl[96] = plane_word<3>(code);
+      scatter_escapes(rec + 1024 + 128 * w + pos, s, zm);
+      return v2_header(base, w, n_esc);
+    }
+  }
+  const uint32_t hdr = v2_encode_chunk(s, rec, lane);
+  const int w = v2_hdr_width(hdr);
+  if (w >= 1 && w <= 4) {
+    hint = hdr & 0xFFFFu;
+    hint_esc = v2_hdr_nesc(hdr);
+  } else {
+    hint = 0xFFFFFFFFu;
+  }
+  return hdr;
+}
+
 // Decode one chunk record into split fields.
 __device__ __forceinline__ void v2_decode_chunk(const uint8_t* rec, uint32_t hdr, int lane, LaneSplit& s) {
   const int w = v2_hdr_width(hdr);

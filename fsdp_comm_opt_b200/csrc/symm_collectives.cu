@@ -125,6 +125,8 @@ __global__ void __launch_bounds__(256) symm_all_gather_kernel(const AgArgs a) {
     const bool copy_own = own != a.in;
     const bool own_al = (reinterpret_cast<uintptr_t>(own) & 15) == 0;
     unsigned long long pushed = 0;
+    uint32_t hint = 0xFFFFFFFFu;  // window of the previous chunk this warp encoded
+    int hint_esc = 0;
     for (long long g = blockIdx.x; g < ngroups; g += a.push_ctas) {
       for (int it = 0; it < GROUP_CHUNKS / 8; ++it) {
         const long long c = g * GROUP_CHUNKS + it * 8 + warp;
@@ -135,7 +137,7 @@ __global__ void __launch_bounds__(256) symm_all_gather_kernel(const AgArgs a) {
         if (copy_own) store_lane(own + e0, a.n - e0, own_al, li);
         LaneSplit s;
         split_lane(li, s);
-        const uint32_t hdr = v2_encode_chunk(s, srec[warp], lane);
+        const uint32_t hdr = v2_encode_chunk_hint(s, srec[warp], lane, hint, hint_esc);
         __syncwarp();
         const int used = v2_record_bytes(hdr);
         for (int q = 0; q < L.world; ++q) {
@@ -268,6 +270,8 @@ __global__ void __launch_bounds__(256) symm_reduce_scatter_kernel(const RsArgs a
     __syncthreads();
     if (!s_ok) return;
     unsigned long long pushed = 0;
+    uint32_t hint = 0xFFFFFFFFu;
+    int hint_esc = 0;
     // work item = (destination, group); destinations interleaved so all links are busy
     const long long items = ngroups * (L.world - 1);
     for (long long i = blockIdx.x; i < items; i += a.push_ctas) {
@@ -303,7 +307,7 @@ __global__ void __launch_bounds__(256) symm_reduce_scatter_kernel(const RsArgs a
         }
         LaneSplit s;
         split_lane(li, s);
-        const uint32_t hdr = v2_encode_chunk(s, srec[warp], lane);
+        const uint32_t hdr = v2_encode_chunk_hint(s, srec[warp], lane, hint, hint_esc);
         __syncwarp();
         const int used = v2_record_bytes(hdr);
         warp_copy16(slot + L.hdr_bytes + c * V2_SLOT_BYTES, srec[warp], used, lane);
