@@ -75,7 +75,9 @@ struct FwdParams {
 };
 
 template <int D>
-__global__ void __maxnreg__(200) attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap mapQ,
+// Ten warps put three warps on two of the four SM sub-partitions, each of which owns 16384
+// registers: 3 x 32 x R <= 16384 caps a thread at 168 registers (a launch with more fails).
+__global__ void __launch_bounds__(THREADS, 1) attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap mapQ,
                                                                  const __grid_constant__ CUtensorMap mapK,
                                                                  const __grid_constant__ CUtensorMap mapV,
                                                                  const FwdParams p) {
@@ -186,24 +188,25 @@ __global__ void __maxnreg__(200) attn_fwd_ws_kernel(const __grid_constant__ CUte
       tc_fence_after_sync();
       const int k0 = j * 128;
       const bool diag = (j == qb) || (k0 + 128 > p.S);
-      uint32_t sa[32], sbv[32];
-      tmem_ld32(tmem_addr(tm + sb * 128, lane_base, sc0), sa);
-      tmem_ld32(tmem_addr(tm + sb * 128, lane_base, sc0 + 32), sbv);
-      tmem_ld_wait();
-      float sv[64];
+      // pass 1: row maximum over this thread's 64 columns (both loads in flight, one wait)
+      float mx = -CUDART_INF_F;
+      {
+        uint32_t sa[32], sbv[32];
+        tmem_ld32(tmem_addr(tm + sb * 128, lane_base, sc0), sa);
+        tmem_ld32(tmem_addr(tm + sb * 128, lane_base, sc0 + 32), sbv);
+        tmem_ld_wait();
+        if (diag) {
 #pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        sv[i] = __uint_as_float(sa[i]);
-        sv[32 + i] = __uint_as_float(sbv[i]);
+          for (int i = 0; i < 32; ++i) {
+            const int c0 = k0 + sc0 + i, c1 = c0 + 32;
+            if (c0 <= row && c0 < p.S) mx = fmaxf(mx, __uint_as_float(sa[i]));
+            if (c1 <= row && c1 < p.S) mx = fmaxf(mx, __uint_as_float(sbv[i]));
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, fmaxf(__uint_as_float(sa[i]), __uint_as_float(sbv[i])));
+        }
       }
-      if (diag) {
-#pragma unroll
-        for (int i = 0; i < 64; ++i)
-          if (k0 + sc0 + i > row || k0 + sc0 + i >= p.S) sv[i] = -CUDART_INF_F;
-      }
-      float mx = sv[0];
-#pragma unroll
-      for (int i = 1; i < 64; ++i) mx = fmaxf(mx, sv[i]);
       s_xchg[half][r] = mx;
       named_bar_sync(1, SM_THREADS);
       mx = fmaxf(mx, s_xchg[half ^ 1][r]);
@@ -223,15 +226,24 @@ __global__ void __maxnreg__(200) attn_fwd_ws_kernel(const __grid_constant__ CUte
           for (int i = 0; i < 32; ++i) o[c + i] = o[c + i] * alpha_prev + __uint_as_float(rr[i]);
         }
       }
+      // pass 2: re-read the scores 32 columns at a time, exponentiate, write P
       float rs = 0.f;
+#pragma unroll 1
+      for (int c = 0; c < 64; c += 32) {
+        uint32_t rr[32];
+        tmem_ld32(tmem_addr(tm + sb * 128, lane_base, sc0 + c), rr);
+        tmem_ld_wait();
+        float pv[32];
 #pragma unroll
-      for (int i = 0; i < 64; ++i) {
-        const float e = exp2f(sv[i] * sl2 - m_use);  // exp2(-inf) = 0 for masked entries
-        sv[i] = e;
-        rs += e;
+        for (int i = 0; i < 32; ++i) {
+          float e = exp2f(__uint_as_float(rr[i]) * sl2 - m_use);
+          const int col = k0 + sc0 + c + i;
+          if (diag && (col > row || col >= p.S)) e = 0.f;
+          pv[i] = e;
+          rs += e;
+        }
+        store_p32(sP, r, sc0 + c, pv);
       }
-      store_p32(sP, r, sc0, sv);
-      store_p32(sP, r, sc0 + 32, sv + 32);
       l = l * alpha + rs;
       m = m_new;
       alpha_prev = alpha;

@@ -70,8 +70,9 @@ __device__ __forceinline__ float block_max(float v, float* red) {
 //   h = x (+ residual, rounded to bf16);  rstd = rsqrt(mean(h^2) + eps);  y = h * rstd * w
 // ---------------------------------------------------------------------------------------------
 constexpr int RN_THREADS = 256;
-constexpr int RN_MAXV = 4;  // vectors of 8 per thread
+constexpr int RN_MAX_COLS = RN_THREADS * 4 * 8;  // MAXV (vectors of 8 per thread) is 1, 2 or 4
 
+template <int MAXV>
 __global__ void __launch_bounds__(RN_THREADS) rmsnorm_fwd_kernel(
     const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ res,
     const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ y, __nv_bfloat16* __restrict__ h_out,
@@ -79,10 +80,10 @@ __global__ void __launch_bounds__(RN_THREADS) rmsnorm_fwd_kernel(
   __shared__ float red[32];
   const int64_t row = blockIdx.x;
   const int nvec = cols / 8;
-  float h[RN_MAXV][8];
+  float h[MAXV][8];
   float ss = 0.f;
 #pragma unroll
-  for (int i = 0; i < RN_MAXV; ++i) {
+  for (int i = 0; i < MAXV; ++i) {
     const int v = threadIdx.x + i * RN_THREADS;
     if (v < nvec) {
       unpack8(ld8(x + row * cols + v * 8), h[i]);
@@ -103,7 +104,7 @@ __global__ void __launch_bounds__(RN_THREADS) rmsnorm_fwd_kernel(
   const float rstd = rsqrtf(ss / (float)cols + eps);
   if (threadIdx.x == 0) rstd_out[row] = rstd;
 #pragma unroll
-  for (int i = 0; i < RN_MAXV; ++i) {
+  for (int i = 0; i < MAXV; ++i) {
     const int v = threadIdx.x + i * RN_THREADS;
     if (v < nvec) {
       float wv[8], o[8];
@@ -117,6 +118,7 @@ __global__ void __launch_bounds__(RN_THREADS) rmsnorm_fwd_kernel(
 
 // dx = rstd * (g - xhat * mean(g * xhat)) (+ dh),  g = dy * w,  xhat = h * rstd
 // dw += sum_rows dy * xhat   (fp32 atomics into dw32 once per CTA)
+template <int MAXV>
 __global__ void __launch_bounds__(RN_THREADS) rmsnorm_bwd_kernel(
     const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ h,
     const __nv_bfloat16* __restrict__ w, const float* __restrict__ rstd_in,
@@ -124,9 +126,9 @@ __global__ void __launch_bounds__(RN_THREADS) rmsnorm_bwd_kernel(
     int64_t rows, int cols) {
   __shared__ float red[32];
   const int nvec = cols / 8;
-  float wv[RN_MAXV][8], dwacc[RN_MAXV][8];
+  float wv[MAXV][8], dwacc[MAXV][8];
 #pragma unroll
-  for (int i = 0; i < RN_MAXV; ++i) {
+  for (int i = 0; i < MAXV; ++i) {
     const int v = threadIdx.x + i * RN_THREADS;
 #pragma unroll
     for (int j = 0; j < 8; ++j) dwacc[i][j] = 0.f;
@@ -134,10 +136,10 @@ __global__ void __launch_bounds__(RN_THREADS) rmsnorm_bwd_kernel(
   }
   for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
     const float rstd = rstd_in[row];
-    float g[RN_MAXV][8], xh[RN_MAXV][8];
+    float g[MAXV][8], xh[MAXV][8];
     float dot = 0.f;
 #pragma unroll
-    for (int i = 0; i < RN_MAXV; ++i) {
+    for (int i = 0; i < MAXV; ++i) {
       const int v = threadIdx.x + i * RN_THREADS;
       if (v < nvec) {
         float d[8];
@@ -154,7 +156,7 @@ __global__ void __launch_bounds__(RN_THREADS) rmsnorm_bwd_kernel(
     }
     dot = block_sum(dot, red) / (float)cols;
 #pragma unroll
-    for (int i = 0; i < RN_MAXV; ++i) {
+    for (int i = 0; i < MAXV; ++i) {
       const int v = threadIdx.x + i * RN_THREADS;
       if (v < nvec) {
         float o[8];
@@ -171,7 +173,7 @@ __global__ void __launch_bounds__(RN_THREADS) rmsnorm_bwd_kernel(
     }
   }
 #pragma unroll
-  for (int i = 0; i < RN_MAXV; ++i) {
+  for (int i = 0; i < MAXV; ++i) {
     const int v = threadIdx.x + i * RN_THREADS;
     if (v < nvec) {
 #pragma unroll
@@ -490,20 +492,33 @@ typedef __nv_bfloat16 bf16;
 
 int zc_rmsnorm_fwd(const void* x, const void* res, const void* w, void* y, void* h_out, float* rstd, int64_t rows,
                    int cols, float eps, cudaStream_t st) {
-  if (cols % 8 || cols > zc::RN_THREADS * zc::RN_MAXV * 8) return ERR_UNSUPPORTED;
+  if (cols % 8 || cols > zc::RN_MAX_COLS) return ERR_UNSUPPORTED;
   if (rows == 0) return 0;
-  zc::rmsnorm_fwd_kernel<<<(unsigned)rows, zc::RN_THREADS, 0, st>>>((const bf16*)x, (const bf16*)res, (const bf16*)w,
-                                                                   (bf16*)y, (bf16*)h_out, rstd, cols, eps);
+  const int nvec = cols / 8;
+#define ZC_RN_FWD(V)                                                                                              \
+  zc::rmsnorm_fwd_kernel<V><<<(unsigned)rows, zc::RN_THREADS, 0, st>>>((const bf16*)x, (const bf16*)res,          \
+                                                                       (const bf16*)w, (bf16*)y, (bf16*)h_out,    \
+                                                                       rstd, cols, eps)
+  if (nvec <= zc::RN_THREADS) ZC_RN_FWD(1);
+  else if (nvec <= 2 * zc::RN_THREADS) ZC_RN_FWD(2);
+  else ZC_RN_FWD(4);
+#undef ZC_RN_FWD
   return zc::launch_status();
 }
 
 int zc_rmsnorm_bwd(const void* dy, const void* h, const void* w, const float* rstd, const void* dh, void* dx,
                    float* dw32, int64_t rows, int cols, cudaStream_t st) {
-  if (cols % 8 || cols > zc::RN_THREADS * zc::RN_MAXV * 8) return ERR_UNSUPPORTED;
+  if (cols % 8 || cols > zc::RN_MAX_COLS) return ERR_UNSUPPORTED;
   if (rows == 0) return 0;
   const int grid = (int)std::min<int64_t>(rows, (int64_t)zc::sm_count() * 4);
-  zc::rmsnorm_bwd_kernel<<<grid, zc::RN_THREADS, 0, st>>>((const bf16*)dy, (const bf16*)h, (const bf16*)w, rstd,
-                                                          (const bf16*)dh, (bf16*)dx, dw32, rows, cols);
+  const int nvec = cols / 8;
+#define ZC_RN_BWD(V)                                                                                             \
+  zc::rmsnorm_bwd_kernel<V><<<grid, zc::RN_THREADS, 0, st>>>((const bf16*)dy, (const bf16*)h, (const bf16*)w,    \
+                                                             rstd, (const bf16*)dh, (bf16*)dx, dw32, rows, cols)
+  if (nvec <= zc::RN_THREADS) ZC_RN_BWD(1);
+  else if (nvec <= 2 * zc::RN_THREADS) ZC_RN_BWD(2);
+  else ZC_RN_BWD(4);
+#undef ZC_RN_BWD
   return zc::launch_status();
 }
 
