@@ -87,8 +87,14 @@ class Channel:
         # collective CTA needs only 16 KB of shared memory, so two of them fit beside a GEMM CTA on
         # every SM.  One pusher and one decoder CTA per SM keeps the wall time of a collective
         # short; fewer CTAs make it encode-bound (measured: 24+37 CTAs -> 89 GB/s bus at 2 GPUs).
+        # Progress argument for two collectives in flight at once (FSDP overlaps the next all-gather
+        # with a reduce-scatter): pusher CTAs never wait, so they always retire; only decoder CTAs
+        # hold an SM slot while they wait for a peer.  Beside a resident GEMM CTA an SM still has
+        # room for two collective CTAs (2 x sm slots); keeping the decoders of both kernels below
+        # that (2 x (sm - 20)) always leaves slots through which every kernel's pushers drain, on
+        # every rank, whatever order the ranks scheduled the two kernels in.
         self.push_ctas = int(os.environ.get("ZC_SYMM_PUSH_CTAS", str(sm)))
-        self.dec_ctas = int(os.environ.get("ZC_SYMM_DEC_CTAS", str(sm)))
+        self.dec_ctas = int(os.environ.get("ZC_SYMM_DEC_CTAS", str(max(8, sm - 20))))
         self._lib = _lib.cuda()
         self._lib._lib.zc_symm_buffer_bytes.restype = ctypes.c_int64
         self._lib._lib.zc_symm_buffer_bytes.argtypes = [ctypes.c_int, ctypes.c_int64]
