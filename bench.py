@@ -270,6 +270,15 @@ def main():
 
     dev_ms, dev_loss, launches, (d0, d1) = run("device")
     e2e_ms, e2e_loss, _, (x0, x1) = run("e2e")
+    if args.impl == "ours":
+        # a bounded device-side wait that expired would have left wrong data behind: fail loudly
+        from fsdp_comm_opt_b200.ops import attention as _attn
+        from fsdp_comm_opt_b200.parallel import symm_impl as _symm
+
+        for ch in _symm.all_channels():
+            ch.check_status()
+        if _attn.status_read_and_clear() != 0:
+            raise RuntimeError("an attention kernel reported an expired wait")
     if rank == 0:
         time.sleep(0.3)
         sampler.stop()

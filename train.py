@@ -36,6 +36,7 @@ from fsdp_comm_opt_b200.utils import checkpoint as ckpt
 from fsdp_comm_opt_b200.utils.data import SyntheticTokens, collate, load_text_dataset
 from fsdp_comm_opt_b200.utils.dist import all_reduce_max, init_distributed, rank0_first
 from fsdp_comm_opt_b200.utils.failure import Heartbeat
+from fsdp_comm_opt_b200.utils.health import check_device_status
 from fsdp_comm_opt_b200.utils.metrics import get_mem_stats, setup_logging
 from fsdp_comm_opt_b200.utils.timing import LocalTimer
 
@@ -211,6 +212,7 @@ def main(argv=None):
                     }
                     LOGGER.info(info)
                     if device.type == "cuda":
+                        check_device_status()  # expired device-side waits become exceptions here
                         torch.cuda.reset_peak_memory_stats(device)
                     state["running_loss"] = 0
                     for t in timers.values():
