@@ -301,13 +301,15 @@ static EncodeFn encode_fn() {
   }
   return fn;
 }
+// bf16 [B, S, H, D] with element strides (s_b, s_s, s_h), viewed as (D, H, S, B); box = one 64-wide
+// slab of `rows` sequence positions of one head
 static bool make_map4(CUtensorMap* m, const void* base, int D, int H, int S, int B, int64_t s_b, int64_t s_s,
-                      int64_t s_h) {
+                      int64_t s_h, int rows = 128) {
   EncodeFn fn = encode_fn();
   if (!fn) return false;
   cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)H, (cuuint64_t)S, (cuuint64_t)B};
   cuuint64_t strides[3] = {(cuuint64_t)s_h * 2, (cuuint64_t)s_s * 2, (cuuint64_t)s_b * 2};
-  cuuint32_t box[4] = {64, 1, 128, 1};
+  cuuint32_t box[4] = {64, 1, (cuuint32_t)rows, 1};
   cuuint32_t el[4] = {1, 1, 1, 1};
   const CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, el,
                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
@@ -318,17 +320,18 @@ static bool make_map4(CUtensorMap* m, const void* base, int D, int H, int S, int
   return r == CUDA_SUCCESS;
 }
 
-// fp32 accumulator [B, S, Hq, D] viewed as (D, Hq, S, B); box = 32 columns x 128 rows of one head
-static bool make_map4_f32(CUtensorMap* m, const void* base, int D, int H, int S, int B) {
+// fp32 accumulator [B, S, Hq, D] viewed as (D, Hq, S, B); box = 32 columns x `rows` rows of one head
+static bool make_map4_f32(CUtensorMap* m, const void* base, int D, int H, int S, int B, int rows = 128,
+                          bool swizzle = true) {
   EncodeFn fn = encode_fn();
   if (!fn) return false;
   cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)H, (cuuint64_t)S, (cuuint64_t)B};
   cuuint64_t strides[3] = {(cuuint64_t)D * 4, (cuuint64_t)H * D * 4, (cuuint64_t)S * H * D * 4};
-  cuuint32_t box[4] = {32, 1, 128, 1};
+  cuuint32_t box[4] = {32, 1, (cuuint32_t)rows, 1};
   cuuint32_t el[4] = {1, 1, 1, 1};
   const CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<void*>(base), dims, strides, box, el,
-                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
-                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                        CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) fprintf(stderr, "[zc_attn_bwd] fp32 tensor map failed (%d)\n", (int)r);
   return r == CUDA_SUCCESS;
 }
@@ -382,6 +385,341 @@ __global__ void __launch_bounds__(256) dq_convert_kernel(const float* __restrict
 }
 
 }  // namespace bws
+
+// =================================================================================================
+// Key-row ("transposed") backward for head dimension 128: the default.
+//
+// The kernel above keeps one Q/dO tile in flight and spends most of an iteration waiting (loads,
+// then MMAs, then the element-wise pass, then the dQ drain, one after the other).  This one works on
+// 64 queries per iteration and computes everything with the KEY index on the TMEM lane axis:
+//   S^T  = K  Q^T   (128 keys x 64 queries)        dP^T = V dO^T
+//   P^T  = exp2(S^T c - lse[q]),  dS^T = P^T (dP^T - delta[q]) scale      (bf16, K-major A tiles)
+//   dV  += P^T dO,  dK += dS^T Q                   (accumulate in TMEM over all iterations)
+//   dQ^T = K^T dS^T (128 dims x 64 queries)        -> transposed through shared memory and added to
+//                                                     the fp32 accumulator by bulk tensor reductions
+// so a 64-query tile is half the size (two Q/dO stages, two P^T/dS^T stages and the dQ staging
+// buffer fit beside K and V in 224 KB) and no operand needs a transpose.  The S^T/dP^T accumulators
+// are read into registers at once and released before the arithmetic, so the tensor core computes
+// iteration i+1's scores during iteration i's element-wise pass, and iteration i's dQ^T is drained
+// while iteration i+1's MMAs run.
+// TMEM (512 columns): dK 128 | dV 128 | S^T 64 | dP^T 64 | dQ^T 2 x 64.
+// CTAs are numbered heaviest first (key block 0 has the most query blocks below the diagonal).
+namespace bkt {
+using namespace bws;
+
+constexpr int QB = 64;  // queries per iteration
+
+// barrier over `nthreads` threads that also ORs a predicate: every participant gets the same answer,
+// so all compute threads leave the loop at the same barrier when one of them timed out
+__device__ __forceinline__ bool named_bar_or(int id, int nthreads, bool pred) {
+  uint32_t r;
+  asm volatile(
+      "{\n"
+      ".reg .pred p, q;\n"
+      "setp.ne.u32 p, %3, 0;\n"
+      "bar.red.or.pred q, %1, %2, p;\n"
+      "selp.u32 %0, 1, 0, q;\n"
+      "}\n"
+      : "=r"(r)
+      : "r"(id), "r"(nthreads), "r"((uint32_t)pred)
+      : "memory");
+  return r != 0;
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait0() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+__global__ void __launch_bounds__(320, 1) attn_bwd_kt_kernel(const __grid_constant__ CUtensorMap mapQ,
+                                                             const __grid_constant__ CUtensorMap mapK,
+                                                             const __grid_constant__ CUtensorMap mapV,
+                                                             const __grid_constant__ CUtensorMap mapdO,
+                                                             const __grid_constant__ CUtensorMap mapdQ,
+                                                             const BwdParams p, const int nkb) {
+  constexpr int D = 128;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sK = smem;                 // [128 keys x 128] bf16, two 64-column slabs of 16 KB
+  uint8_t* sV = smem + 32768;
+  uint8_t* sQ = smem + 65536;         // 2 stages x [64 queries x 128], two slabs of 8 KB each
+  uint8_t* sdO = smem + 98304;        // 2 stages
+  uint8_t* sP = smem + 131072;        // 2 stages x [128 keys x 64 queries] bf16 (one slab)
+  uint8_t* sdS = smem + 163840;       // 2 stages
+  uint8_t* sStage = smem + 196608;    // dQ staging: 4 slabs of [64 queries x 32 dims] fp32
+  __shared__ uint64_t kv_full, qdo_full[2], qdo_empty[2], sdp_full, sdp_empty, pds_full[2], pds_empty[2], dq_full[2],
+      dq_empty[2];
+  __shared__ uint32_t tmem_base;
+  __shared__ volatile int s_abort;
+  __shared__ __align__(16) float s_stat[2][128];  // per stage: lse * log2(e) of the 64 queries, then their delta
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int per_jb = p.Hkv * p.B;
+  const int jb = blockIdx.x / per_jb;
+  const int hk = (blockIdx.x % per_jb) % p.Hkv, b = (blockIdx.x % per_jb) / p.Hkv;
+  const int group = p.Hq / p.Hkv;
+  const int k0 = jb * 128;
+  const int nq64 = (p.S + QB - 1) / QB;
+  const int nqi = nq64 - 2 * jb;  // query blocks at or below this key block's diagonal
+  const int iters = group * nqi;
+  (void)nkb;
+  if (tid == 0) {
+    mbar_init(&kv_full, 1);
+    mbar_init(&sdp_full, 1);
+    mbar_init(&sdp_empty, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&qdo_full[i], 1);
+      mbar_init(&qdo_empty[i], 1);
+      mbar_init(&pds_full[i], 1);
+      mbar_init(&pds_empty[i], 1);
+      mbar_init(&dq_full[i], 1);
+      mbar_init(&dq_empty[i], 1);
+    }
+    mbar_fence_init();
+    s_abort = 0;
+  }
+  if (warp == 1) {
+    tmem_alloc(&tmem_base, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tm_dk = tmem_base, tm_dv = tmem_base + 128, tm_st = tmem_base + 256, tm_dp = tmem_base + 320,
+                 tm_dq = tmem_base + 384;
+
+  // bounded wait of the single-thread roles: also gives up when another role raised the abort flag
+  auto role_wait = [&](uint64_t* bar, uint32_t parity) -> bool {
+    if (mbar_try_wait(bar, parity)) return true;
+    const unsigned long long t0 = globaltimer_ns();
+    for (uint32_t it = 0;; ++it) {
+      __nanosleep(32);
+      if (mbar_try_wait(bar, parity)) return true;
+      if ((it & 63u) == 63u && (s_abort || globaltimer_ns() - t0 > 2000000000ull)) return false;
+    }
+  };
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_expect_tx(&kv_full, 2 * 32768);
+#pragma unroll
+      for (int sl = 0; sl < 2; ++sl) {
+        tma_load_4d(sK + sl * 16384, &mapK, &kv_full, sl * 64, hk, k0, b);
+        tma_load_4d(sV + sl * 16384, &mapV, &kv_full, sl * 64, hk, k0, b);
+      }
+      for (int i = 0; i < iters; ++i) {
+        const int st = i & 1;
+        const int h = hk * group + i / nqi;
+        const int q0 = (2 * jb + i % nqi) * QB;
+        if (!role_wait(&qdo_empty[st], ((i >> 1) & 1) ^ 1)) { s_abort = 1; break; }
+        mbar_expect_tx(&qdo_full[st], 2 * 16384);
+#pragma unroll
+        for (int sl = 0; sl < 2; ++sl) {
+          tma_load_4d(sQ + st * 16384 + sl * 8192, &mapQ, &qdo_full[st], sl * 64, h, q0, b);
+          tma_load_4d(sdO + st * 16384 + sl * 8192, &mapdO, &qdo_full[st], sl * 64, h, q0, b);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t id_st = idesc_bf16(128, QB, MAJOR_K, MAJOR_K);     // S^T, dP^T
+      const uint32_t id_kv = idesc_bf16(128, D, MAJOR_K, MAJOR_MN);     // dV, dK
+      const uint32_t id_dq = idesc_bf16(128, QB, MAJOR_MN, MAJOR_MN);   // dQ^T
+      const uint32_t aK = smem_u32(sK), aV = smem_u32(sV), aQ = smem_u32(sQ), adO = smem_u32(sdO), aP = smem_u32(sP),
+                     adS = smem_u32(sdS);
+      // K-major views: 128-row tile (slab stride 16 KB) and 64-row tile (slab stride 8 KB)
+      auto k128 = [](uint32_t base, int k) { return smem_desc(base + (k >> 2) * 16384 + (k & 3) * 32, 16, 1024); };
+      auto k64 = [](uint32_t base, int k) { return smem_desc(base + (k >> 2) * 8192 + (k & 3) * 32, 16, 1024); };
+      bool ok = role_wait(&kv_full, 0);
+      auto issue_sdp = [&](int i) -> bool {
+        const int st = i & 1;
+        if (!role_wait(&qdo_full[st], (i >> 1) & 1)) return false;
+        if (i > 0 && !role_wait(&sdp_empty, (i - 1) & 1)) return false;
+        tc_fence_after_sync();
+        const uint32_t q = aQ + st * 16384, d_o = adO + st * 16384;
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) mma_bf16(tm_st, k128(aK, k), k64(q, k), id_st, k != 0);
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) mma_bf16(tm_dp, k128(aV, k), k64(d_o, k), id_st, k != 0);
+        mma_commit(&sdp_full);
+        return true;
+      };
+      if (ok) ok = issue_sdp(0);
+      for (int i = 0; i < iters && ok; ++i) {
+        if (i + 1 < iters && !(ok = issue_sdp(i + 1))) break;
+        const int st = i & 1, ph = (i >> 1) & 1;
+        if (!(ok = role_wait(&pds_full[st], ph))) break;
+        if (!(ok = role_wait(&dq_empty[st], ph ^ 1))) break;
+        tc_fence_after_sync();
+        const uint32_t pT = aP + st * 16384, dsT = adS + st * 16384, q = aQ + st * 16384, d_o = adO + st * 16384;
+        // dV += P^T dO and dK += dS^T Q: A = [128 keys x 64 queries] K-major, B = [64 queries x 128] MN-major
+#pragma unroll
+        for (int k = 0; k < QB / 16; ++k)
+          mma_bf16(tm_dv, smem_desc(pT + k * 32, 16, 1024), smem_desc(d_o + k * 2048, 8192, 1024), id_kv, (i | k) != 0);
+#pragma unroll
+        for (int k = 0; k < QB / 16; ++k)
+          mma_bf16(tm_dk, smem_desc(dsT + k * 32, 16, 1024), smem_desc(q + k * 2048, 8192, 1024), id_kv, (i | k) != 0);
+        // dQ^T = K^T dS^T: A = K read MN-major (M = head dim), B = dS^T read MN-major (N = queries)
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+          mma_bf16(tm_dq + st * QB, smem_desc(aK + k * 2048, 16384, 1024), smem_desc(dsT + k * 2048, 8192, 1024), id_dq,
+                   k != 0);
+        mma_commit(&dq_full[st]);
+        mma_commit(&pds_empty[st]);
+        mma_commit(&qdo_empty[st]);
+      }
+      if (!ok) s_abort = 1;
+    }
+  } else {
+    const int ct = tid - 64;               // 0..255
+    const int quarter = warp & 3;          // TMEM lane quarter this warp may access
+    const int half = (warp - 2) >> 2;      // which 32 of the 64 query columns
+    const int r = quarter * 32 + lane;     // key row of the tile == TMEM lane (head dim index for dQ^T)
+    const int key = k0 + r;
+    const uint32_t lane_base = (uint32_t)(quarter * 32);
+    const int c0 = half * 32;
+    const float sl2 = p.scale * LOG2E;
+    // threads 0..63 fetch lse, 64..127 fetch delta of the next iteration's queries (one value each)
+    auto fetch = [&](int i) -> float {
+      if (ct >= 128 || i >= iters) return 0.f;
+      const int h = hk * group + i / nqi;
+      const int q = (2 * jb + i % nqi) * QB + (ct & 63);
+      if (q >= p.S) return 0.f;
+      const int64_t idx = ((int64_t)b * p.Hq + h) * p.S + q;
+      return ct < 64 ? __ldg(p.lse + idx) * LOG2E : __ldg(p.delta + idx);
+    };
+    float pre = fetch(0);
+    bool fail = false, aborted = false;
+    for (int i = 0; i <= iters; ++i) {
+      if (i < iters) {
+        const int st = i & 1, ph = (i >> 1) & 1;
+        // ---- A: scores and dP of this thread's key row into registers, then release the accumulators
+        if (!mbar_wait(&sdp_full, i & 1)) fail = true;
+        tc_fence_after_sync();
+        uint32_t rs[32], rp[32];
+        tmem_ld32(tmem_addr(tm_st, lane_base, c0), rs);
+        tmem_ld32(tmem_addr(tm_dp, lane_base, c0), rp);
+        if (ct < 128) s_stat[st][ct] = pre;
+        if (tid == 64) bulk_wait_read0();  // the previous dQ reduction has read the staging buffer
+        __syncwarp();
+        tmem_ld_wait();
+        tc_fence_before_sync();
+        if (named_bar_or(1, 256, fail || s_abort)) { aborted = true; break; }
+        if (tid == 64) mbar_arrive(&sdp_empty);
+        __syncwarp();
+        pre = fetch(i + 1);
+        // ---- B: P^T and dS^T ------------------------------------------------------------------
+        const int q0 = (2 * jb + i % nqi) * QB;
+        const bool diag = (q0 < k0 + 128) || (q0 + QB > p.S) || (k0 + 128 > p.S);
+        const float4* st_l = reinterpret_cast<const float4*>(&s_stat[st][c0]);
+        const float4* st_d = reinterpret_cast<const float4*>(&s_stat[st][64 + c0]);
+        uint32_t pk[16], dk_[16];
+#pragma unroll
+        for (int g = 0; g < 8; ++g) {
+          const float4 l4 = st_l[g], d4 = st_d[g];
+          const float ls[4] = {l4.x, l4.y, l4.z, l4.w};
+          const float dl[4] = {d4.x, d4.y, d4.z, d4.w};
+          float e[4], ds[4];
+#pragma unroll
+          for (int t = 0; t < 4; ++t) {
+            const int c = g * 4 + t;
+            float ev = exp2f(__uint_as_float(rs[c]) * sl2 - ls[t]);
+            if (diag) {
+              const int q = q0 + c0 + c;
+              if (key > q || key >= p.S || q >= p.S) ev = 0.f;
+            }
+            e[t] = ev;
+            ds[t] = ev * (__uint_as_float(rp[c]) - dl[t]) * p.scale;
+          }
+          pk[2 * g] = pack_bf16(e[0], e[1]);
+          pk[2 * g + 1] = pack_bf16(e[2], e[3]);
+          dk_[2 * g] = pack_bf16(ds[0], ds[1]);
+          dk_[2 * g + 1] = pack_bf16(ds[2], ds[3]);
+        }
+        if (!mbar_wait(&pds_empty[st], ph ^ 1)) fail = true;  // MMAs of iteration i-2 have read this stage
+        uint8_t* tp = sP + st * 16384;
+        uint8_t* td = sdS + st * 16384;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          *reinterpret_cast<uint4*>(tp + sw128_off(r, half * 4 + j)) =
+              make_uint4(pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]);
+          *reinterpret_cast<uint4*>(td + sw128_off(r, half * 4 + j)) =
+              make_uint4(dk_[4 * j], dk_[4 * j + 1], dk_[4 * j + 2], dk_[4 * j + 3]);
+        }
+        fence_proxy_async_smem();
+        if (named_bar_or(2, 256, fail || s_abort)) { aborted = true; break; }
+        if (tid == 64) mbar_arrive(&pds_full[st]);
+        __syncwarp();
+      } else {
+        if (tid == 64) bulk_wait_read0();
+        __syncwarp();
+        if (named_bar_or(1, 256, fail || s_abort)) { aborted = true; break; }
+      }
+      if (i > 0) {
+        // ---- C: drain dQ^T of iteration i-1 (its MMAs ran during this iteration's phases A and B)
+        const int j = i - 1, sj = j & 1;
+        if (!mbar_wait(&dq_full[sj], (j >> 1) & 1)) fail = true;
+        tc_fence_after_sync();
+        uint32_t rr[32];
+        tmem_ld32(tmem_addr(tm_dq + sj * QB, lane_base, c0), rr);
+        tmem_ld_wait();
+        // this thread holds dQ^T[dim r][query c0 + t]; slab `quarter` of the staging buffer is
+        // [64 queries][32 dims] fp32, so a warp writes 32 consecutive floats per query
+        float* slab = reinterpret_cast<float*>(sStage + quarter * 8192);
+#pragma unroll
+        for (int t = 0; t < 32; ++t) slab[(c0 + t) * 32 + lane] = __uint_as_float(rr[t]);
+        fence_proxy_async_smem();
+        tc_fence_before_sync();
+        if (named_bar_or(3, 256, fail || s_abort)) { aborted = true; break; }
+        if (tid == 64) {
+          const int hj = hk * group + j / nqi;
+          const int qj = (2 * jb + j % nqi) * QB;
+#pragma unroll
+          for (int t = 0; t < 4; ++t) tma_reduce_add_4d(&mapdQ, sStage + t * 8192, t * 32, hj, qj, b);
+          bulk_commit();
+          mbar_arrive(&dq_empty[sj]);
+        }
+        __syncwarp();
+      }
+    }
+    if (tid == 64) bulk_wait0();
+    __syncwarp();
+    if (aborted) s_abort = 1;
+    if (!aborted) {
+      // every MMA into dK / dV has completed: dq_full of the last iteration was committed after them
+#pragma unroll 1
+      for (int which = 0; which < 2; ++which) {
+        const uint32_t tmx = which ? tm_dv : tm_dk;
+        __nv_bfloat16* dst = which ? p.dv + b * p.dvs0 + (int64_t)key * p.dvs1 + hk * p.dvs2
+                                   : p.dk + b * p.dks0 + (int64_t)key * p.dks1 + hk * p.dks2;
+#pragma unroll 1
+        for (int c = half * 64; c < half * 64 + 64; c += 32) {
+          uint32_t rr[32];
+          tmem_ld32(tmem_addr(tmx, lane_base, c), rr);
+          tmem_ld_wait();
+          if (key < p.S) {
+#pragma unroll
+            for (int i = 0; i < 32; i += 8) {
+              uint4 u;
+              u.x = pack_bf16(__uint_as_float(rr[i]), __uint_as_float(rr[i + 1]));
+              u.y = pack_bf16(__uint_as_float(rr[i + 2]), __uint_as_float(rr[i + 3]));
+              u.z = pack_bf16(__uint_as_float(rr[i + 4]), __uint_as_float(rr[i + 5]));
+              u.w = pack_bf16(__uint_as_float(rr[i + 6]), __uint_as_float(rr[i + 7]));
+              *reinterpret_cast<uint4*>(dst + c + i) = u;
+            }
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (tid == 0 && s_abort) atomicExch(p.status, 6);
+  if (warp == 1) tmem_dealloc(tmem_base, 512);
+}
+
+}  // namespace bkt
 }  // namespace zc
 
 extern "C" {
@@ -451,6 +789,64 @@ int zc_attn_bwd_ws(const void* q, const void* k, const void* v, const void* o, c
     if (!attr[1]) { cudaFuncSetAttribute(attn_bwd_ws_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); attr[1] = true; }
     attn_bwd_ws_kernel<64><<<grid, 320, smem, st>>>(mq, mk, mv, mdo, mdq, p);
   }
+  const int cgrid = (int)std::min<int64_t>((rows * (D / 4) + 255) / 256, (int64_t)sm_count() * 16);
+  dq_convert_kernel<<<cgrid, 256, 0, st>>>(sc.dq_acc, (__nv_bfloat16*)dq, (int64_t)B * S, Hq, D, dqs1, dqs2);
+  return launch_status();
+}
+
+// Same argument list as zc_attn_bwd.  Head dimension 128 runs the key-row kernel; 64 falls back to
+// zc_attn_bwd_ws.
+int zc_attn_bwd_kt(const void* q, const void* k, const void* v, const void* o, const void* dout, const float* lse,
+                   float* delta, void* dq, void* dk, void* dv, int B, int S, int Hq, int Hkv, int D, int64_t qs0,
+                   int64_t qs1, int64_t qs2, int64_t ks0, int64_t ks1, int64_t ks2, int64_t vs0, int64_t vs1,
+                   int64_t vs2, int64_t dqs0, int64_t dqs1, int64_t dqs2, int64_t dks0, int64_t dks1, int64_t dks2,
+                   int64_t dvs0, int64_t dvs1, int64_t dvs2, float scale, cudaStream_t st) {
+  using namespace zc;
+  using namespace zc::bws;
+  if (D != 128)
+    return zc_attn_bwd_ws(q, k, v, o, dout, lse, delta, dq, dk, dv, B, S, Hq, Hkv, D, qs0, qs1, qs2, ks0, ks1, ks2, vs0,
+                          vs1, vs2, dqs0, dqs1, dqs2, dks0, dks1, dks2, dvs0, dvs1, dvs2, scale, st);
+  if (Hq % Hkv) return ERR_UNSUPPORTED;
+  if ((qs1 | qs2 | ks1 | ks2 | vs1 | vs2 | qs0 | ks0 | vs0 | dqs1 | dqs2 | dks1 | dks2 | dvs1 | dvs2 | dqs0 | dks0 | dvs0) % 8)
+    return ERR_UNSUPPORTED;
+  if (dqs0 != (int64_t)S * dqs1) return ERR_UNSUPPORTED;
+  if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) |
+       reinterpret_cast<uintptr_t>(dout)) & 15)
+    return ERR_UNSUPPORTED;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  cudaSetDevice(dev);
+  Scratch& sc = g_scratch[dev];
+  if (!sc.status) {
+    if (cudaMalloc(&sc.status, sizeof(int)) != cudaSuccess) return ERR_BAD_ARG;
+    cudaMemset(sc.status, 0, sizeof(int));
+  }
+  const size_t need = (size_t)B * S * Hq * D * sizeof(float);
+  if (sc.dq_bytes < need) {
+    if (sc.dq_acc) cudaFreeAsync(sc.dq_acc, st);
+    if (cudaMallocAsync(&sc.dq_acc, need, st) != cudaSuccess) { sc.dq_acc = nullptr; sc.dq_bytes = 0; return (int)cudaGetLastError(); }
+    sc.dq_bytes = need;
+  }
+  cudaMemsetAsync(sc.dq_acc, 0, need, st);
+  CUtensorMap mq, mk, mv, mdo, mdq;
+  if (!make_map4(&mq, q, D, Hq, S, B, qs0, qs1, qs2, bkt::QB) || !make_map4(&mk, k, D, Hkv, S, B, ks0, ks1, ks2) ||
+      !make_map4(&mv, v, D, Hkv, S, B, vs0, vs1, vs2) ||
+      !make_map4(&mdo, dout, D, Hq, S, B, (int64_t)S * Hq * D, (int64_t)Hq * D, D, bkt::QB) ||
+      !make_map4_f32(&mdq, sc.dq_acc, D, Hq, S, B, bkt::QB, false))
+    return ERR_BAD_ARG;
+  BwdParams p;
+  p.lse = lse; p.delta = delta; p.dq_acc = sc.dq_acc; p.dk = (__nv_bfloat16*)dk; p.dv = (__nv_bfloat16*)dv;
+  p.B = B; p.S = S; p.Hq = Hq; p.Hkv = Hkv;
+  p.dks0 = dks0; p.dks1 = dks1; p.dks2 = dks2; p.dvs0 = dvs0; p.dvs1 = dvs1; p.dvs2 = dvs2;
+  p.scale = scale; p.status = sc.status;
+  const int64_t rows = (int64_t)B * S * Hq;
+  delta_kernel<<<(unsigned)((rows * 32 + 255) / 256), 256, 0, st>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)dout,
+                                                                   delta, B, S, Hq, D);
+  const int smem = 7 * 32768 + 1024;
+  static bool attr = false;
+  if (!attr) { cudaFuncSetAttribute(bkt::attn_bwd_kt_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); attr = true; }
+  const int nkb = (S + 127) / 128;
+  bkt::attn_bwd_kt_kernel<<<nkb * Hkv * B, 320, smem, st>>>(mq, mk, mv, mdo, mdq, p, nkb);
   const int cgrid = (int)std::min<int64_t>((rows * (D / 4) + 255) / 256, (int64_t)sm_count() * 16);
   dq_convert_kernel<<<cgrid, 256, 0, st>>>(sc.dq_acc, (__nv_bfloat16*)dq, (int64_t)B * S, Hq, D, dqs1, dqs2);
   return launch_status();

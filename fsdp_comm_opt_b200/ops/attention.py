@@ -3,9 +3,9 @@
 Layout: one packed projection ``[B, S, Hq + 2*Hkv, D]`` (q heads, then k heads, then v heads),
 output ``[B, S, Hq, D]`` contiguous; the backward returns one packed gradient of the same shape,
 so the qkv projection's backward reads it without a concatenation.
-CUDA tensors run the sm_100a flash-style kernels (``zc_attn_fwd`` / ``zc_attn_bwd``: online
-softmax, log-sum-exp saved for the backward, no S x S tensor in memory); CPU tensors run fp32
-matmul/softmax.  The reference reaches PyTorch SDPA through HF attention modules.
+CUDA tensors run the sm_100a flash-style kernels (``zc_attn_fwd_2q`` / ``zc_attn_bwd_kt`` for head
+dimension 128, ``zc_attn_fwd_ws`` / ``zc_attn_bwd_ws`` for 64: online softmax, log-sum-exp saved for
+the backward, no S x S tensor in memory); CPU tensors run fp32 matmul/softmax.  The reference reaches PyTorch SDPA through HF attention modules.
 """
 from __future__ import annotations
 
@@ -17,8 +17,8 @@ import torch
 from .. import _lib
 
 
-_FWD_IMPL = os.environ.get("ZC_ATTN_FWD", "ws")
-_BWD_IMPL = os.environ.get("ZC_ATTN_BWD", "ws")
+_FWD_IMPL = os.environ.get("ZC_ATTN_FWD", "2q")
+_BWD_IMPL = os.environ.get("ZC_ATTN_BWD", "kt")
 
 
 def status_read_and_clear() -> int:
@@ -26,7 +26,7 @@ def status_read_and_clear() -> int:
     (synchronises the device)."""
     lib = _lib.cuda()
     return (int(lib.zc_attn_status_read_and_clear()) | int(lib.zc_attn_ws_status_read_and_clear())
-            | int(lib.zc_attn_bwd_ws_status_read_and_clear()))
+            | int(lib.zc_attn_bwd_ws_status_read_and_clear()) | int(lib.zc_attn_fwd_2q_status_read_and_clear()))
 
 
 def _strides(t):
@@ -76,8 +76,9 @@ class _Attention(torch.autograd.Function):
         o = torch.empty(B, S, Hq, D, dtype=qkv.dtype, device=qkv.device)
         lse = torch.empty(B, Hq, S, dtype=torch.float32, device=qkv.device)
         lib = _lib.cuda()
-        # default: warp-specialised TMA-fed kernel; ZC_ATTN_FWD=simple selects the single-role kernel
-        fwd = lib.zc_attn_fwd if _FWD_IMPL == "simple" else lib.zc_attn_fwd_ws
+        # default: two query tiles per CTA, one softmax thread per row; ZC_ATTN_FWD=ws / simple select
+        # the earlier warp-specialised and single-role kernels
+        fwd = {"simple": lib.zc_attn_fwd, "ws": lib.zc_attn_fwd_ws}.get(_FWD_IMPL, lib.zc_attn_fwd_2q)
         _lib.check(fwd(
             q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(), B, S, Hq, Hkv, D,
             *_strides(q), *_strides(k), *_strides(v), float(scale), _lib.stream_ptr(qkv.device)),
@@ -102,7 +103,9 @@ class _Attention(torch.autograd.Function):
         dq, dk, dv = dqkv[:, :, :Hq], dqkv[:, :, Hq:Hq + Hkv], dqkv[:, :, Hq + Hkv:]
         delta = torch.empty(B, Hq, S, dtype=torch.float32, device=qkv.device)
         lib = _lib.cuda()
-        bwd = lib.zc_attn_bwd if _BWD_IMPL == "simple" else lib.zc_attn_bwd_ws
+        # default: key-row kernel (64-query iterations, pipelined); ZC_ATTN_BWD=ws / simple select
+        # the earlier warp-specialised and single-role kernels
+        bwd = {"simple": lib.zc_attn_bwd, "ws": lib.zc_attn_bwd_ws}.get(_BWD_IMPL, lib.zc_attn_bwd_kt)
         _lib.check(bwd(
             q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), do.data_ptr(), lse.data_ptr(),
             delta.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), B, S, Hq, Hkv, D,

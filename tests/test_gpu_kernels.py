@@ -294,8 +294,13 @@ def _attn_ref(qkv, Hq, Hkv):
     return F.scaled_dot_product_attention(q, k, v, is_causal=True).transpose(1, 2)
 
 
-@pytest.mark.parametrize("B,S,Hq,Hkv,D", [(1, 128, 1, 1, 128), (2, 384, 4, 2, 128), (1, 200, 2, 2, 64), (1, 512, 8, 2, 128)])
-def test_attention_fwd_bwd(B, S, Hq, Hkv, D):
+@pytest.mark.parametrize("impl", ["2q+kt", "ws+ws", "simple+simple"])
+@pytest.mark.parametrize("B,S,Hq,Hkv,D", [(1, 128, 1, 1, 128), (2, 384, 4, 2, 128), (1, 200, 2, 2, 64), (1, 512, 8, 2, 128),
+                                          (1, 1000, 4, 1, 128), (2, 2048, 8, 2, 128)])
+def test_attention_fwd_bwd(B, S, Hq, Hkv, D, impl, monkeypatch):
+    fwd_impl, bwd_impl = impl.split("+")
+    monkeypatch.setattr(attention, "_FWD_IMPL", fwd_impl)
+    monkeypatch.setattr(attention, "_BWD_IMPL", bwd_impl)
     torch.manual_seed(7)
     qkv = (torch.randn(B, S, Hq + 2 * Hkv, D, device=DEV) * 0.5).bfloat16().requires_grad_()
     o = attention.causal_attention(qkv * 1, Hq, Hkv)
@@ -309,6 +314,34 @@ def test_attention_fwd_bwd(B, S, Hq, Hkv, D):
     assert torch.allclose(o.float(), ref, atol=2e-2, rtol=2e-2), (o.float() - ref).abs().max().item()
     err = (qkv.grad.float() - qf.grad).abs().max().item()
     assert torch.allclose(qkv.grad.float(), qf.grad, atol=3e-2, rtol=3e-2), err
+
+
+@pytest.mark.parametrize("impl", ["2q+kt", "ws+ws"])
+def test_attention_rising_scores_rescale_the_accumulator(impl, monkeypatch):
+    """Keys whose scores grow along the sequence raise the running row maximum again and again, so
+    the forward kernel must rescale the output it has accumulated so far (the two-tile kernel does
+    that in TMEM, and only when the maximum rose by more than a factor of 2^8)."""
+    fwd_impl, bwd_impl = impl.split("+")
+    monkeypatch.setattr(attention, "_FWD_IMPL", fwd_impl)
+    monkeypatch.setattr(attention, "_BWD_IMPL", bwd_impl)
+    torch.manual_seed(11)
+    B, S, Hq, Hkv, D = 1, 1024, 2, 1, 128
+    qkv = torch.randn(B, S, Hq + 2 * Hkv, D, device=DEV) * 0.5
+    # q = +1 everywhere, k ramps from -3 to +3: scores rise by ~70 (in log2 units ~100) over the row
+    qkv[:, :, :Hq] = 1.0 + 0.05 * torch.randn(B, S, Hq, D, device=DEV)
+    ramp = torch.linspace(-3.0, 3.0, S, device=DEV)[None, :, None, None]
+    qkv[:, :, Hq:Hq + Hkv] = ramp + 0.05 * torch.randn(B, S, Hkv, D, device=DEV)
+    qkv = qkv.bfloat16().requires_grad_()
+    o = attention.causal_attention(qkv * 1, Hq, Hkv)
+    g = torch.randn_like(o) * 0.5
+    o.backward(g)
+    torch.cuda.synchronize()
+    assert attention.status_read_and_clear() == 0
+    qf = qkv.detach().float().requires_grad_()
+    ref = _attn_ref(qf, Hq, Hkv)
+    ref.backward(g.float())
+    assert torch.allclose(o.float(), ref, atol=3e-2, rtol=3e-2), (o.float() - ref).abs().max().item()
+    assert torch.allclose(qkv.grad.float(), qf.grad, atol=5e-2, rtol=5e-2), (qkv.grad.float() - qf.grad).abs().max().item()
 
 
 def test_attention_with_fused_rope_matches_unfused():
