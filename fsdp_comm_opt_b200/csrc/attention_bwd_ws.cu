@@ -80,6 +80,7 @@ struct BwdParams {
   int64_t dks0, dks1, dks2, dvs0, dvs1, dvs2;
   float scale;
   int* status;
+  long long* trace;  // null, or [3][256][8] SM-clock stamps written by CTA 0 of the key-row kernel
 };
 
 template <int D>
@@ -342,6 +343,7 @@ struct Scratch {
   size_t dq_bytes = 0;
 };
 static Scratch g_scratch[64];
+static long long* g_trace = nullptr;
 
 __global__ void __launch_bounds__(256) delta_kernel(const __nv_bfloat16* __restrict__ o,
                                                     const __nv_bfloat16* __restrict__ dout, float* __restrict__ delta,
@@ -407,6 +409,11 @@ __global__ void __launch_bounds__(256) dq_convert_kernel(const float* __restrict
 namespace bkt {
 using namespace bws;
 
+#define ZC_BTRACE(slot, i, k)                                                                      \
+  do {                                                                                             \
+    if (p.trace && blockIdx.x == 0 && (i) < 256) p.trace[((slot) * 256 + (i)) * 8 + (k)] = clock64(); \
+  } while (0)
+
 constexpr int QB = 64;  // queries per iteration
 
 // barrier over `nthreads` threads that also ORs a predicate: every participant gets the same answer,
@@ -433,7 +440,7 @@ __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
-__global__ void __launch_bounds__(320, 1) attn_bwd_kt_kernel(const __grid_constant__ CUtensorMap mapQ,
+__global__ void __launch_bounds__(352, 1) attn_bwd_kt_kernel(const __grid_constant__ CUtensorMap mapQ,
                                                              const __grid_constant__ CUtensorMap mapK,
                                                              const __grid_constant__ CUtensorMap mapV,
                                                              const __grid_constant__ CUtensorMap mapdO,
@@ -453,7 +460,7 @@ __global__ void __launch_bounds__(320, 1) attn_bwd_kt_kernel(const __grid_consta
       dq_empty[2];
   __shared__ uint32_t tmem_base;
   __shared__ volatile int s_abort;
-  __shared__ __align__(16) float s_stat[2][128];  // per stage: lse * log2(e) of the 64 queries, then their delta
+  __shared__ __align__(16) float s_stat[2][128];  // per stage: lse * log2(e) of the 64 queries, then their delta * scale
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int per_jb = p.Hkv * p.B;
   const int jb = blockIdx.x / per_jb;
@@ -489,16 +496,9 @@ __global__ void __launch_bounds__(320, 1) attn_bwd_kt_kernel(const __grid_consta
   const uint32_t tm_dk = tmem_base, tm_dv = tmem_base + 128, tm_st = tmem_base + 256, tm_dp = tmem_base + 320,
                  tm_dq = tmem_base + 384;
 
-  // bounded wait of the single-thread roles: also gives up when another role raised the abort flag
-  auto role_wait = [&](uint64_t* bar, uint32_t parity) -> bool {
-    if (mbar_try_wait(bar, parity)) return true;
-    const unsigned long long t0 = globaltimer_ns();
-    for (uint32_t it = 0;; ++it) {
-      __nanosleep(32);
-      if (mbar_try_wait(bar, parity)) return true;
-      if ((it & 63u) == 63u && (s_abort || globaltimer_ns() - t0 > 2000000000ull)) return false;
-    }
-  };
+  // bounded wait of the single-thread roles: parked in hardware, woken when the phase completes,
+  // given up after two seconds or when another role raised the abort flag
+  auto role_wait = [&](uint64_t* bar, uint32_t parity) -> bool { return mbar_wait_parked(bar, parity, &s_abort); };
 
   if (warp == 0) {
     if (lane == 0) {
@@ -521,7 +521,7 @@ __global__ void __launch_bounds__(320, 1) attn_bwd_kt_kernel(const __grid_consta
         }
       }
     }
-  } else if (warp == 1) {
+  } else if (warp == 1 || warp == 10) {
     if (lane == 0) {
       const uint32_t id_st = idesc_bf16(128, QB, MAJOR_K, MAJOR_K);     // S^T, dP^T
       const uint32_t id_kv = idesc_bf16(128, D, MAJOR_K, MAJOR_MN);     // dV, dK
@@ -532,42 +532,54 @@ __global__ void __launch_bounds__(320, 1) attn_bwd_kt_kernel(const __grid_consta
       auto k128 = [](uint32_t base, int k) { return smem_desc(base + (k >> 2) * 16384 + (k & 3) * 32, 16, 1024); };
       auto k64 = [](uint32_t base, int k) { return smem_desc(base + (k >> 2) * 8192 + (k & 3) * 32, 16, 1024); };
       bool ok = role_wait(&kv_full, 0);
-      auto issue_sdp = [&](int i) -> bool {
-        const int st = i & 1;
-        if (!role_wait(&qdo_full[st], (i >> 1) & 1)) return false;
-        if (i > 0 && !role_wait(&sdp_empty, (i - 1) & 1)) return false;
-        tc_fence_after_sync();
-        const uint32_t q = aQ + st * 16384, d_o = adO + st * 16384;
+      // Two issuers: a tcgen05.mma takes about a hundred cycles to issue whatever its width, so the
+      // 32 MMAs of an iteration are split between warp 1 (S^T, dP^T) and warp 10 (dV, dK, dQ^T).
+      if (warp == 1) {
+        for (int i = 0; i < iters && ok; ++i) {
+          const int st = i & 1;
+          ZC_BTRACE(1, i, 0);
+          if (!(ok = role_wait(&qdo_full[st], (i >> 1) & 1))) break;
+          ZC_BTRACE(1, i, 1);
+          if (i > 0 && !(ok = role_wait(&sdp_empty, (i - 1) & 1))) break;
+          tc_fence_after_sync();
+          ZC_BTRACE(1, i, 2);
+          const uint32_t q = aQ + st * 16384, d_o = adO + st * 16384;
 #pragma unroll
-        for (int k = 0; k < D / 16; ++k) mma_bf16(tm_st, k128(aK, k), k64(q, k), id_st, k != 0);
+          for (int k = 0; k < D / 16; ++k) mma_bf16(tm_st, k128(aK, k), k64(q, k), id_st, k != 0);
 #pragma unroll
-        for (int k = 0; k < D / 16; ++k) mma_bf16(tm_dp, k128(aV, k), k64(d_o, k), id_st, k != 0);
-        mma_commit(&sdp_full);
-        return true;
-      };
-      if (ok) ok = issue_sdp(0);
-      for (int i = 0; i < iters && ok; ++i) {
-        if (i + 1 < iters && !(ok = issue_sdp(i + 1))) break;
-        const int st = i & 1, ph = (i >> 1) & 1;
-        if (!(ok = role_wait(&pds_full[st], ph))) break;
-        if (!(ok = role_wait(&dq_empty[st], ph ^ 1))) break;
-        tc_fence_after_sync();
-        const uint32_t pT = aP + st * 16384, dsT = adS + st * 16384, q = aQ + st * 16384, d_o = adO + st * 16384;
-        // dV += P^T dO and dK += dS^T Q: A = [128 keys x 64 queries] K-major, B = [64 queries x 128] MN-major
+          for (int k = 0; k < D / 16; ++k) mma_bf16(tm_dp, k128(aV, k), k64(d_o, k), id_st, k != 0);
+          mma_commit(&sdp_full);
+          ZC_BTRACE(1, i, 3);
+        }
+      } else {
+        for (int i = 0; i < iters && ok; ++i) {
+          const int st = i & 1, ph = (i >> 1) & 1;
+          // pds_full(i) also tells that S^T(i) and dP^T(i) have completed (the compute threads read
+          // them before writing P^T and dS^T), so this thread's commits cover every reader of Q/dO
+          ZC_BTRACE(2, i, 0);
+          if (!(ok = role_wait(&pds_full[st], ph))) break;
+          ZC_BTRACE(2, i, 1);
+          if (!(ok = role_wait(&dq_empty[st], ph ^ 1))) break;
+          tc_fence_after_sync();
+          ZC_BTRACE(2, i, 2);
+          const uint32_t pT = aP + st * 16384, dsT = adS + st * 16384, q = aQ + st * 16384, d_o = adO + st * 16384;
+          // dV += P^T dO and dK += dS^T Q: A = [128 keys x 64 queries] K-major, B = [64 queries x 128] MN-major
 #pragma unroll
-        for (int k = 0; k < QB / 16; ++k)
-          mma_bf16(tm_dv, smem_desc(pT + k * 32, 16, 1024), smem_desc(d_o + k * 2048, 8192, 1024), id_kv, (i | k) != 0);
+          for (int k = 0; k < QB / 16; ++k)
+            mma_bf16(tm_dv, smem_desc(pT + k * 32, 16, 1024), smem_desc(d_o + k * 2048, 8192, 1024), id_kv, (i | k) != 0);
 #pragma unroll
-        for (int k = 0; k < QB / 16; ++k)
-          mma_bf16(tm_dk, smem_desc(dsT + k * 32, 16, 1024), smem_desc(q + k * 2048, 8192, 1024), id_kv, (i | k) != 0);
-        // dQ^T = K^T dS^T: A = K read MN-major (M = head dim), B = dS^T read MN-major (N = queries)
+          for (int k = 0; k < QB / 16; ++k)
+            mma_bf16(tm_dk, smem_desc(dsT + k * 32, 16, 1024), smem_desc(q + k * 2048, 8192, 1024), id_kv, (i | k) != 0);
+          // dQ^T = K^T dS^T: A = K read MN-major (M = head dim), B = dS^T read MN-major (N = queries)
 #pragma unroll
-        for (int k = 0; k < 8; ++k)
-          mma_bf16(tm_dq + st * QB, smem_desc(aK + k * 2048, 16384, 1024), smem_desc(dsT + k * 2048, 8192, 1024), id_dq,
-                   k != 0);
-        mma_commit(&dq_full[st]);
-        mma_commit(&pds_empty[st]);
-        mma_commit(&qdo_empty[st]);
+          for (int k = 0; k < 8; ++k)
+            mma_bf16(tm_dq + st * QB, smem_desc(aK + k * 2048, 16384, 1024), smem_desc(dsT + k * 2048, 8192, 1024), id_dq,
+                     k != 0);
+          mma_commit(&dq_full[st]);
+          mma_commit(&pds_empty[st]);
+          mma_commit(&qdo_empty[st]);
+          ZC_BTRACE(2, i, 3);
+        }
       }
       if (!ok) s_abort = 1;
     }
@@ -587,7 +599,7 @@ __global__ void __launch_bounds__(320, 1) attn_bwd_kt_kernel(const __grid_consta
       const int q = (2 * jb + i % nqi) * QB + (ct & 63);
       if (q >= p.S) return 0.f;
       const int64_t idx = ((int64_t)b * p.Hq + h) * p.S + q;
-      return ct < 64 ? __ldg(p.lse + idx) * LOG2E : __ldg(p.delta + idx);
+      return ct < 64 ? __ldg(p.lse + idx) * LOG2E : __ldg(p.delta + idx) * p.scale;
     };
     float pre = fetch(0);
     bool fail = false, aborted = false;
@@ -595,19 +607,20 @@ __global__ void __launch_bounds__(320, 1) attn_bwd_kt_kernel(const __grid_consta
       if (i < iters) {
         const int st = i & 1, ph = (i >> 1) & 1;
         // ---- A: scores and dP of this thread's key row into registers, then release the accumulators
-        if (!mbar_wait(&sdp_full, i & 1)) fail = true;
+        if (tid == 64) ZC_BTRACE(0, i, 0);
+        if (!mbar_wait_parked(&sdp_full, i & 1, &s_abort)) fail = true;
         tc_fence_after_sync();
+        if (tid == 64) ZC_BTRACE(0, i, 1);
         uint32_t rs[32], rp[32];
         tmem_ld32(tmem_addr(tm_st, lane_base, c0), rs);
         tmem_ld32(tmem_addr(tm_dp, lane_base, c0), rp);
         if (ct < 128) s_stat[st][ct] = pre;
-        if (tid == 64) bulk_wait_read0();  // the previous dQ reduction has read the staging buffer
-        __syncwarp();
         tmem_ld_wait();
         tc_fence_before_sync();
         if (named_bar_or(1, 256, fail || s_abort)) { aborted = true; break; }
         if (tid == 64) mbar_arrive(&sdp_empty);
         __syncwarp();
+        if (tid == 64) ZC_BTRACE(0, i, 2);
         pre = fetch(i + 1);
         // ---- B: P^T and dS^T ------------------------------------------------------------------
         const int q0 = (2 * jb + i % nqi) * QB;
@@ -630,14 +643,16 @@ __global__ void __launch_bounds__(320, 1) attn_bwd_kt_kernel(const __grid_consta
               if (key > q || key >= p.S || q >= p.S) ev = 0.f;
             }
             e[t] = ev;
-            ds[t] = ev * (__uint_as_float(rp[c]) - dl[t]) * p.scale;
+            ds[t] = ev * fmaf(__uint_as_float(rp[c]), p.scale, -dl[t]);
           }
           pk[2 * g] = pack_bf16(e[0], e[1]);
           pk[2 * g + 1] = pack_bf16(e[2], e[3]);
           dk_[2 * g] = pack_bf16(ds[0], ds[1]);
           dk_[2 * g + 1] = pack_bf16(ds[2], ds[3]);
         }
-        if (!mbar_wait(&pds_empty[st], ph ^ 1)) fail = true;  // MMAs of iteration i-2 have read this stage
+        if (tid == 64) ZC_BTRACE(0, i, 3);
+        if (!mbar_wait_parked(&pds_empty[st], ph ^ 1, &s_abort)) fail = true;  // MMAs of iteration i-2 have read this stage
+        if (tid == 64) ZC_BTRACE(0, i, 4);
         uint8_t* tp = sP + st * 16384;
         uint8_t* td = sdS + st * 16384;
 #pragma unroll
@@ -648,9 +663,12 @@ __global__ void __launch_bounds__(320, 1) attn_bwd_kt_kernel(const __grid_consta
               make_uint4(dk_[4 * j], dk_[4 * j + 1], dk_[4 * j + 2], dk_[4 * j + 3]);
         }
         fence_proxy_async_smem();
+        if (tid == 64) bulk_wait_read0();  // the previous dQ reduction has read the staging buffer
+        __syncwarp();
         if (named_bar_or(2, 256, fail || s_abort)) { aborted = true; break; }
         if (tid == 64) mbar_arrive(&pds_full[st]);
         __syncwarp();
+        if (tid == 64) ZC_BTRACE(0, i, 5);
       } else {
         if (tid == 64) bulk_wait_read0();
         __syncwarp();
@@ -659,8 +677,9 @@ __global__ void __launch_bounds__(320, 1) attn_bwd_kt_kernel(const __grid_consta
       if (i > 0) {
         // ---- C: drain dQ^T of iteration i-1 (its MMAs ran during this iteration's phases A and B)
         const int j = i - 1, sj = j & 1;
-        if (!mbar_wait(&dq_full[sj], (j >> 1) & 1)) fail = true;
+        if (!mbar_wait_parked(&dq_full[sj], (j >> 1) & 1, &s_abort)) fail = true;
         tc_fence_after_sync();
+        if (tid == 64) ZC_BTRACE(0, i, 6);
         uint32_t rr[32];
         tmem_ld32(tmem_addr(tm_dq + sj * QB, lane_base, c0), rr);
         tmem_ld_wait();
@@ -679,6 +698,7 @@ __global__ void __launch_bounds__(320, 1) attn_bwd_kt_kernel(const __grid_consta
           for (int t = 0; t < 4; ++t) tma_reduce_add_4d(&mapdQ, sStage + t * 8192, t * 32, hj, qj, b);
           bulk_commit();
           mbar_arrive(&dq_empty[sj]);
+          ZC_BTRACE(0, i, 7);
         }
         __syncwarp();
       }
@@ -775,7 +795,7 @@ int zc_attn_bwd_ws(const void* q, const void* k, const void* v, const void* o, c
   p.lse = lse; p.delta = delta; p.dq_acc = sc.dq_acc; p.dk = (__nv_bfloat16*)dk; p.dv = (__nv_bfloat16*)dv;
   p.B = B; p.S = S; p.Hq = Hq; p.Hkv = Hkv;
   p.dks0 = dks0; p.dks1 = dks1; p.dks2 = dks2; p.dvs0 = dvs0; p.dvs1 = dvs1; p.dvs2 = dvs2;
-  p.scale = scale; p.status = sc.status;
+  p.scale = scale; p.status = sc.status; p.trace = nullptr;
   const int64_t rows = (int64_t)B * S * Hq;
   delta_kernel<<<(unsigned)((rows * 32 + 255) / 256), 256, 0, st>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)dout,
                                                                    delta, B, S, Hq, D);
@@ -793,6 +813,10 @@ int zc_attn_bwd_ws(const void* q, const void* k, const void* v, const void* o, c
   dq_convert_kernel<<<cgrid, 256, 0, st>>>(sc.dq_acc, (__nv_bfloat16*)dq, (int64_t)B * S, Hq, D, dqs1, dqs2);
   return launch_status();
 }
+
+// Profiling aid: a device buffer of 3 * 256 * 8 int64 (or null) that CTA 0 of later key-row launches
+// fills with SM-clock stamps of its phases.
+void zc_attn_bwd_kt_set_trace(void* buf) { zc::bws::g_trace = (long long*)buf; }
 
 // Same argument list as zc_attn_bwd.  Head dimension 128 runs the key-row kernel; 64 falls back to
 // zc_attn_bwd_ws.
@@ -838,7 +862,7 @@ int zc_attn_bwd_kt(const void* q, const void* k, const void* v, const void* o, c
   p.lse = lse; p.delta = delta; p.dq_acc = sc.dq_acc; p.dk = (__nv_bfloat16*)dk; p.dv = (__nv_bfloat16*)dv;
   p.B = B; p.S = S; p.Hq = Hq; p.Hkv = Hkv;
   p.dks0 = dks0; p.dks1 = dks1; p.dks2 = dks2; p.dvs0 = dvs0; p.dvs1 = dvs1; p.dvs2 = dvs2;
-  p.scale = scale; p.status = sc.status;
+  p.scale = scale; p.status = sc.status; p.trace = g_trace;
   const int64_t rows = (int64_t)B * S * Hq;
   delta_kernel<<<(unsigned)((rows * 32 + 255) / 256), 256, 0, st>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)dout,
                                                                    delta, B, S, Hq, D);
@@ -846,7 +870,7 @@ int zc_attn_bwd_kt(const void* q, const void* k, const void* v, const void* o, c
   static bool attr = false;
   if (!attr) { cudaFuncSetAttribute(bkt::attn_bwd_kt_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); attr = true; }
   const int nkb = (S + 127) / 128;
-  bkt::attn_bwd_kt_kernel<<<nkb * Hkv * B, 320, smem, st>>>(mq, mk, mv, mdo, mdq, p, nkb);
+  bkt::attn_bwd_kt_kernel<<<nkb * Hkv * B, 352, smem, st>>>(mq, mk, mv, mdo, mdq, p, nkb);
   const int cgrid = (int)std::min<int64_t>((rows * (D / 4) + 255) / 256, (int64_t)sm_count() * 16);
   dq_convert_kernel<<<cgrid, 256, 0, st>>>(sc.dq_acc, (__nv_bfloat16*)dq, (int64_t)B * S, Hq, D, dqs1, dqs2);
   return launch_status();

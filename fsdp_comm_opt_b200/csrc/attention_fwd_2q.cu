@@ -35,7 +35,7 @@ namespace zc {
 namespace fwd2q {
 using namespace attn;
 
-constexpr int THREADS = 320;
+constexpr int THREADS = 352;
 constexpr int KB = 64;          // keys per block
 constexpr int STAGES = 4;       // K/V ring
 constexpr float RAISE = 8.f;    // log2 of the factor by which a row maximum may lag behind
@@ -47,7 +47,12 @@ struct Params {
   float scale;
   int* status;
   int ncb;  // number of 256-query blocks
+  long long* trace;  // null, or [2][blocks][8] SM-clock stamps written by CTA 0 (softmax warp 2, MMA thread)
 };
+#define ZC_TRACE(slot, j, k)                                                          \
+  do {                                                                                \
+    if (p.trace && blockIdx.x == 0 && (j) < 128) p.trace[((slot) * 128 + (j)) * 8 + (k)] = clock64(); \
+  } while (0)
 
 __global__ void __launch_bounds__(THREADS, 1) attn_fwd_2q_kernel(const __grid_constant__ CUtensorMap mapQ,
                                                                  const __grid_constant__ CUtensorMap mapK,
@@ -79,7 +84,7 @@ __global__ void __launch_bounds__(THREADS, 1) attn_fwd_2q_kernel(const __grid_co
     mbar_init(&q_full, 1);
     for (int i = 0; i < STAGES; ++i) {
       mbar_init(&kv_full[i], 1);
-      mbar_init(&kv_empty[i], 1);
+      mbar_init(&kv_empty[i], 2);  // one arrival per MMA issuer
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&s_full[i], 1);
@@ -120,44 +125,54 @@ __global__ void __launch_bounds__(THREADS, 1) attn_fwd_2q_kernel(const __grid_co
         }
       }
     }
-  } else if (warp == 1) {
+  } else if (warp == 1 || warp == 10) {
+    // one MMA issuer per query tile (warp 1: tile 0, warp 10: tile 1): a tcgen05.mma takes about a
+    // hundred cycles to issue whatever its width, so one thread cannot feed the tensor core alone
     if (lane == 0) {
+      const int t = warp == 1 ? 0 : 1;
       const uint32_t id_s = idesc_bf16(128, KB, MAJOR_K, MAJOR_K);
       const uint32_t id_o = idesc_bf16(128, D, MAJOR_K, MAJOR_MN);
-      const uint32_t aQ = smem_u32(sQ), aKV = smem_u32(sKV), aP = smem_u32(sP);
+      const uint32_t aQ = smem_u32(sQ) + t * 32768, aKV = smem_u32(sKV), aP = smem_u32(sP) + t * 16384;
+      const uint32_t tm_s = tm + t * 64, tm_o = tm + 128 + t * 128;
+      const int nbt = nb[t];
       bool ok = role_wait(&q_full, 0, &s_abort);
       // S_t(j) = Q_t K_j^T: A = Q tile (K-major, 16 KB slabs), B = K block (K-major, 8 KB slabs)
-      auto issue_s = [&](int t, int j) -> bool {
+      auto issue_s = [&](int j) -> bool {
         const int s = j % STAGES;
         if (!role_wait(&kv_full[s], (j / STAGES) & 1, &s_abort)) return false;
         if (j > 0 && !role_wait(&s_empty[t], (j - 1) & 1, &s_abort)) return false;
         tc_fence_after_sync();
-        const uint32_t qa = aQ + t * 32768, ka = aKV + s * 32768;
+        const uint32_t ka = aKV + s * 32768;
 #pragma unroll
         for (int k = 0; k < D / 16; ++k)
-          mma_bf16(tm + t * 64, smem_desc(qa + (k >> 2) * 16384 + (k & 3) * 32, 16, 1024),
+          mma_bf16(tm_s, smem_desc(aQ + (k >> 2) * 16384 + (k & 3) * 32, 16, 1024),
                    smem_desc(ka + (k >> 2) * 8192 + (k & 3) * 32, 16, 1024), id_s, k != 0);
         mma_commit(&s_full[t]);
         return true;
       };
-      for (int t = 0; t < 2 && ok; ++t)
-        if (nb[t] > 0) ok = issue_s(t, 0);
+      if (ok && nbt > 0) ok = issue_s(0);
       for (int j = 0; j < nbmax && ok; ++j) {
-        for (int t = 0; t < 2 && ok; ++t)
-          if (j + 1 < nb[t]) ok = issue_s(t, j + 1);
-        for (int t = 0; t < 2 && ok; ++t) {
-          if (j >= nb[t]) continue;
-          if (!(ok = role_wait(&p_full[t], j & 1, &s_abort))) break;
-          tc_fence_after_sync();
-          // O_t += P_t V_j: A = P tile [128 x 64 keys] K-major, B = V block [64 keys x 128] MN-major
-          const uint32_t pa = aP + t * 16384, va = aKV + (j % STAGES) * 32768 + 16384;
-#pragma unroll
-          for (int k = 0; k < KB / 16; ++k)
-            mma_bf16(tm + 128 + t * 128, smem_desc(pa + k * 32, 16, 1024), smem_desc(va + k * 2048, 8192, 1024), id_o,
-                     (j | k) != 0);
-          mma_commit(&o_full[t]);
+        if (t == 0) ZC_TRACE(1, j, 0);
+        if (j >= nbt) {
+          // this tile has no such block: only hand the stage back, and only once it has been
+          // filled, so that each phase of kv_empty gets exactly one arrival from each issuer
+          if (!(ok = role_wait(&kv_full[j % STAGES], (j / STAGES) & 1, &s_abort))) break;
+          mbar_arrive(&kv_empty[j % STAGES]);
+          continue;
         }
-        if (ok) mma_commit(&kv_empty[j % STAGES]);  // every reader of this stage has been issued
+        if (j + 1 < nbt && !(ok = issue_s(j + 1))) break;
+        if (t == 0) ZC_TRACE(1, j, 1);
+        if (!(ok = role_wait(&p_full[t], j & 1, &s_abort))) break;
+        tc_fence_after_sync();
+        if (t == 0) ZC_TRACE(1, j, 2);
+        // O_t += P_t V_j: A = P tile [128 x 64 keys] K-major, B = V block [64 keys x 128] MN-major
+        const uint32_t va = aKV + (j % STAGES) * 32768 + 16384;
+#pragma unroll
+        for (int k = 0; k < KB / 16; ++k)
+          mma_bf16(tm_o, smem_desc(aP + k * 32, 16, 1024), smem_desc(va + k * 2048, 8192, 1024), id_o, (j | k) != 0);
+        mma_commit(&o_full[t]);
+        mma_commit(&kv_empty[j % STAGES]);  // this tile's readers of the stage have been issued
+        if (t == 0) ZC_TRACE(1, j, 3);
       }
       if (!ok) s_abort = 1;
     }
@@ -174,10 +189,13 @@ __global__ void __launch_bounds__(THREADS, 1) attn_fwd_2q_kernel(const __grid_co
     const float sl2 = p.scale * LOG2E;
     float m_ref = -CUDART_INF_F, l = 0.f;
     bool fail = false;
+    const bool tr = (warp == 2 && lane == 0);
     for (int j = 0; j < nbt; ++j) {
-      fail = !mbar_wait(&s_full[t], j & 1);
+      if (tr) ZC_TRACE(0, j, 0);
+      fail = !mbar_wait_parked(&s_full[t], j & 1, &s_abort);
       if (__any_sync(0xffffffffu, fail || s_abort)) { fail = true; break; }
       tc_fence_after_sync();
+      if (tr) ZC_TRACE(0, j, 1);
       uint32_t sa[32], sb[32];
       tmem_ld32(tmem_addr(tm_s, lane_base, 0), sa);
       tmem_ld32(tmem_addr(tm_s, lane_base, 32), sb);
@@ -186,6 +204,7 @@ __global__ void __launch_bounds__(THREADS, 1) attn_fwd_2q_kernel(const __grid_co
       __syncwarp();
       if (lane == 0) mbar_arrive(&s_empty[t]);  // the next block's scores may overwrite S_t now
       __syncwarp();
+      if (tr) ZC_TRACE(0, j, 2);
       const int k0 = j * KB;
       if ((k0 + KB - 1 > qt0) || (k0 + KB > p.S)) {  // block touches the diagonal or the end of the sequence
         const uint32_t ninf = __float_as_uint(-CUDART_INF_F);
@@ -196,9 +215,12 @@ __global__ void __launch_bounds__(THREADS, 1) attn_fwd_2q_kernel(const __grid_co
           if (c + 32 > row || c + 32 >= p.S) sb[i] = ninf;
         }
       }
-      float mx = -CUDART_INF_F;
+      // four independent chains: a single running maximum would serialise 64 dependent operations
+      float mx4[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
 #pragma unroll
-      for (int i = 0; i < 32; ++i) mx = fmaxf(mx, fmaxf(__uint_as_float(sa[i]), __uint_as_float(sb[i])));
+      for (int i = 0; i < 32; ++i)
+        mx4[i & 3] = fmaxf(mx4[i & 3], fmaxf(__uint_as_float(sa[i]), __uint_as_float(sb[i])));
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       const float m_cand = mx * sl2;
       const bool raise = m_cand > m_ref + RAISE;  // also true for the first unmasked block (m_ref = -inf)
       float alpha = 1.f;
@@ -208,9 +230,10 @@ __global__ void __launch_bounds__(THREADS, 1) attn_fwd_2q_kernel(const __grid_co
         l *= alpha;
       }
       const float m_use = (m_ref == -CUDART_INF_F) ? 0.f : m_ref;
+      if (tr) ZC_TRACE(0, j, 3);
       if (j > 0) {
         // the previous P_t V has completed: P_t may be overwritten and O_t may be rescaled
-        fail = !mbar_wait(&o_full[t], (j - 1) & 1);
+        fail = !mbar_wait_parked(&o_full[t], (j - 1) & 1, &s_abort);
         if (__any_sync(0xffffffffu, fail || s_abort)) { fail = true; break; }
         tc_fence_after_sync();
         if (__any_sync(0xffffffffu, raise)) {
@@ -226,7 +249,8 @@ __global__ void __launch_bounds__(THREADS, 1) attn_fwd_2q_kernel(const __grid_co
           tmem_st_wait();
         }
       }
-      float rs = 0.f;
+      if (tr) ZC_TRACE(0, j, 4);
+      float rs4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int q = 0; q < 8; ++q) {
         const uint32_t* src = q < 4 ? &sa[q * 8] : &sb[(q - 4) * 8];
@@ -234,21 +258,23 @@ __global__ void __launch_bounds__(THREADS, 1) attn_fwd_2q_kernel(const __grid_co
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
           e[i] = exp2f(__uint_as_float(src[i]) * sl2 - m_use);
-          rs += e[i];
+          rs4[i & 3] += e[i];
         }
         *reinterpret_cast<uint4*>(tp + sw128_off(r, q)) =
             make_uint4(pack_bf16(e[0], e[1]), pack_bf16(e[2], e[3]), pack_bf16(e[4], e[5]), pack_bf16(e[6], e[7]));
       }
-      l += rs;
+      l += (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
+      if (tr) ZC_TRACE(0, j, 5);
       fence_proxy_async_smem();
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&p_full[t]);
       __syncwarp();
+      if (tr) ZC_TRACE(0, j, 6);
     }
     if (fail) s_abort = 1;
     if (!fail && nbt > 0) {
-      fail = !mbar_wait(&o_full[t], (nbt - 1) & 1);
+      fail = !mbar_wait_parked(&o_full[t], (nbt - 1) & 1, &s_abort);
       if (__any_sync(0xffffffffu, fail)) {
         s_abort = 1;
       } else {
@@ -283,6 +309,8 @@ __global__ void __launch_bounds__(THREADS, 1) attn_fwd_2q_kernel(const __grid_co
   if (warp == 1) tmem_dealloc(tm, 512);
 }
 
+static long long* g_trace = nullptr;
+
 static int* status_word(int dev) {
   static int* st[64] = {nullptr};
   if (!st[dev]) {
@@ -308,6 +336,10 @@ int zc_attn_fwd_2q_status_read_and_clear() {
   return v;
 }
 
+// Profiling aid: a device buffer of 2 * 128 * 8 int64 (or null) that CTA 0 of later launches fills
+// with SM-clock stamps of its phases.
+void zc_attn_fwd_2q_set_trace(void* buf) { zc::fwd2q::g_trace = (long long*)buf; }
+
 // Same argument list as zc_attn_fwd_ws.  Head dimension 128 runs the two-tile kernel; 64 falls back
 // to zc_attn_fwd_ws.
 int zc_attn_fwd_2q(const void* q, const void* k, const void* v, void* o, float* lse, int B, int S, int Hq, int Hkv,
@@ -332,6 +364,7 @@ int zc_attn_fwd_2q(const void* q, const void* k, const void* v, void* o, float* 
   p.o = (__nv_bfloat16*)o; p.lse = lse; p.B = B; p.S = S; p.Hq = Hq; p.Hkv = Hkv; p.scale = scale;
   p.status = status_word(dev);
   p.ncb = (S + 255) / 256;
+  p.trace = g_trace;
   if (!p.status) return ERR_BAD_ARG;
   const int smem = 65536 + STAGES * 32768 + 2 * 16384 + 1024;
   static bool attr = false;

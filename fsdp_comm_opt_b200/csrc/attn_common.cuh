@@ -43,16 +43,11 @@ __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
-// Bounded wait for the TMA and MMA threads: polls with a sleep in between, and gives up after two
+// Bounded wait for the TMA and MMA threads: parked in hardware (no issue slots taken from the
+// softmax warps on the same scheduler), woken when the phase completes, given up after two
 // seconds or as soon as another role has raised `*abort_flag`.
 __device__ __forceinline__ bool role_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const unsigned long long t0 = globaltimer_ns();
-  for (uint32_t it = 0;; ++it) {
-    __nanosleep(32);
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((it & 63u) == 63u && (*abort_flag || globaltimer_ns() - t0 > 2000000000ull)) return false;
-  }
+  return mbar_wait_parked(bar, parity, abort_flag);
 }
 
 typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,

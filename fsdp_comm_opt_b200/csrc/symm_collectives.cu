@@ -402,6 +402,152 @@ __global__ void __launch_bounds__(256) symm_reduce_scatter_kernel(const RsArgs a
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// int8 all-gather: the arithmetic of the int8 hook (per-shard absmax scale = max(absmax/127, 1e-8),
+// q = clamp(round(x / scale), -127, 127)) on the same staging protocol.  A chunk's record is its
+// 1024 int8 values at the start of its slot; the header word carries the source's scale, so the
+// wire cost is 1028 bytes per 1024 elements.  Every rank, the source included, ends up with the
+// dequantised values, so all ranks see identical parameters.
+// ---------------------------------------------------------------------------------------------
+constexpr int CW_ABSMAX = 70;  // bits of max|x| over the shard being gathered (set by absmax_bf16_kernel)
+
+__global__ void __launch_bounds__(256) absmax_bf16_kernel(const uint16_t* __restrict__ x, long long n,
+                                                          uint32_t* __restrict__ word) {
+  uint32_t m = 0;  // |bf16| bit patterns order like the values
+  const long long nv = ((reinterpret_cast<uintptr_t>(x) & 15) == 0) ? n / 8 : 0;
+  for (long long i = (long long)blockIdx.x * 256 + threadIdx.x; i < nv; i += (long long)gridDim.x * 256) {
+    const uint4 v = __ldg(reinterpret_cast<const uint4*>(x) + i);
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) m = max(m, max(w[k] & 0x7FFFu, (w[k] >> 16) & 0x7FFFu));
+  }
+  for (long long i = nv * 8 + (long long)blockIdx.x * 256 + threadIdx.x; i < n; i += (long long)gridDim.x * 256)
+    m = max(m, (uint32_t)x[i] & 0x7FFFu);
+#pragma unroll
+  for (int s = 16; s > 0; s >>= 1) m = max(m, __shfl_xor_sync(0xffffffffu, m, s));
+  if ((threadIdx.x & 31) == 0 && m) atomicMax(word, m << 16);  // fp32 bits of the bf16 magnitude
+}
+
+// one value -> its int8 byte; `dq` receives the value every rank will reconstruct
+__device__ __forceinline__ uint32_t quant_byte(float x, float scale, float& dq) {
+  const float r = fminf(fmaxf(rintf(x / scale), -127.f), 127.f);
+  dq = r * scale;
+  return (uint32_t)((int)r) & 0xFFu;
+}
+
+__global__ void __launch_bounds__(256) symm_all_gather_int8_kernel(const AgArgs a) {
+  __shared__ int s_ok;
+  const SymmLayout& L = a.L;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int parity = a.seq & 1;
+  const long long nc = (a.n + V2_CHUNK_ELEMS - 1) / V2_CHUNK_ELEMS;
+  const long long ngroups = (nc + GROUP_CHUNKS - 1) / GROUP_CHUNKS;
+  if (tid == 0) s_ok = 1;
+  __syncthreads();
+
+  if ((int)blockIdx.x < a.push_ctas) {
+    if (tid < L.world && tid != L.rank && a.seq >= 3) {
+      if (!wait_ge(ctrl(a.local) + CW_DONE + tid, a.seq - 2, a.timeout_ns)) {
+        set_status(a.local, 1, tid, -1);
+        s_ok = 0;
+      }
+    }
+    __syncthreads();
+    if (!s_ok) return;
+    const float absmax = __uint_as_float(ctrl(a.local)[CW_ABSMAX]);
+    const float scale = fmaxf(absmax / 127.f, 1e-8f);
+    const bool in_al = (reinterpret_cast<uintptr_t>(a.in) & 15) == 0;
+    uint16_t* own = a.out + (long long)L.rank * a.n;
+    const bool own_al = (reinterpret_cast<uintptr_t>(own) & 15) == 0;
+    unsigned long long pushed = 0;
+    for (long long g = blockIdx.x; g < ngroups; g += a.push_ctas) {
+      for (int it = 0; it < GROUP_CHUNKS / 8; ++it) {
+        const long long c = g * GROUP_CHUNKS + it * 8 + warp;
+        if (c >= nc) break;
+        const long long e0 = c * V2_CHUNK_ELEMS + lane * 32;
+        LaneIn li, dq;
+        load_lane(a.in + e0, a.n - e0, in_al, li);
+        uint32_t qw[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          float d0, d1, d2, d3;
+          const uint32_t b0 = quant_byte(bf16_bits_to_f(li.w[2 * k] & 0xFFFFu), scale, d0);
+          const uint32_t b1 = quant_byte(bf16_bits_to_f(li.w[2 * k] >> 16), scale, d1);
+          const uint32_t b2 = quant_byte(bf16_bits_to_f(li.w[2 * k + 1] & 0xFFFFu), scale, d2);
+          const uint32_t b3 = quant_byte(bf16_bits_to_f(li.w[2 * k + 1] >> 16), scale, d3);
+          qw[k] = b0 | (b1 << 8) | (b2 << 16) | (b3 << 24);
+          dq.w[2 * k] = f_to_bf16_bits(d0) | (f_to_bf16_bits(d1) << 16);
+          dq.w[2 * k + 1] = f_to_bf16_bits(d2) | (f_to_bf16_bits(d3) << 16);
+        }
+        store_lane(own + e0, a.n - e0, own_al, dq);  // the source keeps what the others will see
+        const uint4 q0 = make_uint4(qw[0], qw[1], qw[2], qw[3]), q1 = make_uint4(qw[4], qw[5], qw[6], qw[7]);
+        for (int q = 0; q < L.world; ++q) {
+          if (q == L.rank) continue;
+          uint8_t* slot = slot_ptr(a.peers[q], L, parity, L.rank);
+          uint4* dst = reinterpret_cast<uint4*>(slot + L.hdr_bytes + c * V2_SLOT_BYTES + lane * 32);
+          dst[0] = q0;
+          dst[1] = q1;
+          if (lane == 0) reinterpret_cast<uint32_t*>(slot)[c] = __float_as_uint(scale);
+        }
+        if (lane == 0) pushed += (unsigned long long)(V2_CHUNK_ELEMS + 4) * (L.world - 1);
+      }
+      __threadfence_system();
+      __syncthreads();
+      if (tid < L.world && tid != L.rank) st_release_sys(flag_ptr(a.peers[tid], L, parity, L.rank, g), a.seq);
+    }
+    if (lane == 0 && pushed) atomicAdd(reinterpret_cast<unsigned long long*>(ctrl(a.local) + CW_WIRE_LO), pushed);
+    return;
+  }
+  const int dec_ctas = gridDim.x - a.push_ctas;
+  const long long items = ngroups * (L.world - 1);
+  for (long long i = (long long)blockIdx.x - a.push_ctas; i < items; i += dec_ctas) {
+    const long long g = i / (L.world - 1);
+    int src = (int)(i % (L.world - 1));
+    if (src >= L.rank) ++src;
+    uint32_t* fl = flag_ptr(a.local, L, parity, src, g);
+    if (tid == 0 && !wait_ge(fl, a.seq, a.timeout_ns)) {
+      set_status(a.local, 2, src, g);
+      s_ok = 0;
+    }
+    __syncthreads();
+    if (!s_ok) break;
+    (void)ld_acquire_sys(fl);
+    const uint8_t* slot = slot_ptr(a.local, L, parity, src);
+    uint16_t* dst = a.out + (long long)src * a.n;
+    const bool al = (reinterpret_cast<uintptr_t>(dst) & 15) == 0;
+    for (int it = 0; it < GROUP_CHUNKS / 8; ++it) {
+      const long long c = g * GROUP_CHUNKS + it * 8 + warp;
+      if (c >= nc) break;
+      const float scale = __uint_as_float(__ldcg(reinterpret_cast<const uint32_t*>(slot) + c));
+      const uint4* rec = reinterpret_cast<const uint4*>(slot + L.hdr_bytes + c * V2_SLOT_BYTES + lane * 32);
+      const uint4 q0 = __ldcg(rec), q1 = __ldcg(rec + 1);
+      const uint32_t qw[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+      LaneIn o;
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        const float d0 = (float)(int8_t)(qw[k] & 0xFFu) * scale, d1 = (float)(int8_t)((qw[k] >> 8) & 0xFFu) * scale;
+        const float d2 = (float)(int8_t)((qw[k] >> 16) & 0xFFu) * scale, d3 = (float)(int8_t)(qw[k] >> 24) * scale;
+        o.w[2 * k] = f_to_bf16_bits(d0) | (f_to_bf16_bits(d1) << 16);
+        o.w[2 * k + 1] = f_to_bf16_bits(d2) | (f_to_bf16_bits(d3) << 16);
+      }
+      const long long e0 = c * V2_CHUNK_ELEMS + lane * 32;
+      store_lane(dst + e0, a.n - e0, al, o);
+    }
+  }
+  __syncthreads();
+  if (tid == 0) {
+    uint32_t* c = ctrl(a.local);
+    __threadfence();
+    const uint32_t prev = atomicAdd(c + CW_COUNTER, 1u);
+    if (prev + 1 == (uint32_t)dec_ctas) {
+      c[CW_COUNTER] = 0;
+      __threadfence_system();
+      for (int q = 0; q < L.world; ++q)
+        if (q != L.rank) st_release_sys(ctrl(a.peers[q]) + CW_DONE + L.rank, a.seq);
+    }
+  }
+}
+
 static SymmLayout make_layout(int world, int rank, long long nc_max) {
   SymmLayout L;
   L.world = world;
@@ -455,6 +601,27 @@ int zc_symm_reduce_scatter(const void* in, void* out, void* residual, void* cons
   a.timeout_ns = (unsigned long long)(timeout_s * 1e9);
   a.L = make_layout(world, rank, nc_max);
   symm_reduce_scatter_kernel<<<push_ctas + dec_ctas, 256, 0, st>>>(a);
+  return launch_status();
+}
+
+// int8 variant of zc_symm_all_gather: three stream-ordered operations (clear the absmax word,
+// reduce max|x| over the shard, then the fused quantise/push/dequantise kernel)
+int zc_symm_all_gather_int8(const void* in, void* out, void* const* peers, void* local, long long n, int rank,
+                            int world, long long nc_max, unsigned seq, int push_ctas, int dec_ctas, double timeout_s,
+                            cudaStream_t st) {
+  using namespace zc;
+  const long long nc = (n + V2_CHUNK_ELEMS - 1) / V2_CHUNK_ELEMS;
+  if (world < 2 || world > 64 || nc > nc_max || nc == 0 || push_ctas < 1 || dec_ctas < 1) return ERR_BAD_ARG;
+  AgArgs a;
+  a.in = (const uint16_t*)in; a.out = (uint16_t*)out; a.peers = (uint8_t* const*)peers; a.local = (uint8_t*)local;
+  a.n = n; a.seq = seq; a.push_ctas = push_ctas;
+  a.timeout_ns = (unsigned long long)(timeout_s * 1e9);
+  a.L = make_layout(world, rank, nc_max);
+  uint32_t* word = reinterpret_cast<uint32_t*>(local) + CW_ABSMAX;
+  cudaMemsetAsync(word, 0, sizeof(uint32_t), st);
+  const int grid = (int)std::min<long long>((n / 8 + 255) / 256 + 1, (long long)sm_count() * 8);
+  absmax_bf16_kernel<<<grid, 256, 0, st>>>((const uint16_t*)in, n, word);
+  symm_all_gather_int8_kernel<<<push_ctas + dec_ctas, 256, 0, st>>>(a);
   return launch_status();
 }
 

@@ -53,6 +53,32 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+// try_wait with a suspend-time hint: the hardware may park the thread for up to `hint_ns` without
+// taking issue slots from the other warps of its scheduler, and wakes it when the phase completes
+__device__ __forceinline__ bool mbar_try_wait_hint(uint64_t* bar, uint32_t parity, uint32_t hint_ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(hint_ns)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait built on the hinted try_wait: no spinning, immediate wake-up.  Returns false after
+// `limit_ns` of wall time, or as soon as `*abort_flag` (may be null) is raised by another role.
+__device__ __forceinline__ bool mbar_wait_parked(uint64_t* bar, uint32_t parity, volatile int* abort_flag = nullptr,
+                                                 unsigned long long limit_ns = 2000000000ull) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const unsigned long long t0 = globaltimer_ns();
+  for (;;) {
+    if (mbar_try_wait_hint(bar, parity, 100000u)) return true;
+    if ((abort_flag && *abort_flag) || globaltimer_ns() - t0 > limit_ns) return false;
+  }
+}
 // Bounded wait.  Returns false when `limit_ns` of wall time passed without the phase completing;
 // callers then raise their error flag and leave instead of spinning forever.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity,
