@@ -508,10 +508,10 @@ __global__ void __launch_bounds__(352, 1) attn_bwd_kt_kernel(const __grid_consta
         tma_load_4d(sK + sl * 16384, &mapK, &kv_full, sl * 64, hk, k0, b);
         tma_load_4d(sV + sl * 16384, &mapV, &kv_full, sl * 64, hk, k0, b);
       }
+      int h = hk * group, ib = 2 * jb;
       for (int i = 0; i < iters; ++i) {
         const int st = i & 1;
-        const int h = hk * group + i / nqi;
-        const int q0 = (2 * jb + i % nqi) * QB;
+        const int q0 = ib * QB;
         if (!role_wait(&qdo_empty[st], ((i >> 1) & 1) ^ 1)) { s_abort = 1; break; }
         mbar_expect_tx(&qdo_full[st], 2 * 16384);
 #pragma unroll
@@ -519,6 +519,7 @@ __global__ void __launch_bounds__(352, 1) attn_bwd_kt_kernel(const __grid_consta
           tma_load_4d(sQ + st * 16384 + sl * 8192, &mapQ, &qdo_full[st], sl * 64, h, q0, b);
           tma_load_4d(sdO + st * 16384 + sl * 8192, &mapdO, &qdo_full[st], sl * 64, h, q0, b);
         }
+        if (++ib == nq64) { ib = 2 * jb; ++h; }
       }
     }
   } else if (warp == 1 || warp == 10) {
@@ -593,15 +594,16 @@ __global__ void __launch_bounds__(352, 1) attn_bwd_kt_kernel(const __grid_consta
     const int c0 = half * 32;
     const float sl2 = p.scale * LOG2E;
     // threads 0..63 fetch lse, 64..127 fetch delta of the next iteration's queries (one value each)
-    auto fetch = [&](int i) -> float {
-      if (ct >= 128 || i >= iters) return 0.f;
-      const int h = hk * group + i / nqi;
-      const int q = (2 * jb + i % nqi) * QB + (ct & 63);
+    auto fetch = [&](int h, int ib, bool valid) -> float {
+      if (ct >= 128 || !valid) return 0.f;
+      const int q = ib * QB + (ct & 63);
       if (q >= p.S) return 0.f;
       const int64_t idx = ((int64_t)b * p.Hq + h) * p.S + q;
       return ct < 64 ? __ldg(p.lse + idx) * LOG2E : __ldg(p.delta + idx) * p.scale;
     };
-    float pre = fetch(0);
+    // (head, 64-query block) of the current and of the previous iteration, advanced without divisions
+    int cur_h = hk * group, cur_ib = 2 * jb, prev_h = 0, prev_q0 = 0;
+    float pre = fetch(cur_h, cur_ib, iters > 0);
     bool fail = false, aborted = false;
     for (int i = 0; i <= iters; ++i) {
       if (i < iters) {
@@ -621,9 +623,13 @@ __global__ void __launch_bounds__(352, 1) attn_bwd_kt_kernel(const __grid_consta
         if (tid == 64) mbar_arrive(&sdp_empty);
         __syncwarp();
         if (tid == 64) ZC_BTRACE(0, i, 2);
-        pre = fetch(i + 1);
+        {
+          int nh = cur_h, nib = cur_ib + 1;
+          if (nib == nq64) { nib = 2 * jb; ++nh; }
+          pre = fetch(nh, nib, i + 1 < iters);
+        }
         // ---- B: P^T and dS^T ------------------------------------------------------------------
-        const int q0 = (2 * jb + i % nqi) * QB;
+        const int q0 = cur_ib * QB;
         const bool diag = (q0 < k0 + 128) || (q0 + QB > p.S) || (k0 + 128 > p.S);
         const float4* st_l = reinterpret_cast<const float4*>(&s_stat[st][c0]);
         const float4* st_d = reinterpret_cast<const float4*>(&s_stat[st][64 + c0]);
@@ -692,16 +698,17 @@ __global__ void __launch_bounds__(352, 1) attn_bwd_kt_kernel(const __grid_consta
         tc_fence_before_sync();
         if (named_bar_or(3, 256, fail || s_abort)) { aborted = true; break; }
         if (tid == 64) {
-          const int hj = hk * group + j / nqi;
-          const int qj = (2 * jb + j % nqi) * QB;
 #pragma unroll
-          for (int t = 0; t < 4; ++t) tma_reduce_add_4d(&mapdQ, sStage + t * 8192, t * 32, hj, qj, b);
+          for (int t = 0; t < 4; ++t) tma_reduce_add_4d(&mapdQ, sStage + t * 8192, t * 32, prev_h, prev_q0, b);
           bulk_commit();
           mbar_arrive(&dq_empty[sj]);
           ZC_BTRACE(0, i, 7);
         }
         __syncwarp();
       }
+      prev_h = cur_h;
+      prev_q0 = cur_ib * QB;
+      if (++cur_ib == nq64) { cur_ib = 2 * jb; ++cur_h; }
     }
     if (tid == 64) bulk_wait0();
     __syncwarp();

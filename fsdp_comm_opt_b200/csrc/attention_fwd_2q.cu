@@ -1,13 +1,13 @@
 // Causal GQA attention forward for sm_100a, head dimension 128: two query tiles per CTA (the
 // default forward path).
 //
-// One CTA (320 threads) owns 256 consecutive queries of one head as two 128-row tiles that share
+// One CTA (352 threads) owns 256 consecutive queries of one head as two 128-row tiles that share
 // every K/V block it loads.  Key blocks hold 64 keys, so a softmax thread owns a whole score row
 // of a block (64 fp32 registers): no partner thread, no exchange through shared memory, and the
 // row maximum, the exponentials and the row sum come from one read of TMEM.
-//   warp 0      TMA producer: both Q tiles once, then K/V blocks into a four-stage ring
-//   warp 1      MMA issuer: S_t = Q_t K_j^T (128 x 64, fp32 in TMEM) and O_t += P_t V_j with the
-//               output accumulating in TMEM for the whole row of blocks
+//   warp 0      TMA producer: both Q tiles once, then K/V blocks into a three-stage ring
+//   warps 1,10  MMA issuers, one per tile: S_t = Q_t K_j^T (128 x 64, fp32 in TMEM) and
+//               O_t += P_t V_j with the output accumulating in TMEM for the whole row of blocks
 //   warps 2-5   softmax of tile 0, warps 6-9 softmax of tile 1, one thread per query row.  A
 //               thread copies its row of S_t to registers and releases the TMEM buffer at once, so
 //               the next block's scores are computed while this block is exponentiated; the two
@@ -16,7 +16,7 @@
 // (exponentials stay below 256, exact enough in bf16 and fp32); raising it rescales the row of O in
 // TMEM (tcgen05.ld, multiply, tcgen05.st), which after the first few blocks almost never happens.
 // TMEM (512 columns allocated): S_0 64 | S_1 64 | O_0 128 | O_1 128.
-// Shared memory: Q 2 x 32 KB, K/V ring 4 x (16 + 16) KB, P 2 x 16 KB.
+// Shared memory: Q 2 x 32 KB, K/V ring 3 x (16 + 16) KB, P 2 tiles x 2 block parities x 16 KB.
 // CTAs are numbered heaviest first (the last 256 queries see the most keys).  Every wait is
 // bounded; a timed-out role raises a CTA-wide abort flag, the CTA frees its TMEM and returns, and the
 // launcher's status word reports it.
@@ -37,7 +37,7 @@ using namespace attn;
 
 constexpr int THREADS = 352;
 constexpr int KB = 64;          // keys per block
-constexpr int STAGES = 4;       // K/V ring
+constexpr int STAGES = 3;       // K/V ring
 constexpr float RAISE = 8.f;    // log2 of the factor by which a row maximum may lag behind
 
 struct Params {
@@ -63,8 +63,8 @@ __global__ void __launch_bounds__(THREADS, 1) attn_fwd_2q_kernel(const __grid_co
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sQ = smem;              // tile t at t * 32 KB: two 64-column slabs of [128 x 128 B]
   uint8_t* sKV = smem + 65536;     // stage s at s * 32 KB: K (two slabs of [64 x 128 B]), then V
-  uint8_t* sP = smem + 196608;     // tile t at t * 16 KB: [128 rows x 64 keys] bf16, one slab
-  __shared__ uint64_t q_full, kv_full[STAGES], kv_empty[STAGES], s_full[2], s_empty[2], p_full[2], o_full[2];
+  uint8_t* sP = smem + 65536 + STAGES * 32768;  // tile t, block parity u at (2 t + u) * 16 KB: [128 rows x 64 keys] bf16
+  __shared__ uint64_t q_full, kv_full[STAGES], kv_empty[STAGES], s_full[2], s_empty[2], p_full[2], o_full[4];  // o_full[2 t + (j & 1)]
   __shared__ uint32_t tmem_base;
   __shared__ volatile int s_abort;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -90,8 +90,8 @@ __global__ void __launch_bounds__(THREADS, 1) attn_fwd_2q_kernel(const __grid_co
       mbar_init(&s_full[i], 1);
       mbar_init(&s_empty[i], 4);  // one arrival per softmax warp of the tile
       mbar_init(&p_full[i], 4);
-      mbar_init(&o_full[i], 1);
     }
+    for (int i = 0; i < 4; ++i) mbar_init(&o_full[i], 1);
     mbar_fence_init();
     s_abort = 0;
   }
@@ -132,7 +132,7 @@ __global__ void __launch_bounds__(THREADS, 1) attn_fwd_2q_kernel(const __grid_co
       const int t = warp == 1 ? 0 : 1;
       const uint32_t id_s = idesc_bf16(128, KB, MAJOR_K, MAJOR_K);
       const uint32_t id_o = idesc_bf16(128, D, MAJOR_K, MAJOR_MN);
-      const uint32_t aQ = smem_u32(sQ) + t * 32768, aKV = smem_u32(sKV), aP = smem_u32(sP) + t * 16384;
+      const uint32_t aQ = smem_u32(sQ) + t * 32768, aKV = smem_u32(sKV), aP = smem_u32(sP) + t * 32768;
       const uint32_t tm_s = tm + t * 64, tm_o = tm + 128 + t * 128;
       const int nbt = nb[t];
       bool ok = role_wait(&q_full, 0, &s_abort);
@@ -169,8 +169,9 @@ __global__ void __launch_bounds__(THREADS, 1) attn_fwd_2q_kernel(const __grid_co
         const uint32_t va = aKV + (j % STAGES) * 32768 + 16384;
 #pragma unroll
         for (int k = 0; k < KB / 16; ++k)
-          mma_bf16(tm_o, smem_desc(aP + k * 32, 16, 1024), smem_desc(va + k * 2048, 8192, 1024), id_o, (j | k) != 0);
-        mma_commit(&o_full[t]);
+          mma_bf16(tm_o, smem_desc(aP + (j & 1) * 16384 + k * 32, 16, 1024), smem_desc(va + k * 2048, 8192, 1024), id_o,
+                   (j | k) != 0);
+        mma_commit(&o_full[2 * t + (j & 1)]);
         mma_commit(&kv_empty[j % STAGES]);  // this tile's readers of the stage have been issued
         if (t == 0) ZC_TRACE(1, j, 3);
       }
@@ -185,7 +186,6 @@ __global__ void __launch_bounds__(THREADS, 1) attn_fwd_2q_kernel(const __grid_co
     const int nbt = nb[t];
     const uint32_t lane_base = (uint32_t)(quarter * 32);
     const uint32_t tm_s = tm + t * 64, tm_o = tm + 128 + t * 128;
-    uint8_t* tp = sP + t * 16384;
     const float sl2 = p.scale * LOG2E;
     float m_ref = -CUDART_INF_F, l = 0.f;
     bool fail = false;
@@ -231,12 +231,17 @@ __global__ void __launch_bounds__(THREADS, 1) attn_fwd_2q_kernel(const __grid_co
       }
       const float m_use = (m_ref == -CUDART_INF_F) ? 0.f : m_ref;
       if (tr) ZC_TRACE(0, j, 3);
-      if (j > 0) {
-        // the previous P_t V has completed: P_t may be overwritten and O_t may be rescaled
-        fail = !mbar_wait_parked(&o_full[t], (j - 1) & 1, &s_abort);
+      // P_t is double-buffered by block parity: block j's buffer was last read by P_t V of block
+      // j-2, which has long completed (the wait returns at once for j < 2)
+      uint8_t* tp = sP + (2 * t + (j & 1)) * 16384;
+      fail = !mbar_wait_parked(&o_full[2 * t + (j & 1)], ((j >> 1) & 1) ^ 1, &s_abort);
+      if (__any_sync(0xffffffffu, fail || s_abort)) { fail = true; break; }
+      if (j > 0 && __any_sync(0xffffffffu, raise)) {
+        // rescaling O_t has to wait for the P_t V of the previous block as well
+        fail = !mbar_wait_parked(&o_full[2 * t + ((j - 1) & 1)], ((j - 1) >> 1) & 1, &s_abort);
         if (__any_sync(0xffffffffu, fail || s_abort)) { fail = true; break; }
         tc_fence_after_sync();
-        if (__any_sync(0xffffffffu, raise)) {
+        {
 #pragma unroll 1
           for (int c = 0; c < D; c += 32) {
             uint32_t rr[32];
@@ -274,7 +279,7 @@ __global__ void __launch_bounds__(THREADS, 1) attn_fwd_2q_kernel(const __grid_co
     }
     if (fail) s_abort = 1;
     if (!fail && nbt > 0) {
-      fail = !mbar_wait_parked(&o_full[t], (nbt - 1) & 1, &s_abort);
+      fail = !mbar_wait_parked(&o_full[2 * t + ((nbt - 1) & 1)], ((nbt - 1) >> 1) & 1, &s_abort);
       if (__any_sync(0xffffffffu, fail)) {
         s_abort = 1;
       } else {
@@ -366,7 +371,7 @@ int zc_attn_fwd_2q(const void* q, const void* k, const void* v, void* o, float* 
   p.ncb = (S + 255) / 256;
   p.trace = g_trace;
   if (!p.status) return ERR_BAD_ARG;
-  const int smem = 65536 + STAGES * 32768 + 2 * 16384 + 1024;
+  const int smem = 65536 + STAGES * 32768 + 4 * 16384 + 1024;
   static bool attr = false;
   if (!attr) { cudaFuncSetAttribute(attn_fwd_2q_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); attr = true; }
   attn_fwd_2q_kernel<<<p.ncb * Hq * B, THREADS, smem, st>>>(mq, mk, mv, p);

@@ -16,7 +16,8 @@
 // Waits are bounded by wall time; on expiry the kernel records {code, peer, group} in the status
 // words of its own control block and returns normally, leaving the context usable.
 //
-// Peer memory is only touched with plain ld/st (st.release.sys for flags); no bulk-tensor copies.
+// Peer memory is only touched with plain ld/st (st.release.sys for flags) and, for the all-gather
+// payload where the buffer has an NVSwitch multicast mapping, multimem.st; no bulk-tensor copies.
 #include <cuda_bf16.h>
 
 #include "codec_v2_dev.cuh"
@@ -87,11 +88,28 @@ __device__ __forceinline__ void warp_copy16(uint8_t* dst, const uint8_t* src, in
     reinterpret_cast<uint4*>(dst)[i] = reinterpret_cast<const uint4*>(src)[i];
 }
 
+// NVSwitch multicast stores: one store to the multicast mapping of the symmetric buffer lands at the
+// same offset in every rank's copy (this rank's included), so an all-gather leaves the GPU once
+// instead of once per peer.  Values are moved as raw bits.
+__device__ __forceinline__ void mc_st128(void* mc_addr, const uint4& v) {
+  asm volatile("multimem.st.weak.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc_addr), "f"(__uint_as_float(v.x)),
+               "f"(__uint_as_float(v.y)), "f"(__uint_as_float(v.z)), "f"(__uint_as_float(v.w))
+               : "memory");
+}
+__device__ __forceinline__ void mc_st32(void* mc_addr, uint32_t v) {
+  asm volatile("multimem.st.weak.global.f32 [%0], %1;" ::"l"(mc_addr), "f"(__uint_as_float(v)) : "memory");
+}
+__device__ __forceinline__ void warp_copy16_mc(uint8_t* mc_dst, const uint8_t* src, int bytes, int lane) {
+  const int nv = (bytes + 15) >> 4;
+  for (int i = lane; i < nv; i += 32) mc_st128(mc_dst + 16 * i, reinterpret_cast<const uint4*>(src)[i]);
+}
+
 struct AgArgs {
   const uint16_t* in;     // this rank's shard, n elements
   uint16_t* out;          // world * n elements
   uint8_t* const* peers;  // device array of world buffer pointers
   uint8_t* local;         // == peers[rank]
+  uint8_t* mc;            // multicast mapping of the same buffer on all ranks, or null (per-peer stores)
   long long n;
   uint32_t seq;
   int push_ctas;
@@ -140,11 +158,17 @@ __global__ void __launch_bounds__(256) symm_all_gather_kernel(const AgArgs a) {
         const uint32_t hdr = v2_encode_chunk_hint(s, srec[warp], lane, hint, hint_esc);
         __syncwarp();
         const int used = v2_record_bytes(hdr);
-        for (int q = 0; q < L.world; ++q) {
-          if (q == L.rank) continue;
-          uint8_t* slot = slot_ptr(a.peers[q], L, parity, L.rank);
-          warp_copy16(slot + L.hdr_bytes + c * V2_SLOT_BYTES, srec[warp], used, lane);
-          if (lane == 0) reinterpret_cast<uint32_t*>(slot)[c] = hdr;
+        if (a.mc) {
+          uint8_t* slot = slot_ptr(a.mc, L, parity, L.rank);
+          warp_copy16_mc(slot + L.hdr_bytes + c * V2_SLOT_BYTES, srec[warp], used, lane);
+          if (lane == 0) mc_st32(reinterpret_cast<uint32_t*>(slot) + c, hdr);
+        } else {
+          for (int q = 0; q < L.world; ++q) {
+            if (q == L.rank) continue;
+            uint8_t* slot = slot_ptr(a.peers[q], L, parity, L.rank);
+            warp_copy16(slot + L.hdr_bytes + c * V2_SLOT_BYTES, srec[warp], used, lane);
+            if (lane == 0) reinterpret_cast<uint32_t*>(slot)[c] = hdr;
+          }
         }
         if (lane == 0) pushed += (unsigned long long)(used + 4) * (L.world - 1);
         __syncwarp();
@@ -481,13 +505,21 @@ __global__ void __launch_bounds__(256) symm_all_gather_int8_kernel(const AgArgs 
         }
         store_lane(own + e0, a.n - e0, own_al, dq);  // the source keeps what the others will see
         const uint4 q0 = make_uint4(qw[0], qw[1], qw[2], qw[3]), q1 = make_uint4(qw[4], qw[5], qw[6], qw[7]);
-        for (int q = 0; q < L.world; ++q) {
-          if (q == L.rank) continue;
-          uint8_t* slot = slot_ptr(a.peers[q], L, parity, L.rank);
-          uint4* dst = reinterpret_cast<uint4*>(slot + L.hdr_bytes + c * V2_SLOT_BYTES + lane * 32);
-          dst[0] = q0;
-          dst[1] = q1;
-          if (lane == 0) reinterpret_cast<uint32_t*>(slot)[c] = __float_as_uint(scale);
+        if (a.mc) {
+          uint8_t* slot = slot_ptr(a.mc, L, parity, L.rank);
+          uint8_t* dst = slot + L.hdr_bytes + c * V2_SLOT_BYTES + lane * 32;
+          mc_st128(dst, q0);
+          mc_st128(dst + 16, q1);
+          if (lane == 0) mc_st32(reinterpret_cast<uint32_t*>(slot) + c, __float_as_uint(scale));
+        } else {
+          for (int q = 0; q < L.world; ++q) {
+            if (q == L.rank) continue;
+            uint8_t* slot = slot_ptr(a.peers[q], L, parity, L.rank);
+            uint4* dst = reinterpret_cast<uint4*>(slot + L.hdr_bytes + c * V2_SLOT_BYTES + lane * 32);
+            dst[0] = q0;
+            dst[1] = q1;
+            if (lane == 0) reinterpret_cast<uint32_t*>(slot)[c] = __float_as_uint(scale);
+          }
         }
         if (lane == 0) pushed += (unsigned long long)(V2_CHUNK_ELEMS + 4) * (L.world - 1);
       }
@@ -572,15 +604,16 @@ long long zc_symm_buffer_bytes(int world, long long nc_max) {
 }
 
 // in: n bf16 elements; out: world*n; peers: device array of `world` buffer pointers
-int zc_symm_all_gather(const void* in, void* out, void* const* peers, void* local, long long n, int rank, int world,
-                       long long nc_max, unsigned seq, int push_ctas, int dec_ctas, double timeout_s,
+// mc: multicast mapping of the symmetric buffer (NVSwitch), or null to push with per-peer stores
+int zc_symm_all_gather(const void* in, void* out, void* const* peers, void* local, void* mc, long long n, int rank,
+                       int world, long long nc_max, unsigned seq, int push_ctas, int dec_ctas, double timeout_s,
                        cudaStream_t st) {
   using namespace zc;
   const long long nc = (n + V2_CHUNK_ELEMS - 1) / V2_CHUNK_ELEMS;
   if (world < 2 || world > 64 || nc > nc_max || nc == 0 || push_ctas < 1 || dec_ctas < 1) return ERR_BAD_ARG;
   AgArgs a;
   a.in = (const uint16_t*)in; a.out = (uint16_t*)out; a.peers = (uint8_t* const*)peers; a.local = (uint8_t*)local;
-  a.n = n; a.seq = seq; a.push_ctas = push_ctas;
+  a.mc = (uint8_t*)mc; a.n = n; a.seq = seq; a.push_ctas = push_ctas;
   a.timeout_ns = (unsigned long long)(timeout_s * 1e9);
   a.L = make_layout(world, rank, nc_max);
   symm_all_gather_kernel<<<push_ctas + dec_ctas, 256, 0, st>>>(a);
@@ -606,15 +639,15 @@ int zc_symm_reduce_scatter(const void* in, void* out, void* residual, void* cons
 
 // int8 variant of zc_symm_all_gather: three stream-ordered operations (clear the absmax word,
 // reduce max|x| over the shard, then the fused quantise/push/dequantise kernel)
-int zc_symm_all_gather_int8(const void* in, void* out, void* const* peers, void* local, long long n, int rank,
-                            int world, long long nc_max, unsigned seq, int push_ctas, int dec_ctas, double timeout_s,
-                            cudaStream_t st) {
+int zc_symm_all_gather_int8(const void* in, void* out, void* const* peers, void* local, void* mc, long long n,
+                            int rank, int world, long long nc_max, unsigned seq, int push_ctas, int dec_ctas,
+                            double timeout_s, cudaStream_t st) {
   using namespace zc;
   const long long nc = (n + V2_CHUNK_ELEMS - 1) / V2_CHUNK_ELEMS;
   if (world < 2 || world > 64 || nc > nc_max || nc == 0 || push_ctas < 1 || dec_ctas < 1) return ERR_BAD_ARG;
   AgArgs a;
   a.in = (const uint16_t*)in; a.out = (uint16_t*)out; a.peers = (uint8_t* const*)peers; a.local = (uint8_t*)local;
-  a.n = n; a.seq = seq; a.push_ctas = push_ctas;
+  a.mc = (uint8_t*)mc; a.n = n; a.seq = seq; a.push_ctas = push_ctas;
   a.timeout_ns = (unsigned long long)(timeout_s * 1e9);
   a.L = make_layout(world, rank, nc_max);
   uint32_t* word = reinterpret_cast<uint32_t*>(local) + CW_ABSMAX;

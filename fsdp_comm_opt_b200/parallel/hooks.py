@@ -68,10 +68,13 @@ class QuantizedAllGather(_CommBase):
 
     scale = max(absmax/127, 1e-8); q = clamp(round(x/scale), -127, 127); every rank contributes
     ``[4 B fp32 scale | numel int8]``; the gathered bytes are dequantised into ``output_tensor``.
-    On CUDA quantise+pack is one kernel that writes straight into this rank's slot of the gather
-    buffer and dequantise is one kernel over all slots (the reference issues about ten ATen
-    kernels and two staging copies).  Inputs smaller than ``min_quantize_numel`` or not floating
-    point are gathered raw.
+    On the ``"lib"`` transport quantise+pack is one kernel that writes straight into this rank's
+    slot of the gather buffer and dequantise is one kernel over all slots (the reference issues
+    about ten ATen kernels and two staging copies).  On the ``"symm"`` transport (bf16 on CUDA) one
+    kernel quantises, pushes the int8 bytes into the peers' symmetric staging buffers over NVLink
+    and dequantises what arrives; the source keeps the dequantised values too, so every rank ends
+    up with identical parameters.  Inputs smaller than ``min_quantize_numel`` or not floating point
+    are gathered raw.
     """
 
     def __init__(self, min_quantize_numel: int = 0, transport: str = "auto"):
@@ -83,11 +86,15 @@ class QuantizedAllGather(_CommBase):
         x = input_tensor.contiguous()
         if x.numel() < self.min_quantize_numel or not x.is_floating_point():
             return dist.all_gather_into_tensor(output_tensor, x, group=group, async_op=async_op)
+        if (world > 1 and x.dtype == torch.bfloat16 and output_tensor.dtype == torch.bfloat16
+                and _resolve_transport(self.transport, x.device, group) == "symm"):
+            from . import symm
+
+            return symm.channel_for(group, x.device, "ag-int8").all_gather(
+                output_tensor, x, mode="int8", async_op=async_op)
         rank = dist.get_rank(group)
         n = x.numel()
         stride = quant_ops.packed_bytes(n)
-        # the int8 payload travels through the collective library (NCCL / gloo); the fused
-        # symmetric-memory kernels carry the lossless codec only
         gathered = torch.empty(world, stride, dtype=torch.uint8, device=x.device)
         quant_ops.quantize_pack(x, gathered[rank])
         work = dist.all_gather_into_tensor(gathered.view(-1), gathered[rank], group=group,

@@ -23,6 +23,11 @@ def _ag_case(rank, world, transport):
     from fsdp_comm_opt_b200.parallel.hooks import ZipCCLAllGather
 
     dev = torch.device("cuda", rank)
+    if transport == "symm-unicast":          # per-peer stores
+        os.environ["ZC_SYMM_MULTICAST"] = "0"
+        transport = "symm"
+    elif transport == "symm":                # NVSwitch multicast stores where the fabric has them
+        os.environ["ZC_SYMM_MULTICAST"] = "1"
     hook = ZipCCLAllGather(transport=transport)
     sizes = [1 << 20, 777, 65536 * 3 + 5, 1 << 22, 4096, 1 << 20, (1 << 20) + 8]
     if transport == "symm":
@@ -57,9 +62,52 @@ def _ag_case(rank, world, transport):
             assert 0.6 * raw < pushed < 0.8 * raw, (pushed, raw)   # ~1.4 of 2 bytes per element
 
 
-@pytest.mark.parametrize("transport", ["symm", "lib"])
+@pytest.mark.parametrize("transport", ["symm", "symm-unicast", "lib"])
 def test_zip_all_gather_nccl_ranks(transport):
     run_ranks(_ag_case, WORLD, (transport,), backend="nccl")
+
+
+def _int8_case(rank, world):
+    """The fused int8 all-gather gives every rank (the source included) the values the NCCL-transport
+    hook gives, and both stay within the quantisation error of the inputs: half a step from the
+    rounding to int8 plus up to a quarter of a step from writing the result as bf16 (a value of
+    127 steps rounded to 8 mantissa bits)."""
+    import torch.distributed as dist
+    from fsdp_comm_opt_b200.parallel.hooks import QuantizedAllGather
+    from fsdp_comm_opt_b200.parallel import symm_impl
+
+    dev = torch.device("cuda", rank)
+    fused, lib = QuantizedAllGather(transport="symm"), QuantizedAllGather(transport="lib")
+    for it, n in enumerate([1 << 20, 1000, 65536 * 3 + 7, 1 << 22, 1 << 20]):
+        g = torch.Generator().manual_seed(31 * it + rank)
+        x = (torch.randn(n, generator=g) * (0.02 * (rank + 1))).to(torch.bfloat16).to(dev)
+        full = torch.zeros(world * n, dtype=torch.bfloat16, device=dev)
+        dist.all_gather_into_tensor(full, x)
+        a = torch.zeros(world * n, dtype=torch.bfloat16, device=dev)
+        b = torch.zeros(world * n, dtype=torch.bfloat16, device=dev)
+        if it % 2 == 0:                      # FSDP2 style: input is a view of the output
+            inp = a.narrow(0, n * rank, n)
+            inp.copy_(x)
+        else:
+            inp = x
+        w = fused(a, inp, dist.group.WORLD, async_op=(it % 2 == 1))
+        if w is not None:
+            w.wait()
+        lib(b, x, dist.group.WORLD)
+        torch.cuda.synchronize()
+        for r in range(world):
+            seg = slice(r * n, (r + 1) * n)
+            step = full[seg].float().abs().max().item() / 127.0
+            assert (a[seg].float() - full[seg].float()).abs().max().item() <= 0.76 * step + 1e-8, (it, r)
+            # same arithmetic on both transports; allow one quantisation step where x/scale rounds apart
+            assert (a[seg].float() - b[seg].float()).abs().max().item() <= 1.01 * step, (it, r)
+        assert (a != b).float().mean().item() < 1e-3
+    for ch in symm_impl.all_channels():
+        ch.check_status()
+
+
+def test_int8_all_gather_fused_matches_library_transport():
+    run_ranks(_int8_case, WORLD, backend="nccl")
 
 
 def _rs_case(rank, world, transport):
@@ -119,6 +167,7 @@ def _timeout_case(rank, world):
 
     dev = torch.device("cuda", rank)
     assert symm_impl.available(dist.group.WORLD)
+    os.environ["ZC_SYMM_MULTICAST"] = "0"   # failure paths are exercised on plain peer stores
     ch = symm_impl.channel_for(dist.group.WORLD, dev, "timeout-test")
     ch.timeout_s = 1.0
     n = 1 << 16
