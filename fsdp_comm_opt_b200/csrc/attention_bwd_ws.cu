@@ -17,6 +17,7 @@
 #include <math_constants.h>
 
 #include <cstdio>
+#include <type_traits>
 
 #include "launch_util.h"
 #include "umma.cuh"
@@ -386,6 +387,39 @@ __global__ void __launch_bounds__(256) dq_convert_kernel(const float* __restrict
   }
 }
 
+// fp32 accumulator kept transposed, [B, H, D, Sp] (queries contiguous, Sp = S rounded up to 4 so
+// that every stride is a multiple of 16 bytes), viewed as (S, D, H, B); box = 32 queries x 128 dims
+static bool make_map_dq_t(CUtensorMap* m, const void* base, int D, int H, int S, int Sp, int B) {
+  EncodeFn fn = encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[4] = {(cuuint64_t)S, (cuuint64_t)D, (cuuint64_t)H, (cuuint64_t)B};
+  cuuint64_t strides[3] = {(cuuint64_t)Sp * 4, (cuuint64_t)D * Sp * 4, (cuuint64_t)H * D * Sp * 4};
+  cuuint32_t box[4] = {32, (cuuint32_t)D, 1, 1};
+  cuuint32_t el[4] = {1, 1, 1, 1};
+  const CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<void*>(base), dims, strides, box, el,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) fprintf(stderr, "[zc_attn_bwd] transposed fp32 tensor map failed (%d)\n", (int)r);
+  return r == CUDA_SUCCESS;
+}
+
+// acc [B, H, D, Sp] fp32 -> dq [B, S, H, D] bf16 (element strides s_b, s_s, s_h), 32 x 32 tiles
+// transposed through shared memory; grid (ceil(S/32), D/32, B*H), block (32, 8)
+__global__ void __launch_bounds__(256) dq_convert_t_kernel(const float* __restrict__ acc, __nv_bfloat16* __restrict__ dq,
+                                                           int S, int Sp, int H, int D, int64_t s_b, int64_t s_s,
+                                                           int64_t s_h) {
+  __shared__ float tile[32][33];
+  const int q0 = blockIdx.x * 32, d0 = blockIdx.y * 32;
+  const int b = blockIdx.z / H, h = blockIdx.z % H;
+  const float* src = acc + ((int64_t)blockIdx.z * D + d0) * Sp + q0;
+  for (int dy = threadIdx.y; dy < 32; dy += 8)
+    tile[dy][threadIdx.x] = (q0 + (int)threadIdx.x < S) ? src[(int64_t)dy * Sp + threadIdx.x] : 0.f;
+  __syncthreads();
+  for (int qy = threadIdx.y; qy < 32; qy += 8)
+    if (q0 + qy < S)
+      dq[b * s_b + (int64_t)(q0 + qy) * s_s + h * s_h + d0 + threadIdx.x] = __float2bfloat16_rn(tile[threadIdx.x][qy]);
+}
+
 }  // namespace bws
 
 // =================================================================================================
@@ -397,8 +431,9 @@ __global__ void __launch_bounds__(256) dq_convert_kernel(const float* __restrict
 //   S^T  = K  Q^T   (128 keys x 64 queries)        dP^T = V dO^T
 //   P^T  = exp2(S^T c - lse[q]),  dS^T = P^T (dP^T - delta[q]) scale      (bf16, K-major A tiles)
 //   dV  += P^T dO,  dK += dS^T Q                   (accumulate in TMEM over all iterations)
-//   dQ^T = K^T dS^T (128 dims x 64 queries)        -> transposed through shared memory and added to
-//                                                     the fp32 accumulator by bulk tensor reductions
+//   dQ^T = K^T dS^T (128 dims x 64 queries)        -> staged in shared memory as it is and added by
+//                                                     bulk tensor reductions to an fp32 accumulator
+//                                                     that is kept transposed ([B, Hq, D, S])
 // so a 64-query tile is half the size (two Q/dO stages, two P^T/dS^T stages and the dQ staging
 // buffer fit beside K and V in 224 KB) and no operand needs a transpose.  The S^T/dP^T accumulators
 // are read into registers at once and released before the arithmetic, so the tensor core computes
@@ -455,7 +490,7 @@ __global__ void __launch_bounds__(352, 1) attn_bwd_kt_kernel(const __grid_consta
   uint8_t* sdO = smem + 98304;        // 2 stages
   uint8_t* sP = smem + 131072;        // 2 stages x [128 keys x 64 queries] bf16 (one slab)
   uint8_t* sdS = smem + 163840;       // 2 stages
-  uint8_t* sStage = smem + 196608;    // dQ staging: 4 slabs of [64 queries x 32 dims] fp32
+  uint8_t* sStage = smem + 196608;    // dQ staging: per query half, [128 dims x 32 queries] fp32, swizzled
   __shared__ uint64_t kv_full, qdo_full[2], qdo_empty[2], sdp_full, sdp_empty, pds_full[2], pds_empty[2], dq_full[2],
       dq_empty[2];
   __shared__ uint32_t tmem_base;
@@ -634,28 +669,34 @@ __global__ void __launch_bounds__(352, 1) attn_bwd_kt_kernel(const __grid_consta
         const float4* st_l = reinterpret_cast<const float4*>(&s_stat[st][c0]);
         const float4* st_d = reinterpret_cast<const float4*>(&s_stat[st][64 + c0]);
         uint32_t pk[16], dk_[16];
+        // two copies of the loop, so that blocks away from the diagonal carry no masking
+        // instructions at all (predicated-off instructions still take issue slots)
+        auto elementwise = [&](auto masked) {
 #pragma unroll
-        for (int g = 0; g < 8; ++g) {
-          const float4 l4 = st_l[g], d4 = st_d[g];
-          const float ls[4] = {l4.x, l4.y, l4.z, l4.w};
-          const float dl[4] = {d4.x, d4.y, d4.z, d4.w};
-          float e[4], ds[4];
+          for (int g = 0; g < 8; ++g) {
+            const float4 l4 = st_l[g], d4 = st_d[g];
+            const float ls[4] = {l4.x, l4.y, l4.z, l4.w};
+            const float dl[4] = {d4.x, d4.y, d4.z, d4.w};
+            float e[4], ds[4];
 #pragma unroll
-          for (int t = 0; t < 4; ++t) {
-            const int c = g * 4 + t;
-            float ev = exp2f(__uint_as_float(rs[c]) * sl2 - ls[t]);
-            if (diag) {
-              const int q = q0 + c0 + c;
-              if (key > q || key >= p.S || q >= p.S) ev = 0.f;
+            for (int t = 0; t < 4; ++t) {
+              const int c = g * 4 + t;
+              float ev = exp2f(__uint_as_float(rs[c]) * sl2 - ls[t]);
+              if (decltype(masked)::value) {
+                const int q = q0 + c0 + c;
+                if (key > q || key >= p.S || q >= p.S) ev = 0.f;
+              }
+              e[t] = ev;
+              ds[t] = ev * fmaf(__uint_as_float(rp[c]), p.scale, -dl[t]);
             }
-            e[t] = ev;
-            ds[t] = ev * fmaf(__uint_as_float(rp[c]), p.scale, -dl[t]);
+            pk[2 * g] = pack_bf16(e[0], e[1]);
+            pk[2 * g + 1] = pack_bf16(e[2], e[3]);
+            dk_[2 * g] = pack_bf16(ds[0], ds[1]);
+            dk_[2 * g + 1] = pack_bf16(ds[2], ds[3]);
           }
-          pk[2 * g] = pack_bf16(e[0], e[1]);
-          pk[2 * g + 1] = pack_bf16(e[2], e[3]);
-          dk_[2 * g] = pack_bf16(ds[0], ds[1]);
-          dk_[2 * g + 1] = pack_bf16(ds[2], ds[3]);
-        }
+        };
+        if (diag) elementwise(std::true_type{});
+        else elementwise(std::false_type{});
         if (tid == 64) ZC_BTRACE(0, i, 3);
         if (!mbar_wait_parked(&pds_empty[st], ph ^ 1, &s_abort)) fail = true;  // MMAs of iteration i-2 have read this stage
         if (tid == 64) ZC_BTRACE(0, i, 4);
@@ -689,17 +730,21 @@ __global__ void __launch_bounds__(352, 1) attn_bwd_kt_kernel(const __grid_consta
         uint32_t rr[32];
         tmem_ld32(tmem_addr(tm_dq + sj * QB, lane_base, c0), rr);
         tmem_ld_wait();
-        // this thread holds dQ^T[dim r][query c0 + t]; slab `quarter` of the staging buffer is
-        // [64 queries][32 dims] fp32, so a warp writes 32 consecutive floats per query
-        float* slab = reinterpret_cast<float*>(sStage + quarter * 8192);
+        // this thread holds dQ^T[dim r][query c0 .. c0+31]: 128 contiguous bytes of row r of the
+        // staging slab of its query half ([128 dims x 32 queries] fp32, 128-byte swizzle), which is
+        // also the layout of the accumulator ([B, Hq, D, S]: queries contiguous), so the drain is
+        // eight 16-byte stores per thread and no transpose
+        uint8_t* slab = sStage + half * 16384;
 #pragma unroll
-        for (int t = 0; t < 32; ++t) slab[(c0 + t) * 32 + lane] = __uint_as_float(rr[t]);
+        for (int t = 0; t < 8; ++t)
+          *reinterpret_cast<uint4*>(slab + sw128_off(r, t)) =
+              make_uint4(rr[4 * t], rr[4 * t + 1], rr[4 * t + 2], rr[4 * t + 3]);
         fence_proxy_async_smem();
         tc_fence_before_sync();
         if (named_bar_or(3, 256, fail || s_abort)) { aborted = true; break; }
         if (tid == 64) {
 #pragma unroll
-          for (int t = 0; t < 4; ++t) tma_reduce_add_4d(&mapdQ, sStage + t * 8192, t * 32, prev_h, prev_q0, b);
+          for (int t = 0; t < 2; ++t) tma_reduce_add_4d(&mapdQ, sStage + t * 16384, prev_q0 + t * 32, 0, prev_h, b);
           bulk_commit();
           mbar_arrive(&dq_empty[sj]);
           ZC_BTRACE(0, i, 7);
@@ -852,7 +897,8 @@ int zc_attn_bwd_kt(const void* q, const void* k, const void* v, const void* o, c
     if (cudaMalloc(&sc.status, sizeof(int)) != cudaSuccess) return ERR_BAD_ARG;
     cudaMemset(sc.status, 0, sizeof(int));
   }
-  const size_t need = (size_t)B * S * Hq * D * sizeof(float);
+  const int Sp = (S + 3) & ~3;  // row stride of the transposed accumulator: a multiple of 16 bytes
+  const size_t need = (size_t)B * Hq * D * Sp * sizeof(float);
   if (sc.dq_bytes < need) {
     if (sc.dq_acc) cudaFreeAsync(sc.dq_acc, st);
     if (cudaMallocAsync(&sc.dq_acc, need, st) != cudaSuccess) { sc.dq_acc = nullptr; sc.dq_bytes = 0; return (int)cudaGetLastError(); }
@@ -863,7 +909,7 @@ int zc_attn_bwd_kt(const void* q, const void* k, const void* v, const void* o, c
   if (!make_map4(&mq, q, D, Hq, S, B, qs0, qs1, qs2, bkt::QB) || !make_map4(&mk, k, D, Hkv, S, B, ks0, ks1, ks2) ||
       !make_map4(&mv, v, D, Hkv, S, B, vs0, vs1, vs2) ||
       !make_map4(&mdo, dout, D, Hq, S, B, (int64_t)S * Hq * D, (int64_t)Hq * D, D, bkt::QB) ||
-      !make_map4_f32(&mdq, sc.dq_acc, D, Hq, S, B, bkt::QB, false))
+      !make_map_dq_t(&mdq, sc.dq_acc, D, Hq, S, Sp, B))
     return ERR_BAD_ARG;
   BwdParams p;
   p.lse = lse; p.delta = delta; p.dq_acc = sc.dq_acc; p.dk = (__nv_bfloat16*)dk; p.dv = (__nv_bfloat16*)dv;
@@ -878,8 +924,8 @@ int zc_attn_bwd_kt(const void* q, const void* k, const void* v, const void* o, c
   if (!attr) { cudaFuncSetAttribute(bkt::attn_bwd_kt_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); attr = true; }
   const int nkb = (S + 127) / 128;
   bkt::attn_bwd_kt_kernel<<<nkb * Hkv * B, 352, smem, st>>>(mq, mk, mv, mdo, mdq, p, nkb);
-  const int cgrid = (int)std::min<int64_t>((rows * (D / 4) + 255) / 256, (int64_t)sm_count() * 16);
-  dq_convert_kernel<<<cgrid, 256, 0, st>>>(sc.dq_acc, (__nv_bfloat16*)dq, (int64_t)B * S, Hq, D, dqs1, dqs2);
+  dq_convert_t_kernel<<<dim3((S + 31) / 32, D / 32, B * Hq), dim3(32, 8), 0, st>>>(
+      sc.dq_acc, (__nv_bfloat16*)dq, S, Sp, Hq, D, dqs0, dqs1, dqs2);
   return launch_status();
 }
 

@@ -433,25 +433,53 @@ __global__ void __launch_bounds__(256) adamw_vec_kernel(TP* __restrict__ p, TG* 
                                                         float eps, float wd, float bc1, float rsqrt_bc2,
                                                         int zero_grad) {
   const float decay = 1.f - lr * wd, step = lr / bc1;
-  for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < nvec; i += (int64_t)gridDim.x * 256) {
-    float pf[8], gf[8], mf[8], vf[8];
-    load8<TP>(p + i * 8, pf);
-    load8<TG>(g + i * 8, gf);
-    load8<TS>(m + i * 8, mf);
-    load8<TS>(v + i * 8, vf);
+  auto update = [&](float (&pf)[8], const float (&gf)[8], float (&mf)[8], float (&vf)[8]) {
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
       mf[j] = mf[j] * b1 + (1.f - b1) * gf[j];
       vf[j] = vf[j] * b2 + (1.f - b2) * gf[j] * gf[j];
       pf[j] = pf[j] * decay - step * mf[j] / (sqrtf(vf[j]) * rsqrt_bc2 + eps);
     }
+  };
+  const float z[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  const int64_t stride = (int64_t)gridDim.x * 256;
+  int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
+  // two vectors per thread and trip: eight 16-byte loads in flight before the first use
+  for (; i + stride < nvec; i += 2 * stride) {
+    const int64_t k = i + stride;
+    float pf[8], gf[8], mf[8], vf[8], pf2[8], gf2[8], mf2[8], vf2[8];
+    load8<TP>(p + i * 8, pf);
+    load8<TG>(g + i * 8, gf);
+    load8<TS>(m + i * 8, mf);
+    load8<TS>(v + i * 8, vf);
+    load8<TP>(p + k * 8, pf2);
+    load8<TG>(g + k * 8, gf2);
+    load8<TS>(m + k * 8, mf2);
+    load8<TS>(v + k * 8, vf2);
+    update(pf, gf, mf, vf);
+    update(pf2, gf2, mf2, vf2);
     store8<TP>(p + i * 8, pf);
     store8<TS>(m + i * 8, mf);
     store8<TS>(v + i * 8, vf);
+    store8<TP>(p + k * 8, pf2);
+    store8<TS>(m + k * 8, mf2);
+    store8<TS>(v + k * 8, vf2);
     if (zero_grad) {
-      const float z[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
       store8<TG>(g + i * 8, z);
+      store8<TG>(g + k * 8, z);
     }
+  }
+  for (; i < nvec; i += stride) {
+    float pf[8], gf[8], mf[8], vf[8];
+    load8<TP>(p + i * 8, pf);
+    load8<TG>(g + i * 8, gf);
+    load8<TS>(m + i * 8, mf);
+    load8<TS>(v + i * 8, vf);
+    update(pf, gf, mf, vf);
+    store8<TP>(p + i * 8, pf);
+    store8<TS>(m + i * 8, mf);
+    store8<TS>(v + i * 8, vf);
+    if (zero_grad) store8<TG>(g + i * 8, z);
   }
 }
 
