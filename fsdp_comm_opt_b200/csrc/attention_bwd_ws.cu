@@ -403,21 +403,27 @@ static bool make_map_dq_t(CUtensorMap* m, const void* base, int D, int H, int S,
   return r == CUDA_SUCCESS;
 }
 
-// acc [B, H, D, Sp] fp32 -> dq [B, S, H, D] bf16 (element strides s_b, s_s, s_h), 32 x 32 tiles
-// transposed through shared memory; grid (ceil(S/32), D/32, B*H), block (32, 8)
+// acc [B, H, D, Sp] fp32 -> dq [B, S, H, D] bf16 (element strides s_b, s_s, s_h): tiles of 32 queries
+// x 64 dims transposed through shared memory (128-byte rows on both sides);
+// grid (ceil(S/32), D/64, B*H), block (32, 8)
 __global__ void __launch_bounds__(256) dq_convert_t_kernel(const float* __restrict__ acc, __nv_bfloat16* __restrict__ dq,
                                                            int S, int Sp, int H, int D, int64_t s_b, int64_t s_s,
                                                            int64_t s_h) {
-  __shared__ float tile[32][33];
-  const int q0 = blockIdx.x * 32, d0 = blockIdx.y * 32;
+  __shared__ float tile[64][33];
+  const int q0 = blockIdx.x * 32, d0 = blockIdx.y * 64;
   const int b = blockIdx.z / H, h = blockIdx.z % H;
   const float* src = acc + ((int64_t)blockIdx.z * D + d0) * Sp + q0;
-  for (int dy = threadIdx.y; dy < 32; dy += 8)
-    tile[dy][threadIdx.x] = (q0 + (int)threadIdx.x < S) ? src[(int64_t)dy * Sp + threadIdx.x] : 0.f;
+  const bool qok = q0 + (int)threadIdx.x < S;
+#pragma unroll
+  for (int dy = threadIdx.y; dy < 64; dy += 8) tile[dy][threadIdx.x] = qok ? src[(int64_t)dy * Sp + threadIdx.x] : 0.f;
   __syncthreads();
-  for (int qy = threadIdx.y; qy < 32; qy += 8)
-    if (q0 + qy < S)
-      dq[b * s_b + (int64_t)(q0 + qy) * s_s + h * s_h + d0 + threadIdx.x] = __float2bfloat16_rn(tile[threadIdx.x][qy]);
+#pragma unroll
+  for (int qy = threadIdx.y; qy < 32; qy += 8) {
+    if (q0 + qy < S) {
+      const __nv_bfloat162 v = __floats2bfloat162_rn(tile[2 * threadIdx.x][qy], tile[2 * threadIdx.x + 1][qy]);
+      *reinterpret_cast<__nv_bfloat162*>(dq + b * s_b + (int64_t)(q0 + qy) * s_s + h * s_h + d0 + 2 * threadIdx.x) = v;
+    }
+  }
 }
 
 }  // namespace bws
@@ -924,7 +930,7 @@ int zc_attn_bwd_kt(const void* q, const void* k, const void* v, const void* o, c
   if (!attr) { cudaFuncSetAttribute(bkt::attn_bwd_kt_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); attr = true; }
   const int nkb = (S + 127) / 128;
   bkt::attn_bwd_kt_kernel<<<nkb * Hkv * B, 352, smem, st>>>(mq, mk, mv, mdo, mdq, p, nkb);
-  dq_convert_t_kernel<<<dim3((S + 31) / 32, D / 32, B * Hq), dim3(32, 8), 0, st>>>(
+  dq_convert_t_kernel<<<dim3((S + 31) / 32, D / 64, B * Hq), dim3(32, 8), 0, st>>>(
       sc.dq_acc, (__nv_bfloat16*)dq, S, Sp, Hq, D, dqs0, dqs1, dqs2);
   return launch_status();
 }

@@ -117,13 +117,16 @@ __global__ void __launch_bounds__(RN_THREADS) rmsnorm_fwd_kernel(
 }
 
 // dx = rstd * (g - xhat * mean(g * xhat)) (+ dh),  g = dy * w,  xhat = h * rstd
-// dw += sum_rows dy * xhat   (fp32 atomics into dw32 once per CTA)
+// dw = sum_rows dy * xhat: every CTA keeps partial sums in registers over its rows and writes them
+// to its row of `partials` ([gridDim.x, cols] fp32), which rmsnorm_dw_reduce_kernel then sums
+// (one fp32 atomic per column and CTA instead was 2.4 M atomics on 4096 addresses per call and
+// took most of the kernel's time); with partials == nullptr the atomics into dw32 remain
 template <int MAXV>
 __global__ void __launch_bounds__(RN_THREADS) rmsnorm_bwd_kernel(
     const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ h,
     const __nv_bfloat16* __restrict__ w, const float* __restrict__ rstd_in,
     const __nv_bfloat16* __restrict__ dh, __nv_bfloat16* __restrict__ dx, float* __restrict__ dw32,
-    int64_t rows, int cols) {
+    float* __restrict__ partials, int64_t rows, int cols) {
   __shared__ float red[32];
   const int nvec = cols / 8;
   float wv[MAXV][8], dwacc[MAXV][8];
@@ -176,9 +179,39 @@ __global__ void __launch_bounds__(RN_THREADS) rmsnorm_bwd_kernel(
   for (int i = 0; i < MAXV; ++i) {
     const int v = threadIdx.x + i * RN_THREADS;
     if (v < nvec) {
+      if (partials) {
+        float4* dst = reinterpret_cast<float4*>(partials + (int64_t)blockIdx.x * cols + v * 8);
+        dst[0] = make_float4(dwacc[i][0], dwacc[i][1], dwacc[i][2], dwacc[i][3]);
+        dst[1] = make_float4(dwacc[i][4], dwacc[i][5], dwacc[i][6], dwacc[i][7]);
+      } else {
 #pragma unroll
-      for (int j = 0; j < 8; ++j) atomicAdd(dw32 + v * 8 + j, dwacc[i][j]);
+        for (int j = 0; j < 8; ++j) atomicAdd(dw32 + v * 8 + j, dwacc[i][j]);
+      }
     }
+  }
+}
+
+// dw[c] = sum over the CTAs' partial rows; block (32, 32): 32 float4 columns x 32 row groups
+__global__ void __launch_bounds__(1024) rmsnorm_dw_reduce_kernel(const float* __restrict__ partials, int nblocks,
+                                                                int cols, float* __restrict__ dw) {
+  __shared__ float4 acc[32][32];
+  const int c4 = blockIdx.x * 32 + threadIdx.x;  // float4 column
+  float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (c4 * 4 < cols) {
+    for (int r = threadIdx.y; r < nblocks; r += 32) {
+      const float4 v = __ldg(reinterpret_cast<const float4*>(partials + (int64_t)r * cols) + c4);
+      s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+    }
+  }
+  acc[threadIdx.y][threadIdx.x] = s;
+  __syncthreads();
+  if (threadIdx.y == 0 && c4 * 4 < cols) {
+#pragma unroll
+    for (int k = 1; k < 32; ++k) {
+      const float4 v = acc[k][threadIdx.x];
+      s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+    }
+    reinterpret_cast<float4*>(dw)[c4] = s;
   }
 }
 
@@ -534,19 +567,27 @@ int zc_rmsnorm_fwd(const void* x, const void* res, const void* w, void* y, void*
   return zc::launch_status();
 }
 
+// CTAs the backward launches for `rows` rows: the number of rows `partials` must have
+int zc_rmsnorm_bwd_ctas(int64_t rows) { return (int)std::min<int64_t>(rows, (int64_t)zc::sm_count() * 4); }
+
+// dw32: [cols] fp32.  With partials ([zc_rmsnorm_bwd_ctas(rows), cols] fp32) it is overwritten with
+// the column sums; with partials == nullptr it must be zero on entry and is accumulated with atomics.
 int zc_rmsnorm_bwd(const void* dy, const void* h, const void* w, const float* rstd, const void* dh, void* dx,
-                   float* dw32, int64_t rows, int cols, cudaStream_t st) {
+                   float* dw32, float* partials, int64_t rows, int cols, cudaStream_t st) {
   if (cols % 8 || cols > zc::RN_MAX_COLS) return ERR_UNSUPPORTED;
   if (rows == 0) return 0;
-  const int grid = (int)std::min<int64_t>(rows, (int64_t)zc::sm_count() * 4);
+  const int grid = zc_rmsnorm_bwd_ctas(rows);
   const int nvec = cols / 8;
 #define ZC_RN_BWD(V)                                                                                             \
   zc::rmsnorm_bwd_kernel<V><<<grid, zc::RN_THREADS, 0, st>>>((const bf16*)dy, (const bf16*)h, (const bf16*)w,    \
-                                                             rstd, (const bf16*)dh, (bf16*)dx, dw32, rows, cols)
+                                                             rstd, (const bf16*)dh, (bf16*)dx, dw32, partials,   \
+                                                             rows, cols)
   if (nvec <= zc::RN_THREADS) ZC_RN_BWD(1);
   else if (nvec <= 2 * zc::RN_THREADS) ZC_RN_BWD(2);
   else ZC_RN_BWD(4);
 #undef ZC_RN_BWD
+  if (partials)
+    zc::rmsnorm_dw_reduce_kernel<<<(cols / 4 + 31) / 32, dim3(32, 32), 0, st>>>(partials, grid, cols, dw32);
   return zc::launch_status();
 }
 

@@ -60,11 +60,15 @@ class _RMSNorm(torch.autograd.Function):
         if _use_cuda(h):
             dy2 = dy2.contiguous()
             dx = torch.empty_like(h)
-            dw32 = torch.zeros(cols, dtype=torch.float32, device=h.device)
+            lib = _lib.cuda()
+            dw32 = torch.empty(cols, dtype=torch.float32, device=h.device)
+            # one row of partial column sums per CTA, summed by a second small kernel
+            partials = torch.empty(int(lib.zc_rmsnorm_bwd_ctas(rows)), cols, dtype=torch.float32, device=h.device)
             dh2 = dh_out.reshape(rows, cols).contiguous() if dh_out is not None else None
-            _lib.check(_lib.cuda().zc_rmsnorm_bwd(
+            _lib.check(lib.zc_rmsnorm_bwd(
                 dy2.data_ptr(), h.data_ptr(), w.data_ptr(), rstd.data_ptr(), _lib.ptr(dh2),
-                dx.data_ptr(), dw32.data_ptr(), rows, cols, _lib.stream_ptr(h.device)), "zc_rmsnorm_bwd")
+                dx.data_ptr(), dw32.data_ptr(), partials.data_ptr(), rows, cols, _lib.stream_ptr(h.device)),
+                "zc_rmsnorm_bwd")
             dw = dw32.to(ctx.wdtype)
         else:
             hf, dyf, wf = h.float(), dy2.float(), w.float()

@@ -126,12 +126,10 @@ class Channel:
         # NVSwitch multicast mapping of the buffer (0 when the fabric or the driver has none): the
         # all-gather then stores its payload once instead of once per peer.  With two ranks there is
         # nothing to save (measured: 387 against 471 GB/s bus at 2^28 elements, because the store
-        # also lands in the sender's own copy), so the default uses it from four ranks on.
-        # ZC_SYMM_MULTICAST=1 / 0 forces it on / off.
+        # also lands in the sender's own copy); it pays from four ranks on.  It has been run on two
+        # ranks only so far, so it is opt-in: ZC_SYMM_MULTICAST=1 turns it on.
         mc = int(getattr(hdl, "multicast_ptr", 0) or 0)
-        want = os.environ.get("ZC_SYMM_MULTICAST", "auto")
-        use = (self.world >= 4) if want == "auto" else (want != "0")
-        self.mc_ptr = mc if use else 0
+        self.mc_ptr = mc if os.environ.get("ZC_SYMM_MULTICAST", "0") == "1" else 0
 
     def _next_seq(self) -> int:
         self.seq += 1
