@@ -70,8 +70,8 @@ def test_zip_all_gather_nccl_ranks(transport):
 def _int8_case(rank, world):
     """The fused int8 all-gather gives every rank (the source included) the values the NCCL-transport
     hook gives, and both stay within the quantisation error of the inputs: half a step from the
-    rounding to int8 plus up to a quarter of a step from writing the result as bf16 (a value of
-    127 steps rounded to 8 mantissa bits)."""
+    rounding to int8 plus up to half a step from writing the result as bf16 (a value of up to 127
+    steps rounded to 8 significant bits)."""
     import torch.distributed as dist
     from fsdp_comm_opt_b200.parallel.hooks import QuantizedAllGather
     from fsdp_comm_opt_b200.parallel import symm_impl
@@ -98,7 +98,7 @@ def _int8_case(rank, world):
         for r in range(world):
             seg = slice(r * n, (r + 1) * n)
             step = full[seg].float().abs().max().item() / 127.0
-            assert (a[seg].float() - full[seg].float()).abs().max().item() <= 0.76 * step + 1e-8, (it, r)
+            assert (a[seg].float() - full[seg].float()).abs().max().item() <= 1.0 * step + 1e-8, (it, r)
             # same arithmetic on both transports; allow one quantisation step where x/scale rounds apart
             assert (a[seg].float() - b[seg].float()).abs().max().item() <= 1.01 * step, (it, r)
         assert (a != b).float().mean().item() < 1e-3
