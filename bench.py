@@ -32,6 +32,8 @@ MODEL_SHAPES = {
     "llama2-13b": (32000, 5120, 40, 40, 40, 13824, 10000.0),
     "34b": (32000, 8192, 48, 64, 8, 22016, 1000000.0),
     "small": (32768, 1024, 4, 8, 2, 4096, 500000.0),
+    # GPT-2 family (rope_theta None): the reference's shipped run is GPT-2-XL, batch 2 per GPU, seq 1024
+    "gpt2-xl": (50257, 1600, 48, 25, 25, 6400, None),
 }
 
 
@@ -135,9 +137,17 @@ def make_reference(args, device, world):
     from transformers.models.llama.modeling_llama import LlamaRMSNorm
 
     v, d, L, H, Hkv, ffn, theta = MODEL_SHAPES[args.model]
-    cfg = LlamaConfig(vocab_size=v, hidden_size=d, intermediate_size=ffn, num_hidden_layers=L,
-                      num_attention_heads=H, num_key_value_heads=Hkv, max_position_embeddings=max(args.seq, 4096),
-                      rope_theta=theta, use_cache=False, tie_word_embeddings=False)
+    is_gpt2 = theta is None
+    if is_gpt2:
+        from transformers import GPT2Config
+
+        cfg = GPT2Config(vocab_size=v, n_embd=d, n_layer=L, n_head=H, n_inner=ffn, n_positions=max(args.seq, 1024),
+                         use_cache=False, resid_pdrop=0.0, embd_pdrop=0.0, attn_pdrop=0.0)
+    else:
+        cfg = LlamaConfig(vocab_size=v, hidden_size=d, intermediate_size=ffn, num_hidden_layers=L,
+                          num_attention_heads=H, num_key_value_heads=Hkv,
+                          max_position_embeddings=max(args.seq, 4096), rope_theta=theta, use_cache=False,
+                          tie_word_embeddings=False)
     with torch.device("meta"):
         model = AutoModelForCausalLM.from_config(cfg, dtype=torch.bfloat16)
     fsdp_config = dict(reshard_after_forward=True,
@@ -149,7 +159,7 @@ def make_reference(args, device, world):
 
         assert ref_zip.__file__.startswith(ref_root) and ref_comm.__file__.startswith(ref_root)
         hook_cls = ref_zip.ZipCCLAllGather if args.ref_variant == "zip" else ref_comm.QuantizedAllGather
-    layers = list(model.model.layers)
+    layers = list(model.transformer.h if is_gpt2 else model.model.layers)
     fl = []
     for dec in layers:
         m = fully_shard(dec, **fsdp_config)
@@ -168,12 +178,17 @@ def make_reference(args, device, world):
         for mod in model.modules():
             if isinstance(mod, (torch.nn.Linear, torch.nn.Embedding)):
                 torch.nn.init.normal_(mod.weight, mean=0.0, std=0.02)
-            elif isinstance(mod, LlamaRMSNorm):
+            elif isinstance(mod, (LlamaRMSNorm, torch.nn.LayerNorm)):
                 torch.nn.init.ones_(mod.weight)
-        hd = d // H
-        inv = 1.0 / (theta ** (torch.arange(0, hd, 2, dtype=torch.float32, device=device) / hd))
-        model.model.rotary_emb.inv_freq = inv
-        model.model.rotary_emb.original_inv_freq = inv.clone()
+            elif type(mod).__name__ == "Conv1D":  # GPT-2 projections
+                torch.nn.init.normal_(mod.weight, mean=0.0, std=0.02)
+            if getattr(mod, "bias", None) is not None and isinstance(mod.bias, torch.Tensor) and mod.bias.dim() == 1:
+                torch.nn.init.zeros_(mod.bias)
+        if not is_gpt2:
+            hd = d // H
+            inv = 1.0 / (theta ** (torch.arange(0, hd, 2, dtype=torch.float32, device=device) / hd))
+            model.model.rotary_emb.inv_freq = inv
+            model.model.rotary_emb.original_inv_freq = inv.clone()
     opt = torch.optim.AdamW(model.parameters(), lr=3e-5, fused=True)
     sched = torch.optim.lr_scheduler.CosineAnnealingLR(opt, T_max=1000, eta_min=3e-7)
 

@@ -29,6 +29,11 @@ def declare(lib) -> None:
     _sig(lib, "zc_rmsnorm_fwd", P, P, P, P, P, P, L, I, F, P)
     _sig(lib, "zc_rmsnorm_bwd", P, P, P, P, P, P, P, P, L, I, P)
     _sig(lib, "zc_rmsnorm_bwd_ctas", L)
+    _sig(lib, "zc_layernorm_fwd", P, P, P, P, P, P, L, I, F, P)
+    _sig(lib, "zc_layernorm_bwd_ctas", L)
+    _sig(lib, "zc_layernorm_bwd", P, P, P, P, P, P, P, P, L, I, P)
+    _sig(lib, "zc_bias_gelu_fwd", P, P, P, L, I, P)
+    _sig(lib, "zc_bias_gelu_bwd", P, P, P, P, L, I, P)
     _sig(lib, "zc_rope_inplace", P, P, P, L, I, I, I, I, F, P)
     _sig(lib, "zc_swiglu_fwd", P, P, L, I, P)
     _sig(lib, "zc_swiglu_bwd", P, P, P, L, I, P)

@@ -1,7 +1,8 @@
 """GPT-2-shape decoder (LayerNorm, learned positions, biased projections, tanh-GELU MLP, tied
 output embedding): the family of the reference's shipped run (run.sh:1, GPT-2-XL), discovered by
-the reference at ``model.transformer.h`` (train.py:99-100).  Attention, GEMMs, loss and the
-optimizer are the package's own ops; LayerNorm, GELU and bias adds use PyTorch elementwise ops.
+the reference at ``model.transformer.h`` (train.py:99-100).  Attention, GEMMs, LayerNorm, the fused
+bias + GELU of the MLP, the loss and the optimizer are the package's own ops; the remaining bias
+adds and residual adds are PyTorch elementwise ops.
 """
 from __future__ import annotations
 
@@ -13,7 +14,7 @@ import torch.nn.functional as F
 from torch.utils.checkpoint import checkpoint
 
 from ..ops import attention as attn_ops
-from ..ops import gemm, loss as loss_ops
+from ..ops import gemm, gpt2_ops, loss as loss_ops
 from .config import ModelConfig
 from .llama import CausalLMOutput
 
@@ -49,14 +50,16 @@ class GPT2Block(nn.Module):
         cfg = self.cfg
         B, S, d = x.shape
         H, hd = cfg.n_heads, cfg.head_dim
-        qkv = self.c_attn(self.ln_1(x)).view(B, S, 3 * H, hd)
+        ln1 = gpt2_ops.layer_norm(x, self.ln_1.weight, self.ln_1.bias, self.ln_1.eps)
+        qkv = self.c_attn(ln1).view(B, S, 3 * H, hd)
         if x.is_cuda and hd not in (64, 128):
             q, k, v = (t.transpose(1, 2) for t in qkv.split(H, dim=2))
             o = F.scaled_dot_product_attention(q, k, v, is_causal=True).transpose(1, 2).reshape(B, S, d)
         else:
             o = attn_ops.causal_attention(qkv, H, H).view(B, S, d)
         x = x + self.c_proj(o)
-        h = F.gelu(self.c_fc(self.ln_2(x)), approximate="tanh")
+        ln2 = gpt2_ops.layer_norm(x, self.ln_2.weight, self.ln_2.bias, self.ln_2.eps)
+        h = gpt2_ops.bias_gelu(gemm.linear(ln2, self.c_fc.weight), self.c_fc.bias)
         return x + self.c_mlp_proj(h)
 
 
@@ -95,7 +98,7 @@ class GPT2ForCausalLM(nn.Module):
                 x = checkpoint(blk, x, use_reentrant=False)
             else:
                 x = blk(x)
-        x = t.ln_f(x)
+        x = gpt2_ops.layer_norm(x, t.ln_f.weight, t.ln_f.bias, t.ln_f.eps)
         logits = gemm.linear(x, t.wte.weight)  # tied output embedding
         loss = None
         if labels is not None:

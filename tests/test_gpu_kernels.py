@@ -9,7 +9,7 @@ import torch.nn.functional as F
 pytestmark = pytest.mark.gpu
 
 from fsdp_comm_opt_b200 import _lib
-from fsdp_comm_opt_b200.ops import adamw, attention, codec, loss, norm, quant, rope, swiglu
+from fsdp_comm_opt_b200.ops import adamw, attention, codec, gpt2_ops, loss, norm, quant, rope, swiglu
 from zipccl import hopper_fastzip2 as hz
 
 DEV = "cuda"
@@ -364,6 +364,41 @@ def test_attention_with_fused_rope_matches_unfused():
     assert torch.allclose(qkv.grad.float(), qf.grad, atol=4e-2, rtol=4e-2)
 
 
+# ------------------------------------------------------------------ GPT-2 family ops
+@pytest.mark.parametrize("rows,cols", [(64, 1600), (300, 256), (17, 4096), (8, 8192)])
+def test_layernorm_fwd_bwd(rows, cols):
+    torch.manual_seed(21)
+    x = (torch.randn(rows, cols, device=DEV) * 2 + 0.5).bfloat16().requires_grad_()
+    w = (1 + 0.1 * torch.randn(cols, device=DEV)).bfloat16().requires_grad_()
+    b = (0.1 * torch.randn(cols, device=DEV)).bfloat16().requires_grad_()
+    y = gpt2_ops.layer_norm(x, w, b, 1e-5)
+    g = torch.randn_like(y)
+    y.backward(g)
+    xf, wf, bf = (t.detach().float().requires_grad_() for t in (x, w, b))
+    ref = F.layer_norm(xf, (cols,), wf, bf, 1e-5)
+    ref.backward(g.float())
+    assert torch.allclose(y.float(), ref, atol=3e-2, rtol=2e-2)
+    assert torch.allclose(x.grad.float(), xf.grad, atol=3e-2, rtol=3e-2), (x.grad.float() - xf.grad).abs().max().item()
+    assert torch.allclose(w.grad.float(), wf.grad, atol=0.02 * rows ** 0.5 + 0.05, rtol=3e-2)
+    assert torch.allclose(b.grad.float(), bf.grad, atol=0.02 * rows ** 0.5 + 0.05, rtol=3e-2)
+
+
+@pytest.mark.parametrize("rows,cols", [(128, 6400), (33, 1024)])
+def test_bias_gelu_fwd_bwd(rows, cols):
+    torch.manual_seed(22)
+    x = (torch.randn(rows, cols, device=DEV) * 1.5).bfloat16().requires_grad_()
+    b = (0.2 * torch.randn(cols, device=DEV)).bfloat16().requires_grad_()
+    y = gpt2_ops.bias_gelu(x, b)
+    g = torch.randn_like(y)
+    y.backward(g)
+    xf, bf = (t.detach().float().requires_grad_() for t in (x, b))
+    ref = F.gelu(xf + bf, approximate="tanh")
+    ref.backward(g.float())
+    assert torch.allclose(y.float(), ref, atol=2e-2, rtol=2e-2)
+    assert torch.allclose(x.grad.float(), xf.grad, atol=2e-2, rtol=2e-2)
+    assert torch.allclose(b.grad.float(), bf.grad, atol=0.02 * rows ** 0.5 + 0.05, rtol=3e-2)
+
+
 # ------------------------------------------------------------------ GEMM
 @pytest.mark.parametrize("M,N,K", [(128, 128, 128), (256, 512, 384), (4096, 1536, 1024), (384, 256, 4096), (128, 384, 128),
                                    (4096, 4096, 14336)])
@@ -409,3 +444,35 @@ def test_linear_autograd_on_tcgen05_matches_cublas():
     gemm.set_backend("auto")
     assert torch.allclose(gx.float(), x.grad.float(), atol=3e-2, rtol=3e-2)
     assert torch.allclose(gw.float(), w.grad.float(), atol=0.3, rtol=3e-2)
+
+
+# ------------------------------------------------------------------ whole models on the GPU
+@pytest.mark.parametrize("shape", ["tiny", "gpt2-tiny"])
+def test_model_forward_backward_matches_cpu(shape):
+    """One forward + backward of a tiny model of each family on the GPU kernels against the same
+    weights and tokens on the CPU reference paths of the ops."""
+    from fsdp_comm_opt_b200.models import build_model, get_config
+
+    cfg = get_config(shape)
+    torch.manual_seed(3)
+    ref = build_model(cfg).to(torch.bfloat16)
+    ref.init_weights()
+    gpu = build_model(cfg).to(torch.bfloat16)
+    gpu.load_state_dict(ref.state_dict())
+    gpu = gpu.to(DEV)
+    ids = torch.randint(0, cfg.vocab_size, (2, 128))
+    out_r = ref(input_ids=ids, labels=ids)
+    out_r.loss.backward()
+    out_g = gpu(input_ids=ids.to(DEV), labels=ids.to(DEV))
+    out_g.loss.backward()
+    torch.cuda.synchronize()
+    assert abs(out_g.loss.item() - out_r.loss.item()) < 5e-2, (out_g.loss.item(), out_r.loss.item())
+    checked = 0
+    for (n, pr), (_, pg) in zip(ref.named_parameters(), gpu.named_parameters()):
+        assert pg.grad is not None, n
+        gr, gg = pr.grad.float(), pg.grad.float().cpu()
+        assert torch.isfinite(gg).all(), n
+        denom = gr.abs().max().item() + 1e-6
+        assert (gg - gr).abs().max().item() / denom < 0.15, (n, (gg - gr).abs().max().item(), denom)
+        checked += 1
+    assert checked > 5

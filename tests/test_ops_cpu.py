@@ -150,3 +150,33 @@ def test_int8_quant_error_bound():
     for r in range(world):
         scale = (x * (r + 1)).abs().max() / 127
         assert (out[r * 1000:(r + 1) * 1000] - x * (r + 1)).abs().max() <= scale / 2 + 1e-7
+
+
+def test_gpt2_ops_cpu_paths_match_torch():
+    """CPU paths of layer_norm and bias_gelu (the arithmetic the CUDA kernels implement)."""
+    import torch.nn.functional as F
+
+    from fsdp_comm_opt_b200.ops import gpt2_ops
+
+    torch.manual_seed(5)
+    x = torch.randn(12, 64, requires_grad=True)
+    w = (1 + 0.1 * torch.randn(64)).requires_grad_()
+    b = (0.1 * torch.randn(64)).requires_grad_()
+    y = gpt2_ops.layer_norm(x, w, b, 1e-5)
+    g = torch.randn_like(y)
+    y.backward(g)
+    x2, w2, b2 = (t.detach().clone().requires_grad_() for t in (x, w, b))
+    ref = F.layer_norm(x2, (64,), w2, b2, 1e-5)
+    ref.backward(g)
+    for got, want in ((y, ref), (x.grad, x2.grad), (w.grad, w2.grad), (b.grad, b2.grad)):
+        assert torch.allclose(got, want, atol=1e-5, rtol=1e-4)
+    u = torch.randn(7, 32, requires_grad=True)
+    c = torch.randn(32, requires_grad=True)
+    z = gpt2_ops.bias_gelu(u, c)
+    gz = torch.randn_like(z)
+    z.backward(gz)
+    u2, c2 = u.detach().clone().requires_grad_(), c.detach().clone().requires_grad_()
+    zr = F.gelu(u2 + c2, approximate="tanh")
+    zr.backward(gz)
+    for got, want in ((z, zr), (u.grad, u2.grad), (c.grad, c2.grad)):
+        assert torch.allclose(got, want, atol=1e-5, rtol=1e-4)
