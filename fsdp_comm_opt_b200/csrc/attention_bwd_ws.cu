@@ -1,4 +1,6 @@
-// Warp-specialised causal GQA attention backward for sm_100a (the default backward path).
+// Causal GQA attention backward for sm_100a.  Two kernels: the warp-specialised kernel below (head
+// dimension 64, and 128 with ZC_ATTN_BWD=ws) and, further down, the key-row kernel that is the default
+// for head dimension 128.
 //
 // One CTA (320 threads) per (128-key block, kv head, batch); it loops over the query heads of the
 // group and over the query blocks at or below the diagonal, with dK and dV accumulating in TMEM.

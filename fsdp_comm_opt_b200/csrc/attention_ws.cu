@@ -1,4 +1,5 @@
-// Warp-specialised causal GQA attention forward for sm_100a (the default forward path).
+// Warp-specialised causal GQA attention forward for sm_100a: the path for head dimension 64 (and for
+// 128 with ZC_ATTN_FWD=ws; attention_fwd_2q.cu is the default there).
 //
 // One CTA (320 threads) per (128-query block, query head, batch):
 //   warp 0      TMA producer: Q once, then K/V tiles of 128 keys into a two-stage ring (4-D tensor
