@@ -476,3 +476,14 @@ def test_model_forward_backward_matches_cpu(shape):
         assert (gg - gr).abs().max().item() / denom < 0.15, (n, (gg - gr).abs().max().item(), denom)
         checked += 1
     assert checked > 5
+
+
+def test_device_status_check_is_clean_after_kernels():
+    """The host-side health check reads every kernel family's status word; after normal launches it
+    must find nothing (a wait that ran out would raise here instead of hanging the GPU)."""
+    from fsdp_comm_opt_b200.utils.health import check_device_status
+
+    qkv = (torch.randn(1, 256, 6, 128, device=DEV) * 0.5).bfloat16().requires_grad_()
+    attention.causal_attention(qkv, 4, 1).sum().backward()
+    torch.cuda.synchronize()
+    check_device_status()
