@@ -124,10 +124,10 @@ class Channel:
         self.peers_dev = hdl.buffer_ptrs_dev
         self.local_ptr = hdl.buffer_ptrs[self.rank]
         # NVSwitch multicast mapping of the buffer (0 when the fabric or the driver has none): the
-        # all-gather then stores its payload once instead of once per peer.  With two ranks there is
-        # nothing to save (measured: 387 against 471 GB/s bus at 2^28 elements, because the store
-        # also lands in the sender's own copy); it pays from four ranks on.  It has been run on two
-        # ranks only so far, so it is opt-in: ZC_SYMM_MULTICAST=1 turns it on.
+        # all-gather then stores its payload once instead of once per peer.  Measured at 2^28
+        # elements: 387 against 471 GB/s bus on two ranks (the store also lands in the sender's own
+        # copy) and 459 against 460 on eight (the receiving side's decode is the limit, not the
+        # bytes leaving the GPU), so it is opt-in: ZC_SYMM_MULTICAST=1 turns it on.
         mc = int(getattr(hdl, "multicast_ptr", 0) or 0)
         self.mc_ptr = mc if os.environ.get("ZC_SYMM_MULTICAST", "0") == "1" else 0
 
