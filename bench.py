@@ -103,7 +103,7 @@ def parse_args():
     ap.add_argument("--transport", default="auto", choices=["auto", "symm", "lib"])
     ap.add_argument("--no-compress", action="store_true", help="ours: stock NCCL collectives")
     ap.add_argument("--act-ckpt", action="store_true")
-    ap.add_argument("--gemm", default=None, choices=[None, "auto", "tcgen05", "cublas"])
+    ap.add_argument("--gemm", default=None, choices=[None, "auto", "tcgen05", "tcgen05_2sm", "cublas"])
     return ap.parse_args()
 
 

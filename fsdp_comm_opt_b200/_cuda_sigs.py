@@ -54,6 +54,7 @@ def declare(lib) -> None:
     _sig(lib, "zc_attn_fwd_2q_status_read_and_clear")
     _sig(lib, "zc_attn_bwd_kt", P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, *([L] * 18), F, P)
     _sig(lib, "zc_gemm_bf16", P, P, P, L, L, L, I, I, I, P)
+    _sig(lib, "zc_gemm_bf16_2sm", P, P, P, L, L, L, I, I, I, P)
     _sig(lib, "zc_gemm_status_read_and_clear")
     # fused collectives
     from ctypes import c_double, c_uint

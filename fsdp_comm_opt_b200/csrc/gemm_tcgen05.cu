@@ -246,6 +246,13 @@ static int* gemm_status(int dev) {
 
 extern "C" {
 
+// device pointer of the current device's GEMM status word (shared with the two-SM kernel)
+int* zc_gemm_status_word() {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  return zc::gemm_status(dev);
+}
+
 int zc_gemm_status_read_and_clear() {
   int dev = 0;
   cudaGetDevice(&dev);

@@ -6,6 +6,10 @@ Backends (``set_backend``):
                  elected thread, warp-specialised producer / MMA / epilogue, persistent over tiles.
                  Forward uses K-major operands; dgrad and wgrad use the MN-major descriptor forms,
                  so no transposed copy of the weight or the activations is made.
+  ``"tcgen05_2sm"``  the two-SM variant in ``csrc/gemm_tcgen05_2sm.cu`` (clusters of two CTAs,
+                 ``tcgen05.mma.cta_group::2`` on 256 x 256 tiles, B operand split between the pair) for
+                 shapes with M and N multiples of 256; other shapes fall back to ``"tcgen05"``.
+                 Compiled, not yet timed or verified on a GPU: never chosen by ``"auto"``.
   ``"cublas"``   ``torch.matmul`` (cuBLASLt), the plain library GEMM.
   ``"auto"``     cuBLAS.  The linear layers are plain GEMMs with nothing fused into them, and on
                  B200 the library's 2-SM kernels are 10-25 % faster than the 1-SM tcgen05 kernel
@@ -27,7 +31,7 @@ _BACKEND = os.environ.get("ZC_GEMM_BACKEND", "auto")
 
 def set_backend(name: str) -> None:
     global _BACKEND
-    if name not in ("auto", "tcgen05", "cublas"):
+    if name not in ("auto", "tcgen05", "tcgen05_2sm", "cublas"):
         raise ValueError(name)
     _BACKEND = name
 
@@ -41,7 +45,7 @@ def _tc_ok(M: int, N: int, K: int) -> bool:
 
 
 def _use_tc(a: torch.Tensor, M: int, N: int, K: int) -> bool:
-    if not a.is_cuda or a.dtype != torch.bfloat16 or _BACKEND != "tcgen05":
+    if not a.is_cuda or a.dtype != torch.bfloat16 or _BACKEND not in ("tcgen05", "tcgen05_2sm"):
         return False
     return _tc_ok(M, N, K)
 
@@ -59,7 +63,9 @@ def gemm(a: torch.Tensor, b: torch.Tensor, trans_a: bool, trans_b: bool,
         if out is None:
             out = torch.empty(M, N, dtype=a.dtype, device=a.device)
             accumulate = False
-        _lib.check(_lib.cuda().zc_gemm_bf16(
+        lib = _lib.cuda()
+        fn = lib.zc_gemm_bf16_2sm if (_BACKEND == "tcgen05_2sm" and M % 256 == 0 and N % 256 == 0) else lib.zc_gemm_bf16
+        _lib.check(fn(
             a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, int(trans_a), int(trans_b),
             int(accumulate), _lib.stream_ptr(a.device)), "zc_gemm_bf16")
         return out
