@@ -45,9 +45,20 @@ struct GemmParams {
   __nv_bfloat16* C;
   int64_t M, N, K;
   int a_major, b_major, accumulate;
-  int m_fast;  // 1: consecutive tiles walk m (B tile shared), 0: walk n (A tile shared)
+  int group_m;  // tiles are walked in bands of `group_m` m-tiles, n-major inside a band
   int* status;
 };
+
+// Tile order: bands of `group_m` m-tiles keep the tiles in flight a compact block of the output, so
+// the A rows and B columns they share stay in L2 however large K is.
+__device__ __forceinline__ void tile_coords(int64_t t, int64_t m_tiles, int64_t n_tiles, int group_m, int64_t& mi,
+                                            int64_t& ni) {
+  const int64_t per_band = (int64_t)group_m * n_tiles;
+  const int64_t band = t / per_band, r = t - band * per_band;
+  const int64_t rows = min((int64_t)group_m, m_tiles - band * group_m);
+  mi = band * group_m + r % rows;
+  ni = r / rows;
+}
 
 template <int BN>
 __global__ void __launch_bounds__(G_THREADS, 1) gemm_kernel(const __grid_constant__ CUtensorMap mapA,
@@ -90,8 +101,9 @@ __global__ void __launch_bounds__(G_THREADS, 1) gemm_kernel(const __grid_constan
     if (lane == 0) {
       uint32_t it = 0;
       for (int64_t t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
-        const int m0 = (int)(p.m_fast ? t % m_tiles : t / n_tiles) * G_BM;
-        const int n0 = (int)(p.m_fast ? t / m_tiles : t % n_tiles) * BN;
+        int64_t mi, ni;
+        tile_coords(t, m_tiles, n_tiles, p.group_m, mi, ni);
+        const int m0 = (int)mi * G_BM, n0 = (int)ni * BN;
         for (int64_t kb = 0; kb < k_blocks; ++kb, ++it) {
           const int s = it % G_STAGES;
           const uint32_t ph = (it / G_STAGES) & 1;
@@ -151,8 +163,9 @@ __global__ void __launch_bounds__(G_THREADS, 1) gemm_kernel(const __grid_constan
     for (int64_t t = blockIdx.x; t < tiles && ok; t += gridDim.x, ++tile_it) {
       const int acc = tile_it & 1;
       const uint32_t acc_ph = (tile_it >> 1) & 1;
-      const int64_t m0 = (p.m_fast ? t % m_tiles : t / n_tiles) * G_BM;
-      const int64_t n0 = (p.m_fast ? t / m_tiles : t % n_tiles) * BN;
+      int64_t mi, ni;
+      tile_coords(t, m_tiles, n_tiles, p.group_m, mi, ni);
+      const int64_t m0 = mi * G_BM, n0 = ni * BN;
       if (!(ok = mbar_wait(&acc_full[acc], acc_ph))) break;
       tc_fence_after_sync();
       const int64_t row = m0 + quarter * 32 + lane;
@@ -296,7 +309,10 @@ int zc_gemm_bf16(const void* A, const void* B, void* C, int64_t M, int64_t N, in
   GemmParams p;
   p.C = (__nv_bfloat16*)C; p.M = M; p.N = N; p.K = K;
   p.a_major = a_major; p.b_major = b_major; p.accumulate = accumulate;
-  p.m_fast = (M <= N) ? 1 : 0;  // re-stream the smaller operand, keep the larger one's tile resident
+  {
+    static const int forced = getenv("ZC_GEMM_GROUP_M") ? atoi(getenv("ZC_GEMM_GROUP_M")) : 0;
+    p.group_m = forced > 0 ? forced : 16;
+  }
   p.status = gemm_status(dev);
   if (!p.status) {
     fprintf(stderr, "[zc_gemm] could not allocate the status word on device %d\n", dev);
@@ -304,7 +320,8 @@ int zc_gemm_bf16(const void* A, const void* B, void* C, int64_t M, int64_t N, in
   }
   const int64_t tiles = (M / G_BM) * (N / BN);
   const int grid = (int)std::min<int64_t>(tiles, sm_count());
-  static bool attr[2] = {false, false};
+  static bool attr_all[64][2] = {{false, false}};  // per device
+  bool* attr = attr_all[dev & 63];
   if (BN == 256) {
     const int smem = G_STAGES * (16384 + 32768) + 1024;
     if (!attr[0]) { cudaFuncSetAttribute(gemm_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); attr[0] = true; }

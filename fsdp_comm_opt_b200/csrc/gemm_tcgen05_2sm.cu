@@ -1,28 +1,33 @@
-// Two-SM (cta_group::2) variant of the persistent bf16 GEMM: a cluster of two CTAs owns a 256 x 256
-// output tile.  Each CTA stages its own 128 rows of A and its own 128 of the tile's 256 columns of
-// B; one thread of the even CTA issues tcgen05.mma.cta_group::2 (M = 256, N = 256, K = 16), which
-// reads both CTAs' shared memory and accumulates each CTA's 128 rows into that CTA's TMEM.
+// Two-SM (cta_group::2) persistent bf16 GEMM for sm_100a: C[M,N] (+)= op(A) * op(B), fp32 accumulate.
 //
-// Why: a tcgen05.mma fetches its shared-memory operands at about 68 B per clock per SM (measured
-// with the 1-SM kernel and the attention kernels), so the 1-SM 128 x 256 tile (12 KB per K = 16
-// step) is operand-bound at ~190 clocks against 128 of tensor work.  With the B operand split
-// between the pair an SM fetches 8 KB per step (~118 clocks): the tile becomes tensor-bound.
+// A cluster of two CTAs owns a 256 x 256 output tile.  Each CTA stages its own 128 rows of A and its
+// own 128 of the tile's 256 columns of B; one thread of the even CTA issues
+// tcgen05.mma.cta_group::2 (M = 256, N = 256, K = 16), which reads both CTAs' shared memory and
+// accumulates each CTA's 128 rows into that CTA's TMEM.
 //
-//   warp 0      TMA producer (both CTAs): cp.async.bulk.tensor...cta_group::2 loads into the CTA's
+//   warp 0      TMA producer (both CTAs): cp.async.bulk.tensor ... cta_group::2 loads into the CTA's
 //               own stage buffers, transaction bytes counted on the even CTA's `full` barrier
 //   warp 1      even CTA: MMA issuer; commits arrive on the `empty` / `acc_full` barriers of both CTAs
 //   warps 2-5   epilogue (both CTAs): tcgen05.ld the CTA's 128 x 256 accumulator, convert, store;
 //               arrivals of both CTAs' epilogue warps free the accumulator on the even CTA
 // Every CTA fetches its own tiles with plain per-CTA TMA loads; no load is shared between CTAs.
-// Every wait is bounded; on expiry the status word is set and both CTAs reach the teardown.
 //
-// State: written against the 1-SM kernel and compiled for sm_100a; selected only by
-// ZC_GEMM_BACKEND=tcgen05_2sm (never by "auto").
+// The issuing thread is the scarce resource: one thread has to launch a 128-clock MMA every 128
+// clocks, so everything that can be is precomputed (stage-0 descriptors, remote barrier addresses)
+// and the operand layouts are template parameters; per MMA the loop adds a constant to the
+// descriptors and nothing else.
+//
+// Work is cut into units: whole tiles first, then the tiles of the last, partial wave are split
+// along K into `split` slices each, so that all clusters stay busy to the end.  A slice writes its
+// fp32 partial sums to a workspace and a small second kernel adds the slices and rounds to bf16.
+// Every wait is bounded; on expiry the status word is set and both CTAs reach the teardown.
 #include <cuda.h>
 #include <cuda_bf16.h>
 
 #include <algorithm>
 #include <cstdio>
+#include <cstdlib>
+#include <mutex>
 
 #include "launch_util.h"
 #include "umma.cuh"
@@ -33,6 +38,7 @@ using namespace umma;
 
 constexpr int BM_CTA = 128;   // rows of A per CTA (256 per cluster)
 constexpr int BN_CTA = 128;   // columns of B staged per CTA (256 per cluster)
+constexpr int BM = 256;
 constexpr int BN = 256;       // accumulator columns
 constexpr int BK = 64;
 constexpr int STAGES = 6;
@@ -40,6 +46,7 @@ constexpr int THREADS = 192;
 constexpr int A_BYTES = BM_CTA * BK * 2;  // 16 KB
 constexpr int B_BYTES = BN_CTA * BK * 2;  // 16 KB
 constexpr int STAGE = A_BYTES + B_BYTES;
+constexpr int MAX_SPLIT = 4;
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;
@@ -61,23 +68,12 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
 }
 // TMA load into this CTA's shared memory; the bytes are counted on the barrier at `bar_cluster_addr`
 // (the even CTA's `full` barrier)
-__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* map, uint32_t bar_cluster_addr,
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t smem_dst, const CUtensorMap* map, uint32_t bar_cluster_addr,
                                                  int c0, int c1) {
   asm volatile(
       "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-      ::"r"(smem_u32(smem_dst)), "l"(map), "r"(bar_cluster_addr), "r"(c0), "r"(c1)
+      ::"r"(smem_dst), "l"(map), "r"(bar_cluster_addr), "r"(c0), "r"(c1)
       : "memory");
-}
-__device__ __forceinline__ void tmem_alloc_pair(uint32_t* smem_dst, uint32_t ncols) {
-  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_dst)),
-               "r"(ncols)
-               : "memory");
-}
-__device__ __forceinline__ void tmem_relinquish_pair() {
-  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
-  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
 }
 __device__ __forceinline__ void mma_bf16_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
                                               uint32_t accumulate) {
@@ -96,15 +92,79 @@ __device__ __forceinline__ void mma_commit_pair(uint32_t cluster_addr) {
   asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_addr)
                : "memory");
 }
+__device__ __forceinline__ uint32_t mbar_addr_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok;
+}
+// bounded spin on a barrier given by its shared::cta address; the limit is only looked at on the slow path
+__device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  if (mbar_addr_try_wait(bar, parity)) return true;
+  const unsigned long long t0 = globaltimer_ns();
+  for (uint32_t it = 0;; ++it) {
+    if (mbar_addr_try_wait(bar, parity)) return true;
+    if ((it & 255u) == 255u && (*abort_flag || globaltimer_ns() - t0 > 2000000000ull)) return false;
+  }
+}
 
 struct Params {
   __nv_bfloat16* C;
+  float* partial;      // [tail tiles][split][256][256] fp32, or null when split == 1
   int64_t M, N, K;
-  int a_major, b_major, accumulate;
-  int m_fast;
+  int accumulate;
+  int group_m;         // tiles are walked in bands of `group_m` m-tiles, n-major inside a band
+  int64_t full_tiles;  // tiles computed whole; the remaining tiles are split along K
+  int split;           // K slices per tail tile (1: no tile is split)
   int* status;
 };
 
+// Tile order.  The clusters running at one time work on consecutive tile indices; walking bands of
+// `group_m` m-tiles keeps that set a compact block of the output, so the A rows and B columns it
+// needs together stay in L2 however large K is (a full column of m-tiles does not once M * K
+// outgrows the cache).
+__device__ __forceinline__ void tile_coords(int64_t t, int64_t m_tiles, int64_t n_tiles, int group_m, int64_t& mi,
+                                            int64_t& ni) {
+  const int64_t per_band = (int64_t)group_m * n_tiles;
+  const int64_t band = t / per_band, r = t - band * per_band;
+  const int64_t rows = min((int64_t)group_m, m_tiles - band * group_m);
+  mi = band * group_m + r % rows;
+  ni = r / rows;
+}
+
+// One unit of work: a tile and a range of its K blocks.
+struct Unit {
+  int64_t mi, ni;
+  int kb0, kb1;
+  int64_t slice;  // index of the fp32 partial slab, or -1 for a whole tile
+};
+__device__ __forceinline__ Unit unit_of(int64_t u, const Params& p, int64_t m_tiles, int64_t n_tiles, int k_blocks) {
+  Unit w;
+  int64_t t = u;
+  w.kb0 = 0;
+  w.kb1 = k_blocks;
+  w.slice = -1;
+  if (u >= p.full_tiles) {
+    const int64_t r = u - p.full_tiles;
+    t = p.full_tiles + r / p.split;
+    const int s = (int)(r % p.split);
+    const int per = (k_blocks + p.split - 1) / p.split;
+    w.kb0 = s * per;
+    w.kb1 = min(k_blocks, w.kb0 + per);
+    w.slice = r;
+  }
+  tile_coords(t, m_tiles, n_tiles, p.group_m, w.mi, w.ni);
+  return w;
+}
+
+template <int A_MAJOR, int B_MAJOR>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
     gemm_2sm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB, const Params p) {
   extern __shared__ uint8_t smem_raw[];
@@ -120,139 +180,168 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
       mbar_init(&empty[s], 1);   // one commit per use, on both CTAs
     }
     for (int a = 0; a < 2; ++a) {
-      mbar_init(&acc_full[a], 1);   // one commit per tile, on both CTAs
+      mbar_init(&acc_full[a], 1);   // one commit per unit, on both CTAs
       mbar_init(&acc_empty[a], 8);  // used on the even CTA: four epilogue warps of each CTA
     }
     mbar_fence_init();
     s_abort = 0;
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&mapA) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&mapB) : "memory");
   }
   if (warp == 1) {
-    tmem_alloc_pair(&tmem_base, 2 * BN);
-    tmem_relinquish_pair();
+    // each CTA allocates its own SM's whole TMEM (512 columns, so the base is column 0 in both)
+    tmem_alloc(&tmem_base, 2 * BN);
+    tmem_relinquish();
   }
   tc_fence_before_sync();
   __syncthreads();
   cluster_sync_all();  // both CTAs' barriers are initialised before any remote arrival
   tc_fence_after_sync();
   const uint32_t tm = tmem_base;
-  const int64_t m_tiles = p.M / (2 * BM_CTA), n_tiles = p.N / BN, k_blocks = p.K / BK;
+  const int64_t m_tiles = p.M / BM, n_tiles = p.N / BN;
+  const int k_blocks = (int)(p.K / BK);
   const int64_t tiles = m_tiles * n_tiles;
+  const int64_t units = p.full_tiles + (tiles - p.full_tiles) * p.split;
   const int64_t cluster_id = blockIdx.x >> 1, n_clusters = gridDim.x >> 1;
+  const uint32_t smem_base = smem_u32(smem);
+  const uint32_t full_base = smem_u32(&full[0]), empty_base = smem_u32(&empty[0]);
   bool ok = true;
 
   if (warp == 0) {
     if (lane == 0) {
-      uint32_t it = 0;
-      for (int64_t t = cluster_id; t < tiles && ok; t += n_clusters) {
-        const int m0 = (int)(p.m_fast ? t % m_tiles : t / n_tiles) * (2 * BM_CTA) + (int)rank * BM_CTA;
-        const int n0 = (int)(p.m_fast ? t / m_tiles : t % n_tiles) * BN + (int)rank * BN_CTA;
-        for (int64_t kb = 0; kb < k_blocks; ++kb, ++it) {
-          const int s = it % STAGES;
-          const uint32_t ph = (it / STAGES) & 1;
-          if (!(ok = mbar_wait_parked(&empty[s], ph ^ 1, &s_abort))) break;
-          uint8_t* sa = smem + s * STAGE;
-          uint8_t* sb = sa + A_BYTES;
-          const uint32_t full0 = map_to_cta(smem_u32(&full[s]), 0);
+      const uint32_t full0 = map_to_cta(full_base, 0);  // the even CTA's full[0]; full[s] is 8 s bytes on
+      uint32_t s = 0, ph = 0;
+      for (int64_t u = cluster_id; u < units && ok; u += n_clusters) {
+        const Unit w = unit_of(u, p, m_tiles, n_tiles, k_blocks);
+        const int m0 = (int)w.mi * BM + (int)rank * BM_CTA;
+        const int n0 = (int)w.ni * BN + (int)rank * BN_CTA;
+        for (int kb = w.kb0; kb < w.kb1; ++kb) {
+          if (!(ok = wait_bar(empty_base + 8 * s, ph ^ 1, &s_abort))) break;
+          const uint32_t sa = smem_base + s * STAGE, sb = sa + A_BYTES;
+          const uint32_t fb = full0 + 8 * s;
           if (rank == 0) mbar_expect_tx(&full[s], 2 * STAGE);  // both CTAs' bytes land on this barrier
-          const int k0 = (int)kb * BK;
-          if (p.a_major == MAJOR_K) {
-            tma_load_2d_pair(sa, &mapA, full0, k0, m0);
+          const int k0 = kb * BK;
+          if (A_MAJOR == MAJOR_K) {
+            tma_load_2d_pair(sa, &mapA, fb, k0, m0);
           } else {
 #pragma unroll
-            for (int sl = 0; sl < BM_CTA / 64; ++sl) tma_load_2d_pair(sa + sl * 8192, &mapA, full0, m0 + sl * 64, k0);
+            for (int sl = 0; sl < BM_CTA / 64; ++sl) tma_load_2d_pair(sa + sl * 8192, &mapA, fb, m0 + sl * 64, k0);
           }
-          if (p.b_major == MAJOR_K) {
-            tma_load_2d_pair(sb, &mapB, full0, k0, n0);
+          if (B_MAJOR == MAJOR_K) {
+            tma_load_2d_pair(sb, &mapB, fb, k0, n0);
           } else {
 #pragma unroll
-            for (int sl = 0; sl < BN_CTA / 64; ++sl) tma_load_2d_pair(sb + sl * 8192, &mapB, full0, n0 + sl * 64, k0);
+            for (int sl = 0; sl < BN_CTA / 64; ++sl) tma_load_2d_pair(sb + sl * 8192, &mapB, fb, n0 + sl * 64, k0);
           }
+          if (++s == STAGES) { s = 0; ph ^= 1; }
         }
       }
       if (!ok) s_abort = 1;
     }
   } else if (warp == 1) {
     if (lane == 0 && rank == 0) {
-      const uint32_t idesc = idesc_bf16(2 * BM_CTA, BN, p.a_major, p.b_major);
-      uint32_t it = 0, tile_it = 0;
-      for (int64_t t = cluster_id; t < tiles && ok; t += n_clusters, ++tile_it) {
-        const int acc = tile_it & 1;
-        const uint32_t acc_ph = (tile_it >> 1) & 1;
-        if (!(ok = mbar_wait_parked(&acc_empty[acc], acc_ph ^ 1, &s_abort))) break;
+      constexpr uint32_t idesc = idesc_bf16(BM, BN, A_MAJOR, B_MAJOR);
+      // descriptors of stage 0, K step 0; a stage adds STAGE >> 4, a K = 16 step adds KSTEP >> 4 to the
+      // start-address field (shared memory is below 256 KB, so the 14-bit field never carries)
+      const uint64_t a0 = (A_MAJOR == MAJOR_K) ? smem_desc(smem_base, 16, 1024) : smem_desc(smem_base, 8192, 1024);
+      const uint64_t b0 = (B_MAJOR == MAJOR_K) ? smem_desc(smem_base + A_BYTES, 16, 1024)
+                                               : smem_desc(smem_base + A_BYTES, 8192, 1024);
+      constexpr uint64_t A_KSTEP = ((A_MAJOR == MAJOR_K) ? 32 : 2048) >> 4;
+      constexpr uint64_t B_KSTEP = ((B_MAJOR == MAJOR_K) ? 32 : 2048) >> 4;
+      constexpr uint64_t STAGE_STEP = STAGE >> 4;
+      const uint32_t empty_c0 = map_to_cta(empty_base, 0), empty_c1 = map_to_cta(empty_base, 1);
+      const uint32_t accf_c0 = map_to_cta(smem_u32(&acc_full[0]), 0), accf_c1 = map_to_cta(smem_u32(&acc_full[0]), 1);
+      const uint32_t acce = smem_u32(&acc_empty[0]);
+      uint32_t s = 0, ph = 0, unit_it = 0;
+      for (int64_t u = cluster_id; u < units && ok; u += n_clusters, ++unit_it) {
+        const Unit w = unit_of(u, p, m_tiles, n_tiles, k_blocks);
+        const uint32_t acc = unit_it & 1, acc_ph = (unit_it >> 1) & 1;
+        if (!(ok = wait_bar(acce + 8 * acc, acc_ph ^ 1, &s_abort))) break;
         tc_fence_after_sync();
         const uint32_t d = tm + acc * BN;
-        for (int64_t kb = 0; kb < k_blocks; ++kb, ++it) {
-          const int s = it % STAGES;
-          const uint32_t ph = (it / STAGES) & 1;
-          if (!(ok = mbar_wait_parked(&full[s], ph, &s_abort))) break;
-          tc_fence_after_sync();
-          const uint32_t sa = smem_u32(smem + s * STAGE), sb = sa + A_BYTES;
+        uint32_t accum = 0;
+        for (int kb = w.kb0; kb < w.kb1; ++kb) {
+          if (!(ok = wait_bar(full_base + 8 * s, ph, &s_abort))) break;
+          const uint64_t da = a0 + s * STAGE_STEP, db = b0 + s * STAGE_STEP;
 #pragma unroll
           for (int k = 0; k < BK / 16; ++k) {
-            const uint64_t da = (p.a_major == MAJOR_K) ? smem_desc(sa + k * 32, 16, 1024)
-                                                       : smem_desc(sa + k * 2048, 8192, 1024);
-            const uint64_t db = (p.b_major == MAJOR_K) ? smem_desc(sb + k * 32, 16, 1024)
-                                                       : smem_desc(sb + k * 2048, 8192, 1024);
-            mma_bf16_pair(d, da, db, idesc, (kb | k) != 0);
+            mma_bf16_pair(d, da + k * A_KSTEP, db + k * B_KSTEP, idesc, accum);
+            accum = 1;
           }
           // the stage is reusable in both CTAs once these MMAs have read it
-          mma_commit_pair(map_to_cta(smem_u32(&empty[s]), 0));
-          mma_commit_pair(map_to_cta(smem_u32(&empty[s]), 1));
+          mma_commit_pair(empty_c0 + 8 * s);
+          mma_commit_pair(empty_c1 + 8 * s);
+          if (++s == STAGES) { s = 0; ph ^= 1; }
         }
         if (ok) {
-          mma_commit_pair(map_to_cta(smem_u32(&acc_full[acc]), 0));
-          mma_commit_pair(map_to_cta(smem_u32(&acc_full[acc]), 1));
+          mma_commit_pair(accf_c0 + 8 * acc);
+          mma_commit_pair(accf_c1 + 8 * acc);
         }
       }
       if (!ok) s_abort = 1;
     }
   } else {
     const int quarter = warp & 3;
-    uint32_t tile_it = 0;
-    for (int64_t t = cluster_id; t < tiles && ok; t += n_clusters, ++tile_it) {
-      const int acc = tile_it & 1;
-      const uint32_t acc_ph = (tile_it >> 1) & 1;
-      const int64_t m0 = (p.m_fast ? t % m_tiles : t / n_tiles) * (2 * BM_CTA) + (int64_t)rank * BM_CTA;
-      const int64_t n0 = (p.m_fast ? t / m_tiles : t % n_tiles) * BN;
-      ok = mbar_wait_parked(&acc_full[acc], acc_ph, &s_abort);
+    const uint32_t accf = smem_u32(&acc_full[0]);
+    const uint32_t acce_c0 = map_to_cta(smem_u32(&acc_empty[0]), 0);
+    uint32_t unit_it = 0;
+    for (int64_t u = cluster_id; u < units && ok; u += n_clusters, ++unit_it) {
+      const Unit w = unit_of(u, p, m_tiles, n_tiles, k_blocks);
+      const uint32_t acc = unit_it & 1, acc_ph = (unit_it >> 1) & 1;
+      ok = wait_bar(accf + 8 * acc, acc_ph, &s_abort);
       if (__any_sync(0xffffffffu, !ok)) { ok = false; break; }
       tc_fence_after_sync();
-      const int64_t row = m0 + quarter * 32 + lane;
-      __nv_bfloat16* crow = p.C + row * p.N + n0;
+      const int row_in_tile = (int)rank * BM_CTA + quarter * 32 + lane;
+      if (w.slice < 0) {
+        const int64_t row = w.mi * BM + row_in_tile;
+        __nv_bfloat16* crow = p.C + row * p.N + w.ni * BN;
 #pragma unroll 1
-      for (int c = 0; c < BN; c += 32) {
-        uint32_t r[32];
-        tmem_ld32(tmem_addr(tm + acc * BN, quarter * 32, c), r);
-        tmem_ld_wait();
+        for (int c = 0; c < BN; c += 32) {
+          uint32_t r[32];
+          tmem_ld32(tmem_addr(tm + acc * BN, quarter * 32, c), r);
+          tmem_ld_wait();
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          float f[8];
+          for (int q = 0; q < 4; ++q) {
+            float f[8];
 #pragma unroll
-          for (int j = 0; j < 8; ++j) f[j] = __uint_as_float(r[q * 8 + j]);
-          uint4* dst = reinterpret_cast<uint4*>(crow + c + q * 8);
-          if (p.accumulate) {
-            const uint4 old = *dst;
-            const __nv_bfloat162* ob = reinterpret_cast<const __nv_bfloat162*>(&old);
+            for (int j = 0; j < 8; ++j) f[j] = __uint_as_float(r[q * 8 + j]);
+            uint4* dst = reinterpret_cast<uint4*>(crow + c + q * 8);
+            if (p.accumulate) {
+              const uint4 old = *dst;
+              const __nv_bfloat162* ob = reinterpret_cast<const __nv_bfloat162*>(&old);
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const float2 o2 = __bfloat1622float2(ob[j]);
-              f[2 * j] += o2.x;
-              f[2 * j + 1] += o2.y;
+              for (int j = 0; j < 4; ++j) {
+                const float2 o2 = __bfloat1622float2(ob[j]);
+                f[2 * j] += o2.x;
+                f[2 * j + 1] += o2.y;
+              }
             }
+            uint4 v;
+            __nv_bfloat162 a0 = __floats2bfloat162_rn(f[0], f[1]), a1 = __floats2bfloat162_rn(f[2], f[3]);
+            __nv_bfloat162 a2 = __floats2bfloat162_rn(f[4], f[5]), a3 = __floats2bfloat162_rn(f[6], f[7]);
+            v.x = *reinterpret_cast<uint32_t*>(&a0);
+            v.y = *reinterpret_cast<uint32_t*>(&a1);
+            v.z = *reinterpret_cast<uint32_t*>(&a2);
+            v.w = *reinterpret_cast<uint32_t*>(&a3);
+            *dst = v;
           }
-          uint4 u;
-          __nv_bfloat162 a0 = __floats2bfloat162_rn(f[0], f[1]), a1 = __floats2bfloat162_rn(f[2], f[3]);
-          __nv_bfloat162 a2 = __floats2bfloat162_rn(f[4], f[5]), a3 = __floats2bfloat162_rn(f[6], f[7]);
-          u.x = *reinterpret_cast<uint32_t*>(&a0);
-          u.y = *reinterpret_cast<uint32_t*>(&a1);
-          u.z = *reinterpret_cast<uint32_t*>(&a2);
-          u.w = *reinterpret_cast<uint32_t*>(&a3);
-          *dst = u;
+        }
+      } else {
+        // K slice of a tail tile: fp32 partial sums, added up by gemm_2sm_fixup_kernel
+        float* prow = p.partial + (w.slice * BM + row_in_tile) * BN;
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 32) {
+          uint32_t r[32];
+          tmem_ld32(tmem_addr(tm + acc * BN, quarter * 32, c), r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int q = 0; q < 8; ++q)
+            reinterpret_cast<uint4*>(prow + c)[q] = make_uint4(r[4 * q], r[4 * q + 1], r[4 * q + 2], r[4 * q + 3]);
         }
       }
       tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty[acc]), 0));
+      if (lane == 0) mbar_arrive_cluster(acce_c0 + 8 * acc);
     }
     if (!ok) s_abort = 1;
   }
@@ -261,7 +350,44 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
   if (tid == 0 && s_abort) atomicExch(p.status, 8);
   // neither CTA may leave (or free its TMEM) while the pair's MMAs can still touch its memory
   cluster_sync_all();
-  if (warp == 1) tmem_dealloc_pair(tm, 2 * BN);
+  if (warp == 1) tmem_dealloc(tm, 2 * BN);
+}
+
+// C tile (+)= sum over the K slices of its fp32 partials, rounded once to bf16.
+__global__ void __launch_bounds__(256) gemm_2sm_fixup_kernel(const Params p, int64_t m_tiles, int64_t n_tiles) {
+  const int64_t tail = blockIdx.y;  // index among the split tiles
+  int64_t mi, ni;
+  tile_coords(p.full_tiles + tail, m_tiles, n_tiles, p.group_m, mi, ni);
+  const float* base = p.partial + tail * p.split * (int64_t)(BM * BN);
+  for (int i = blockIdx.x * 256 + threadIdx.x; i < BM * BN / 8; i += gridDim.x * 256) {
+    const int row = i / (BN / 8), c8 = i % (BN / 8);
+    float f[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int s = 0; s < p.split; ++s) {
+      const float4* src = reinterpret_cast<const float4*>(base + (int64_t)s * (BM * BN) + row * BN + c8 * 8);
+      const float4 x = src[0], y = src[1];
+      f[0] += x.x; f[1] += x.y; f[2] += x.z; f[3] += x.w;
+      f[4] += y.x; f[5] += y.y; f[6] += y.z; f[7] += y.w;
+    }
+    uint4* dst = reinterpret_cast<uint4*>(p.C + (mi * BM + row) * p.N + ni * BN + c8 * 8);
+    if (p.accumulate) {
+      const uint4 old = *dst;
+      const __nv_bfloat162* ob = reinterpret_cast<const __nv_bfloat162*>(&old);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 o2 = __bfloat1622float2(ob[j]);
+        f[2 * j] += o2.x;
+        f[2 * j + 1] += o2.y;
+      }
+    }
+    uint4 v;
+    __nv_bfloat162 a0 = __floats2bfloat162_rn(f[0], f[1]), a1 = __floats2bfloat162_rn(f[2], f[3]);
+    __nv_bfloat162 a2 = __floats2bfloat162_rn(f[4], f[5]), a3 = __floats2bfloat162_rn(f[6], f[7]);
+    v.x = *reinterpret_cast<uint32_t*>(&a0);
+    v.y = *reinterpret_cast<uint32_t*>(&a1);
+    v.z = *reinterpret_cast<uint32_t*>(&a2);
+    v.w = *reinterpret_cast<uint32_t*>(&a3);
+    *dst = v;
+  }
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -295,6 +421,40 @@ static bool make_map(CUtensorMap* m, const void* ptr, int64_t rows, int64_t cols
   return r == CUDA_SUCCESS;
 }
 
+// Per-device launch state: how many clusters of two the device runs at once, and the fp32 workspace
+// of the split tail (grown on demand, never shrunk; growing it is the only allocation this file
+// makes and it happens before the launch that needs it).
+struct DeviceState {
+  bool ready = false;
+  int clusters = 0;
+  float* partial = nullptr;
+  size_t partial_elems = 0;
+};
+static DeviceState g_state[64];
+static std::mutex g_mutex;
+
+template <int A_MAJOR, int B_MAJOR>
+static int max_clusters(int smem) {
+  cudaFuncSetAttribute(gemm_2sm_kernel<A_MAJOR, B_MAJOR>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * (sm_count() / 2));
+  cfg.blockDim = dim3(THREADS);
+  cfg.dynamicSmemBytes = smem;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeClusterDimension;
+  at[0].val.clusterDim.x = 2;
+  at[0].val.clusterDim.y = 1;
+  at[0].val.clusterDim.z = 1;
+  cfg.attrs = at;
+  cfg.numAttrs = 1;
+  int n = 0;
+  if (cudaOccupancyMaxActiveClusters(&n, gemm_2sm_kernel<A_MAJOR, B_MAJOR>, &cfg) != cudaSuccess || n <= 0) {
+    cudaGetLastError();
+    n = sm_count() / 2;
+  }
+  return std::min(n, sm_count() / 2);
+}
+
 }  // namespace g2
 }  // namespace zc
 
@@ -308,7 +468,7 @@ int zc_gemm_bf16_2sm(const void* A, const void* B, void* C, int64_t M, int64_t N
                      int accumulate, cudaStream_t st) {
   using namespace zc;
   using namespace zc::g2;
-  if (M <= 0 || N <= 0 || K <= 0 || M % (2 * BM_CTA) || N % BN || K % BK) return ERR_UNSUPPORTED;
+  if (M <= 0 || N <= 0 || K <= 0 || M % BM || N % BN || K % BK) return ERR_UNSUPPORTED;
   int* status = zc_gemm_status_word();
   if (!status) return ERR_BAD_ARG;
   if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(C)) & 15)
@@ -316,8 +476,10 @@ int zc_gemm_bf16_2sm(const void* A, const void* B, void* C, int64_t M, int64_t N
   int dev = 0;
   cudaGetDevice(&dev);
   cudaSetDevice(dev);
+  if (dev < 0 || dev >= 64) return ERR_BAD_ARG;
   const int a_major = trans_a ? MAJOR_MN : MAJOR_K;
   const int b_major = trans_b ? MAJOR_K : MAJOR_MN;
+  if (a_major == MAJOR_MN && b_major == MAJOR_K) return ERR_UNSUPPORTED;  // no layer GEMM has this form
   CUtensorMap mapA, mapB;
   bool ok;
   if (a_major == MAJOR_K) ok = make_map(&mapA, A, M, K, BK, BM_CTA);
@@ -325,18 +487,67 @@ int zc_gemm_bf16_2sm(const void* A, const void* B, void* C, int64_t M, int64_t N
   if (b_major == MAJOR_K) ok = ok && make_map(&mapB, B, N, K, BK, BN_CTA);
   else ok = ok && make_map(&mapB, B, K, N, 64, BK);
   if (!ok) return ERR_BAD_ARG;
+  const int smem = STAGES * STAGE + 1024;
+  DeviceState& ds = g_state[dev];
+  {
+    std::lock_guard<std::mutex> lock(g_mutex);
+    if (!ds.ready) {
+      int c = max_clusters<MAJOR_K, MAJOR_K>(smem);
+      c = std::min(c, max_clusters<MAJOR_K, MAJOR_MN>(smem));
+      c = std::min(c, max_clusters<MAJOR_MN, MAJOR_MN>(smem));
+      ds.clusters = c;
+      ds.ready = true;
+    }
+  }
   Params p;
   p.C = (__nv_bfloat16*)C; p.M = M; p.N = N; p.K = K;
-  p.a_major = a_major; p.b_major = b_major; p.accumulate = accumulate;
-  p.m_fast = (M <= N) ? 1 : 0;
+  p.accumulate = accumulate;
+  static const int forced_gm = getenv("ZC_GEMM_GROUP_M") ? atoi(getenv("ZC_GEMM_GROUP_M")) : 0;
+  static const int forced_split = getenv("ZC_GEMM_SPLIT") ? atoi(getenv("ZC_GEMM_SPLIT")) : -1;
+  p.group_m = forced_gm > 0 ? forced_gm : 8;
   p.status = status;
-  const int64_t tiles = (M / (2 * BM_CTA)) * (N / BN);
-  const int clusters = (int)std::min<int64_t>(tiles, sm_count() / 2);
-  const int smem = STAGES * STAGE + 1024;
-  static bool attr = false;
-  if (!attr) { cudaFuncSetAttribute(gemm_2sm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); attr = true; }
-  gemm_2sm_kernel<<<2 * clusters, THREADS, smem, st>>>(mapA, mapB, p);
-  return launch_status();
+  const int64_t tiles = (M / BM) * (N / BN);
+  const int64_t k_blocks = K / BK;
+  const int clusters = (int)std::min<int64_t>(tiles, ds.clusters);
+  // Tail: the tiles of the last, partial wave are cut into K slices so that every cluster has one
+  // unit of about the same length to finish with.
+  const int64_t rem = tiles % clusters;
+  int split = 1;
+  if (rem > 0 && tiles > clusters) {
+    split = (int)std::min<int64_t>(std::min<int64_t>(clusters / rem, MAX_SPLIT), k_blocks / 8);
+    if (forced_split >= 0) split = std::min(forced_split, MAX_SPLIT);
+    if (split < 2 || rem * 10 > (int64_t)clusters * 8) split = 1;  // a nearly full last wave is left alone
+  }
+  p.split = split;
+  p.full_tiles = split > 1 ? tiles - rem : tiles;
+  p.partial = nullptr;
+  if (split > 1) {
+    const size_t need = (size_t)rem * split * BM * BN;
+    std::lock_guard<std::mutex> lock(g_mutex);
+    if (ds.partial_elems < need) {
+      // earlier launches may still read the old buffer: drain the device before replacing it
+      if (ds.partial) { cudaDeviceSynchronize(); cudaFree(ds.partial); ds.partial = nullptr; ds.partial_elems = 0; }
+      const size_t want = std::max(need, (size_t)ds.clusters * BM * BN);
+      if (cudaMalloc(&ds.partial, want * sizeof(float)) != cudaSuccess) {
+        cudaGetLastError();
+        p.split = 1;
+        p.full_tiles = tiles;
+      } else {
+        ds.partial_elems = want;
+      }
+    }
+    p.partial = ds.partial;
+  }
+  const dim3 grid(2 * clusters);
+  if (a_major == MAJOR_K && b_major == MAJOR_K) gemm_2sm_kernel<MAJOR_K, MAJOR_K><<<grid, THREADS, smem, st>>>(mapA, mapB, p);
+  else if (a_major == MAJOR_K) gemm_2sm_kernel<MAJOR_K, MAJOR_MN><<<grid, THREADS, smem, st>>>(mapA, mapB, p);
+  else gemm_2sm_kernel<MAJOR_MN, MAJOR_MN><<<grid, THREADS, smem, st>>>(mapA, mapB, p);
+  int rc = launch_status();
+  if (rc == 0 && p.split > 1) {
+    gemm_2sm_fixup_kernel<<<dim3(16, (unsigned)rem), 256, 0, st>>>(p, M / BM, N / BN);
+    rc = launch_status();
+  }
+  return rc;
 }
 
 }  // extern "C"

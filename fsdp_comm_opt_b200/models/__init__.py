@@ -19,3 +19,20 @@ def decoder_layers(model):
     if hasattr(model, "model") and hasattr(model.model, "layers"):
         return model.model.layers
     raise ValueError("Unknown model structure")
+
+
+def shard_groups(model):
+    """Groups of the flat-shard engine in execution order: the embedding, one group per decoder
+    block, the head.  Parameters used at both ends of the step (tied output embedding, GPT-2's
+    tables and final LayerNorm, which its forward reads functionally) form one persistent group."""
+    from ..parallel.flat_shard import GroupSpec
+
+    layers = list(decoder_layers(model))
+    blocks = [GroupSpec(f"layers.{i}", [m]) for i, m in enumerate(layers)]
+    if hasattr(model, "transformer"):
+        t = model.transformer
+        return [GroupSpec("root", [t.wte, t.wpe, t.ln_f], persistent=True)] + blocks
+    if model.lm_head.weight is model.model.embed_tokens.weight:
+        return [GroupSpec("root", [model.model.embed_tokens, model.model.norm, model.lm_head], persistent=True)] + blocks
+    return ([GroupSpec("embed", [model.model.embed_tokens], backward_needs_params=False)] + blocks
+            + [GroupSpec("head", [model.model.norm, model.lm_head])])

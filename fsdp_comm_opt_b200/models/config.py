@@ -52,7 +52,48 @@ SHAPES: dict[str, ModelConfig] = {
 }
 
 
+# Hub ids the reference's ``-m`` flag is given (reference: run.sh:1, train.py:86-88) -> local shapes.
+HUB_ALIASES: dict[str, str] = {
+    "openai-community/gpt2-xl": "gpt2-xl",
+    "gpt2-xl": "gpt2-xl",
+    "meta-llama/meta-llama-3-8b": "llama3-8b",
+    "meta-llama/llama-3.1-8b": "llama3-8b",
+    "meta-llama/llama-2-13b-hf": "llama2-13b",
+    "codellama/codellama-34b-hf": "34b",
+}
+
+
+def config_from_hf_dict(d: dict) -> ModelConfig:
+    """A ``config.json`` of a HF Llama- or GPT-2-family checkpoint -> ``ModelConfig``."""
+    mt = d.get("model_type", "llama")
+    if mt == "gpt2":
+        dm = d["n_embd"]
+        return ModelConfig("gpt2", d["vocab_size"], dm, d["n_layer"], d["n_head"], d["n_head"],
+                           d.get("n_inner") or 4 * dm, d.get("n_positions", 1024),
+                           norm_eps=d.get("layer_norm_epsilon", 1e-5), tie_embeddings=True,
+                           init_std=d.get("initializer_range", 0.02))
+    return ModelConfig("llama", d["vocab_size"], d["hidden_size"], d["num_hidden_layers"], d["num_attention_heads"],
+                       d.get("num_key_value_heads", d["num_attention_heads"]), d["intermediate_size"],
+                       d.get("max_position_embeddings", 4096), d.get("rope_theta", 10000.0),
+                       d.get("rms_norm_eps", 1e-5), bool(d.get("tie_word_embeddings", False)),
+                       d.get("initializer_range", 0.02))
+
+
 def get_config(name: str) -> ModelConfig:
-    if name not in SHAPES:
-        raise KeyError(f"unknown model shape {name!r}; known: {sorted(SHAPES)}")
-    return SHAPES[name]
+    """A named shape, a hub id of one of them, or a local directory / ``config.json`` in HF format
+    (the reference resolves ``-m`` through ``AutoConfig.from_pretrained``, which also reads local
+    directories; reference: train.py:86-88)."""
+    import json
+    import os
+
+    if name in SHAPES:
+        return SHAPES[name]
+    alias = HUB_ALIASES.get(name.lower())
+    if alias is not None:
+        return SHAPES[alias]
+    path = os.path.join(name, "config.json") if os.path.isdir(name) else name
+    if os.path.isfile(path):
+        with open(path) as fp:
+            return config_from_hf_dict(json.load(fp))
+    raise KeyError(f"unknown model {name!r}; known shapes: {sorted(SHAPES)}, hub ids: {sorted(HUB_ALIASES)}, "
+                   "or a local directory with a HF config.json")

@@ -16,7 +16,7 @@ from torch.utils.checkpoint import checkpoint
 from ..ops import attention as attn_ops
 from ..ops import gemm, gpt2_ops, loss as loss_ops
 from .config import ModelConfig
-from .llama import CausalLMOutput
+from .llama import CausalLMOutput, Embedding
 
 
 class BiasLinear(nn.Module):
@@ -66,15 +66,10 @@ class GPT2Block(nn.Module):
 class GPT2Backbone(nn.Module):
     def __init__(self, cfg: ModelConfig):
         super().__init__()
-        self._std = cfg.init_std
-        self.wte = nn.Embedding(cfg.vocab_size, cfg.d_model)
-        self.wpe = nn.Embedding(cfg.max_seq, cfg.d_model)
+        self.wte = Embedding(cfg.vocab_size, cfg.d_model, cfg.init_std)
+        self.wpe = Embedding(cfg.max_seq, cfg.d_model, cfg.init_std)
         self.h = nn.ModuleList(GPT2Block(cfg) for _ in range(cfg.n_layers))
         self.ln_f = nn.LayerNorm(cfg.d_model, eps=cfg.norm_eps)
-
-    def reset_parameters(self):
-        nn.init.normal_(self.wte.weight, mean=0.0, std=self._std)
-        nn.init.normal_(self.wpe.weight, mean=0.0, std=self._std)
 
 
 class GPT2ForCausalLM(nn.Module):

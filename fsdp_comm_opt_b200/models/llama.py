@@ -41,6 +41,17 @@ class RMSNorm(nn.Module):
         return norm.rms_norm(x, self.weight, self.eps)
 
 
+class Embedding(nn.Embedding):
+    """Token / position table initialised with the model's ``init_std``."""
+
+    def __init__(self, num_embeddings: int, embedding_dim: int, init_std: float):
+        self.init_std = init_std
+        super().__init__(num_embeddings, embedding_dim)
+
+    def reset_parameters(self):
+        nn.init.normal_(self.weight, mean=0.0, std=self.init_std)
+
+
 class Linear(nn.Module):
     """Bias-free linear layer on the package GEMM."""
 
@@ -86,13 +97,9 @@ class LlamaBlock(nn.Module):
 class LlamaBackbone(nn.Module):
     def __init__(self, cfg: ModelConfig):
         super().__init__()
-        self.embed_tokens = nn.Embedding(cfg.vocab_size, cfg.d_model)
+        self.embed_tokens = Embedding(cfg.vocab_size, cfg.d_model, cfg.init_std)
         self.layers = nn.ModuleList(LlamaBlock(cfg) for _ in range(cfg.n_layers))
         self.norm = RMSNorm(cfg.d_model, cfg.norm_eps)
-        self._init_std = cfg.init_std
-
-    def reset_parameters(self):
-        nn.init.normal_(self.embed_tokens.weight, mean=0.0, std=self._init_std)
 
 
 class LlamaForCausalLM(nn.Module):
@@ -101,11 +108,9 @@ class LlamaForCausalLM(nn.Module):
         self.config = cfg
         self.model = LlamaBackbone(cfg)
         self.lm_head = Linear(cfg.d_model, cfg.vocab_size, cfg.init_std)
-        self.activation_checkpointing = False
-
-    def reset_parameters(self):
-        if self.config.tie_embeddings:
+        if cfg.tie_embeddings:
             self.lm_head.weight = self.model.embed_tokens.weight
+        self.activation_checkpointing = False
 
     def init_weights(self):
         """Calls ``reset_parameters`` on every submodule, as the reference does after

@@ -35,6 +35,17 @@ class FusedAdamW(torch.optim.Optimizer):
         self.zero_grad_in_step = zero_grad_in_step
         self.kernel_launches = 0
 
+    def ensure_state(self) -> None:
+        """Create the (zero) moments of every parameter that has none yet, so that a checkpoint can
+        be loaded into, or saved from, an optimizer that has not stepped."""
+        for group in self.param_groups:
+            for p in group["params"]:
+                st = self.state[p]
+                if len(st) == 0:
+                    st["step"] = torch.zeros((), dtype=torch.float32)
+                    st["exp_avg"] = torch.zeros_like(p, memory_format=torch.preserve_format)
+                    st["exp_avg_sq"] = torch.zeros_like(p, memory_format=torch.preserve_format)
+
     @torch.no_grad()
     def step(self, closure=None):
         loss = None

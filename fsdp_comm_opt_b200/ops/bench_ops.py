@@ -1,6 +1,10 @@
 """Device-timed micro-benchmarks of the hot kernels against their roofline denominators.
 
     python -m fsdp_comm_opt_b200.ops.bench_ops [--peaks MEASURED_PEAKS.json] [--only gemm,attn,codec,elt]
+        [--case SUBSTRING] [--gemm-backends tcgen05_2sm,tcgen05,cublas] [--iters N] [--warmup W]
+
+``--case`` keeps the cases whose name contains the substring; with ``--iters 1 --warmup 1`` and one
+backend the program launches a handful of kernels, which is the form to run under a profiler.
 
 Every number: >= 3 warm-up launches, CUDA events on the launching stream around ``iters`` launches,
 inputs larger than the 126 MB L2 or an L2 flush between launches (stated per line).  Fractions are
@@ -41,6 +45,9 @@ def main():
     ap.add_argument("--peaks", default="MEASURED_PEAKS.json")
     ap.add_argument("--only", default="gemm,attn,codec,elt")
     ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--case", default="", help="only cases whose name contains this")
+    ap.add_argument("--gemm-backends", default="tcgen05_2sm,tcgen05,cublas")
     args = ap.parse_args()
     if os.path.exists(args.peaks):
         pk = json.load(open(args.peaks))
@@ -56,22 +63,28 @@ def main():
 
     if "gemm" in only:
         shapes = [("fwd wgu", 4096, 28672, 4096, False, True), ("fwd wd", 4096, 4096, 14336, False, True),
-                  ("fwd qkv", 4096, 6144, 4096, False, True), ("dgrad wgu", 4096, 4096, 28672, False, False),
-                  ("wgrad wgu", 28672, 4096, 4096, True, False), ("lm_head", 4096, 128256, 4096, False, True),
+                  ("fwd qkv", 4096, 6144, 4096, False, True), ("fwd wo", 4096, 4096, 4096, False, True),
+                  ("dgrad wgu", 4096, 4096, 28672, False, False), ("dgrad wd", 4096, 14336, 4096, False, False),
+                  ("wgrad wgu", 28672, 4096, 4096, True, False), ("wgrad wd", 4096, 14336, 4096, True, False),
+                  ("lm_head", 4096, 128256, 4096, False, True), ("mid 4096x8192x4096", 4096, 8192, 4096, False, True),
                   ("square 8192", 8192, 8192, 8192, False, True)]
+        backends = [b for b in args.gemm_backends.split(",") if b]
         for name, M, N, K, ta, tb in shapes:
+            if args.case not in name:
+                continue
             a = torch.randn((K, M) if ta else (M, K), device=dev).bfloat16()
             b = torch.randn((N, K) if tb else (K, N), device=dev).bfloat16()
             out = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
             res = {}
-            for be in ("tcgen05", "cublas"):
+            for be in backends:
                 gemm.set_backend(be)
-                ms = _time(lambda: gemm.gemm(a, b, ta, tb, out=out), args.iters, flush=flush)
-                res[be] = 2.0 * M * N * K / ms / 1e9
+                ms = _time(lambda: gemm.gemm(a, b, ta, tb, out=out), args.iters, args.warmup, flush=flush)
+                res["tflops_" + be] = round(2.0 * M * N * K / ms / 1e9, 1)
             gemm.set_backend("auto")
-            emit(kernel="gemm_bf16", case=name, M=M, N=N, K=K, tflops_tcgen05=round(res["tcgen05"], 1),
-                 tflops_cublas=round(res["cublas"], 1), frac=round(res["tcgen05"] / tf, 3), frac_of=tag,
-                 l2="flushed between launches")
+            status = int(_lib.cuda().zc_gemm_status_read_and_clear())
+            ours = res.get("tflops_tcgen05_2sm", res.get("tflops_tcgen05"))
+            emit(kernel="gemm_bf16", case=name, M=M, N=N, K=K, **res, status=status,
+                 frac=round(ours / tf, 3) if ours else None, frac_of=tag, l2="flushed between launches")
     if "attn" in only:
         for B, S, Hq, Hkv, D in [(1, 4096, 32, 8, 128), (2, 4096, 40, 40, 128), (1, 8192, 32, 8, 128)]:
             qkv = (torch.randn(B, S, Hq + 2 * Hkv, D, device=dev) * 0.5).bfloat16().requires_grad_()

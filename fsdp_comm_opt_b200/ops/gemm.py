@@ -79,16 +79,24 @@ def gemm(a: torch.Tensor, b: torch.Tensor, trans_a: bool, trans_b: bool,
 
 
 class _Linear(torch.autograd.Function):
+    """``y = x w^T``.  The weight is kept by reference (not as a saved tensor): under the sharded
+    engines its storage is released after forward and gathered again before backward, and backward
+    must read whatever the parameter points at then.  When the weight carries ``main_grad`` (a view
+    of the engine's flat gradient buffer) the weight-gradient GEMM writes there directly and no
+    ``.grad`` tensor is produced."""
+
     @staticmethod
     def forward(ctx, x, w):
-        ctx.save_for_backward(x, w)
+        ctx.save_for_backward(x)
+        ctx.w = w
         x2 = x.reshape(-1, x.shape[-1])
         y = gemm(x2, w, False, True)           # [T,K] @ [N,K]^T
         return y.view(*x.shape[:-1], w.shape[0])
 
     @staticmethod
     def backward(ctx, dy):
-        x, w = ctx.saved_tensors
+        (x,) = ctx.saved_tensors
+        w = ctx.w
         x2 = x.reshape(-1, x.shape[-1])
         dy2 = dy.reshape(-1, dy.shape[-1])
         if not dy2.is_contiguous():
@@ -97,7 +105,12 @@ class _Linear(torch.autograd.Function):
         if ctx.needs_input_grad[0]:
             dx = gemm(dy2, w, False, False).view(x.shape)      # [T,N] @ [N,K]
         if ctx.needs_input_grad[1]:
-            dw = gemm(dy2, x2, True, False)                    # [T,N]^T @ [T,K]
+            mg = getattr(w, "main_grad", None)
+            if mg is not None and mg.dtype == dy2.dtype:
+                gemm(dy2, x2, True, False, out=mg, accumulate=bool(w.main_grad_written))
+                w.main_grad_written = True
+            else:
+                dw = gemm(dy2, x2, True, False)                # [T,N]^T @ [T,K]
         return dx, dw
 
 

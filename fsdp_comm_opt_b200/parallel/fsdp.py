@@ -52,6 +52,48 @@ def _install_hooks(m: FSDPModule, plan: FSDPPlan) -> None:
         plan.rs_hooks.append(rs)
 
 
+def make_hook_factories(plan: FSDPPlan, reduce_out_dtype: torch.dtype = torch.bfloat16):
+    """Constructors of one all-gather and one reduce-scatter hook per shard group for the flat-shard
+    engine, from the same flags ``apply_fsdp`` reads.  ``None`` means the plain library collective.
+    Every hook made is also listed in ``plan.ag_hooks`` / ``plan.rs_hooks``."""
+    ag = rs = None
+    if plan.quantize:
+        def ag():
+            hook = (ZipCCLAllGather(codec_version=plan.codec_version, transport=plan.transport) if plan.zip_ccl
+                    else QuantizedAllGather(transport=plan.transport))
+            plan.ag_hooks.append(hook)
+            return hook
+    if plan.compress_rs:
+        def rs():
+            hook = ZipCCLReduceScatter(error_feedback=plan.error_feedback, reduce_dtype=reduce_out_dtype,
+                                       transport=plan.transport)
+            plan.rs_hooks.append(hook)
+            return hook
+    return ag, rs
+
+
+def comm_report(plan: FSDPPlan) -> dict:
+    """What the installed hooks ran on so far: the transport each kind of hook resolved to, calls and
+    wire bytes per element of the fused channels (synchronises the device).  Raises when compression
+    was requested on CUDA with ``transport="symm"`` semantics expected but every call fell back."""
+    from . import symm_impl
+
+    rep: dict = {"all_gather": "library", "reduce_scatter": "library"}
+    if plan.ag_hooks:
+        rep["all_gather"] = sorted({getattr(h, "last_transport", None) or "not called" for h in plan.ag_hooks})
+    if plan.rs_hooks:
+        rep["reduce_scatter"] = sorted({getattr(h, "last_transport", None) or "not called" for h in plan.rs_hooks})
+    chans = {}
+    for ch in symm_impl.all_channels():
+        wire = ch.wire_bytes()
+        chans[ch.kind] = {"calls": ch.calls, "wire_bytes": wire,
+                          "wire_bytes_per_element": round(wire / ch.elements, 4) if ch.elements else None,
+                          "push_ctas": ch.push_ctas, "dec_ctas": ch.dec_ctas,
+                          "multicast": bool(getattr(ch, "mc_ptr", 0))}
+    rep["channels"] = chans
+    return rep
+
+
 def apply_fsdp(model: torch.nn.Module, plan: FSDPPlan) -> torch.nn.Module:
     # With bf16 parameters the gradients entering the reduce-scatter are bf16 values and FSDP2
     # casts the reduced result back to bf16.  The compressed reduce-scatter hook accumulates in

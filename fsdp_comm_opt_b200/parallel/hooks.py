@@ -45,7 +45,7 @@ def _resolve_transport(transport: str, device: torch.device, group) -> str:
         if transport == "symm":
             raise RuntimeError("the symmetric-memory transport needs CUDA tensors")
         return "lib"
-    from . import symm
+    from . import symm_impl as symm
 
     if transport == "symm":
         return "symm"
@@ -80,6 +80,7 @@ class QuantizedAllGather(_CommBase):
     def __init__(self, min_quantize_numel: int = 0, transport: str = "auto"):
         self.min_quantize_numel = min_quantize_numel
         self.transport = transport
+        self.last_transport: Optional[str] = None
 
     def __call__(self, output_tensor, input_tensor, group, async_op: bool = False):
         world = dist.get_world_size(group)
@@ -88,10 +89,12 @@ class QuantizedAllGather(_CommBase):
             return dist.all_gather_into_tensor(output_tensor, x, group=group, async_op=async_op)
         if (world > 1 and x.dtype == torch.bfloat16 and output_tensor.dtype == torch.bfloat16
                 and _resolve_transport(self.transport, x.device, group) == "symm"):
-            from . import symm
+            from . import symm_impl as symm
 
+            self.last_transport = "symm"
             return symm.channel_for(group, x.device, "ag-int8").all_gather(
                 output_tensor, x, mode="int8", async_op=async_op)
+        self.last_transport = "lib"
         rank = dist.get_rank(group)
         n = x.numel()
         stride = quant_ops.packed_bytes(n)
@@ -140,6 +143,7 @@ class ZipCCLAllGather(_CommBase):
         self.base_update_interval = max(1, base_update_interval)
         self.codec_version = codec_version
         self.transport = transport
+        self.last_transport: Optional[str] = None
         self._bases_cache: dict = {}
         self._base_update_steps: dict = {}
         self.last_wire_bytes: Optional[int] = None  # set on the lib/v1 path (host knows the sizes)
@@ -181,11 +185,12 @@ class ZipCCLAllGather(_CommBase):
                 output_tensor.view(-1)[: x.numel()].copy_(x.view(-1))
             return None
         transport = _resolve_transport(self.transport, x.device, group)
+        self.last_transport = transport
         version = self.codec_version
         if version == "auto":
             version = "v2" if (transport == "symm" or x.device.type == "cpu") else "v1"
         if transport == "symm":
-            from . import symm
+            from . import symm_impl as symm
 
             return symm.channel_for(group, x.device, "ag").all_gather(
                 output_tensor, x, mode="zip", async_op=async_op)
@@ -298,6 +303,7 @@ class ZipCCLReduceScatter(_CommBase):
         self.residual_dtype = residual_dtype
         self.transport = transport
         self._residual: Optional[torch.Tensor] = None
+        self.last_transport: Optional[str] = None
         self.last_wire_bytes: Optional[int] = None
 
     # -- residual -----------------------------------------------------------------------------
@@ -309,10 +315,16 @@ class ZipCCLReduceScatter(_CommBase):
         return self._residual
 
     def state_dict(self) -> dict:
-        return {"residual": None if self._residual is None else self._residual.detach().cpu()}
+        r = self._residual
+        return {"residual": None if r is None else r.detach().cpu(), "numel": None if r is None else r.numel()}
 
     def load_state_dict(self, state: dict, device=None) -> None:
         r = state.get("residual")
+        if r is not None and state.get("numel") not in (None, r.numel()):
+            raise ValueError("corrupt reduce-scatter residual: size field does not match the tensor")
+        if r is not None and self._residual is not None and self._residual.numel() != r.numel():
+            raise ValueError(f"residual of {r.numel()} elements does not fit this hook's bucket "
+                             f"({self._residual.numel()} elements)")
         self._residual = None if r is None else r.to(device or r.device)
 
     # -- call ----------------------------------------------------------------------------------
@@ -326,8 +338,9 @@ class ZipCCLReduceScatter(_CommBase):
         if x.dtype not in (torch.float32, torch.bfloat16) or x.numel() % world:
             raise TypeError("ZipCCLReduceScatter needs fp32 or bf16 input divisible by the world size")
         transport = _resolve_transport(self.transport, x.device, group)
+        self.last_transport = transport
         if transport == "symm":
-            from . import symm
+            from . import symm_impl as symm
 
             return symm.channel_for(group, x.device, "rs").reduce_scatter(
                 output_tensor, x, scale=scale, residual=self._residual_for(x), async_op=async_op)

@@ -11,13 +11,19 @@ host sync, no allocation.  The reference has no counterpart: all of its traffic 
 Sequence numbers: every call on a channel increments ``seq``; the kernels use ``seq & 1`` as the
 staging parity and wait (bounded) for the peers' ``done >= seq - 2`` before reusing a parity.
 
-Failure reporting: a device wait that runs out sets status words in the control block;
-``check_status()`` (synchronising) turns them into ``SymmTimeout``.  It is called from
-``AggregatedWork.wait`` on the async path and can be called by the training loop between steps.
+Failure reporting: a device wait that runs out sets status words in the control block and the
+library's per-device health word; the kernel then returns normally.  The fused AdamW kernel reads
+the health word on the device and leaves parameters and moments untouched when it is set, so a
+step whose collectives gave up is never applied, without any host synchronisation in the step.
+``check_status()`` (synchronising) turns the status words into ``SymmTimeout``; the training loop
+calls it where it synchronises anyway (next to the loss read) and before every checkpoint.
+The ``Work`` returned on the async path carries an event recorded on the launch stream, so
+``wait()`` orders the caller's stream after the kernel; it does not poll the status words.
 """
 from __future__ import annotations
 
 import ctypes
+import logging
 import os
 
 import torch
@@ -29,6 +35,8 @@ from .work import AggregatedWork
 
 _CHANNELS: dict = {}
 _AVAILABLE: dict = {}
+_WHY: dict = {}
+LOGGER = logging.getLogger("fsdp_comm_opt_b200.symm")
 
 CTRL_WORDS = 1024
 CW_STATUS, CW_STATUS_PEER, CW_STATUS_GROUP, CW_WIRE_LO = 65, 66, 67, 68
@@ -50,26 +58,46 @@ def _symm_mod():
 
 
 def available(group) -> bool:
-    """True when symmetric memory can be rendezvoused for ``group`` (probed once, collectively)."""
+    """True when symmetric memory can be rendezvoused for ``group`` (probed once, collectively).
+    ``why_unavailable(group)`` gives the reason after a False."""
     key = group.group_name if hasattr(group, "group_name") else str(group)
     if key in _AVAILABLE:
         return _AVAILABLE[key]
-    ok = False
-    try:
-        if dist.get_backend(group) == "nccl" and dist.get_world_size(group) > 1 and hasattr(
-                _lib.cuda()._lib, "zc_symm_all_gather"):
+    if os.environ.get("ZC_DISABLE_SYMM", "0") == "1" or not torch.cuda.is_available():
+        _AVAILABLE[key], _WHY[key] = False, "disabled by ZC_DISABLE_SYMM or no CUDA device"
+        return False
+    ok, why = False, ""
+    if dist.get_backend(group) != "nccl":
+        why = f"backend is {dist.get_backend(group)}, not nccl"
+    elif dist.get_world_size(group) < 2:
+        why = "world size 1"
+    elif not hasattr(_lib.cuda()._lib, "zc_symm_all_gather"):
+        why = "libzc_cuda.so has no fused collective kernels"
+    else:
+        try:
             symm_mem = _symm_mod()
             t = symm_mem.empty(4096, dtype=torch.uint8, device=torch.device("cuda", torch.cuda.current_device()))
             hdl = symm_mem.rendezvous(t, group)
             ok = hdl is not None and len(hdl.buffer_ptrs) == dist.get_world_size(group)
-    except Exception:
-        ok = False
+            if not ok:
+                why = "rendezvous returned no peer pointers"
+        except (RuntimeError, ImportError, AttributeError, NotImplementedError) as e:
+            why = f"{type(e).__name__}: {e}"
     # every rank must agree, otherwise some would wait in a kernel for peers that use NCCL
     flag = torch.tensor([1 if ok else 0], device=torch.device("cuda", torch.cuda.current_device()))
     dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=group)
-    ok = bool(flag.item())
-    _AVAILABLE[key] = ok
-    return ok
+    agreed = bool(flag.item())
+    if ok and not agreed:
+        why = "another rank could not rendezvous symmetric memory"
+    if not agreed:
+        LOGGER.warning("symmetric-memory transport unavailable: %s", why)
+    _AVAILABLE[key], _WHY[key] = agreed, why
+    return agreed
+
+
+def why_unavailable(group) -> str:
+    key = group.group_name if hasattr(group, "group_name") else str(group)
+    return _WHY.get(key, "")
 
 
 class Channel:
@@ -81,7 +109,11 @@ class Channel:
         self.nc_max = 0
         self.buf = None
         self.hdl = None
-        self.timeout_s = float(os.environ.get("ZC_SYMM_TIMEOUT_S", "5"))
+        # a peer may lag by a checkpoint write or a profiler flush; NCCL would simply wait, so the
+        # bound is generous (tests set ``timeout_s`` to a second)
+        self.timeout_s = float(os.environ.get("ZC_SYMM_TIMEOUT_S", "120"))
+        self.calls = 0
+        self.elements = 0
         sm = torch.cuda.get_device_properties(device).multi_processor_count
         # The codec is integer-ALU work, the GEMMs it overlaps with are tensor-pipe work, and a
         # collective CTA needs only 16 KB of shared memory, so two of them fit beside a GEMM CTA on
@@ -170,9 +202,14 @@ class Channel:
             x.data_ptr(), output_tensor.data_ptr(), self.peers_dev, self.local_ptr, self.mc_ptr or None, n, self.rank,
             self.world, self.nc_max, seq, self.push_ctas, self.dec_ctas, self.timeout_s,
             _lib.stream_ptr(self.device)), "zc_symm_all_gather")
-        if not async_op:
-            return None
-        return AggregatedWork([], status_fn=None)
+        self.calls += 1
+        self.elements += n * (self.world - 1)
+        return self._work() if async_op else None
+
+    def _work(self) -> AggregatedWork:
+        ev = torch.cuda.Event()
+        ev.record(torch.cuda.current_stream(self.device))
+        return AggregatedWork([], ready_event=ev)
 
     def reduce_scatter(self, output_tensor: torch.Tensor, x: torch.Tensor, scale: float, residual, async_op=False):
         shard = x.numel() // self.world
@@ -187,9 +224,9 @@ class Channel:
             self.rank, self.world, self.nc_max, seq, int(x.dtype == torch.float32),
             int(output_tensor.dtype == torch.float32), float(scale), self.push_ctas, self.dec_ctas,
             self.timeout_s, _lib.stream_ptr(self.device)), "zc_symm_reduce_scatter")
-        if not async_op:
-            return None
-        return AggregatedWork([], status_fn=None)
+        self.calls += 1
+        self.elements += shard * (self.world - 1)
+        return self._work() if async_op else None
 
 
 def channel_for(group, device: torch.device, kind: str) -> Channel:

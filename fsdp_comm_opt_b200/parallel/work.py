@@ -11,6 +11,10 @@ Same constructor and the same eight methods as the reference class
   work is CPU-only.  ``synchronize()`` is the explicit host-blocking form.
 * an optional ``status_fn`` is polled after completion so that a device-side bounded wait that
   gave up (fused symmetric-memory kernels) surfaces as a Python exception.
+* an optional ``ready_event`` (recorded by the caller on the stream that launched the device work)
+  ties the Work to that stream: ``wait`` / ``block_current_stream`` make the *current* stream wait
+  for it and ``is_completed`` reports ``event.query()``, so a caller on another stream is ordered
+  after a collective that is one kernel launch with no child ``Work`` at all.
 """
 from __future__ import annotations
 
@@ -24,8 +28,10 @@ import torch.distributed as dist
 
 class AggregatedWork(dist.Work):
     def __init__(self, works: Iterable[dist.Work], postprocess_fn: Optional[Callable[[], None]] = None,
-                 *, status_fn: Optional[Callable[[], None]] = None):
+                 *, status_fn: Optional[Callable[[], None]] = None,
+                 ready_event: Optional["torch.cuda.Event"] = None):
         super().__init__()
+        self.ready_event = ready_event
         self.works = [w for w in works if w is not None]
         self.postprocess_fn = postprocess_fn
         self.status_fn = status_fn
@@ -65,6 +71,8 @@ class AggregatedWork(dist.Work):
             return True
         if not all(w.is_completed() for w in self.works):
             return False
+        if self.ready_event is not None and not self.ready_event.query():
+            return False
         try:
             self._run_postprocess_once()
         except BaseException:
@@ -87,6 +95,11 @@ class AggregatedWork(dist.Work):
         try:
             for w in self.works:
                 self._child_wait(w, timeout)
+            if self.ready_event is not None:
+                if timeout is not None:
+                    self.ready_event.synchronize()
+                else:
+                    torch.cuda.current_stream().wait_event(self.ready_event)
             self._run_postprocess_once()
             if self._event is not None:
                 if timeout is not None:
@@ -103,6 +116,8 @@ class AggregatedWork(dist.Work):
     def synchronize(self) -> None:
         """Host-blocking wait (what the reference's ``wait`` did)."""
         self.wait()
+        if self.ready_event is not None:
+            self.ready_event.synchronize()
         if self._event is not None:
             self._event.synchronize()
 
@@ -112,6 +127,8 @@ class AggregatedWork(dist.Work):
                 w.block_current_stream()
             else:
                 w.wait()
+        if self.ready_event is not None:
+            torch.cuda.current_stream().wait_event(self.ready_event)
         self._run_postprocess_once()
         if self._event is not None:
             torch.cuda.current_stream().wait_event(self._event)

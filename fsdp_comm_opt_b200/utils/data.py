@@ -3,8 +3,10 @@
 ``SyntheticTokens``: uniform random token ids of a fixed shape, reproducible per (seed, index);
 ``labels = input_ids`` like the reference's grouped LM data.
 ``load_text_dataset``: the reference's HF pipeline (tokenise everything, concatenate, cut into
-``seq_length`` blocks, ``labels = input_ids.copy()``; reference: train.py:316-371).  It needs the
-``datasets`` package, a tokenizer and network or a local cache, so it is imported lazily.
+``seq_length`` blocks, ``labels = input_ids.copy()``; reference: train.py:316-371).  The dataset
+name may be a hub id (needs network or a local cache) or a local ``.txt`` / ``.json`` / ``.jsonl`` /
+``.csv`` file or a directory of them; the tokenizer may be a hub id, a local directory, or
+``"bytes"`` for the built-in byte-level tokenizer (ids 0..255), so the pipeline also runs offline.
 """
 from __future__ import annotations
 
@@ -32,17 +34,53 @@ def collate(batch):
     return {k: torch.stack([b[k] for b in batch]) for k in batch[0]}
 
 
-def load_text_dataset(dataset_name: str, dataset_subset, tokenizer_name: str, seq_length: int,
-                      max_position_embeddings: int):
-    import datasets  # noqa: lazy, optional dependency
-    from transformers import AutoTokenizer
+class ByteTokenizer:
+    """Byte-level tokenizer: UTF-8 bytes as ids 0..255.  Needs no files; any vocabulary of at least
+    256 entries can train on it."""
 
-    tokenizer = AutoTokenizer.from_pretrained(tokenizer_name)
-    data = datasets.load_dataset(dataset_name, dataset_subset)
+    model_max_length = 1 << 30
+
+    def __call__(self, texts):
+        if isinstance(texts, str):
+            texts = [texts]
+        ids = [list(t.encode("utf-8")) for t in texts]
+        return {"input_ids": ids, "attention_mask": [[1] * len(i) for i in ids]}
+
+
+def _load_raw(dataset_name: str, dataset_subset):
+    import os
+
+    import datasets  # noqa: lazy, optional dependency
+
+    kinds = {".txt": "text", ".json": "json", ".jsonl": "json", ".csv": "csv"}
+    if os.path.isdir(dataset_name):
+        files = sorted(os.path.join(dataset_name, f) for f in os.listdir(dataset_name)
+                       if os.path.splitext(f)[1] in kinds)
+        if not files:
+            raise FileNotFoundError(f"no .txt/.json/.jsonl/.csv files in {dataset_name}")
+        return datasets.load_dataset(kinds[os.path.splitext(files[0])[1]], data_files={"train": files})
+    if os.path.isfile(dataset_name):
+        return datasets.load_dataset(kinds[os.path.splitext(dataset_name)[1]], data_files={"train": dataset_name})
+    return datasets.load_dataset(dataset_name, dataset_subset)
+
+
+def load_text_dataset(dataset_name: str, dataset_subset, tokenizer_name: str, seq_length: int,
+                      max_position_embeddings: int, vocab_size: int | None = None, num_proc: int | None = None):
+    if tokenizer_name == "bytes":
+        tokenizer = ByteTokenizer()
+    else:
+        from transformers import AutoTokenizer
+
+        tokenizer = AutoTokenizer.from_pretrained(tokenizer_name)
+    n_tok = 256 if tokenizer_name == "bytes" else len(tokenizer)
+    if vocab_size is not None and n_tok > vocab_size:
+        raise ValueError(f"tokenizer has {n_tok} ids but the model's vocabulary is {vocab_size}")
+    data = _load_raw(dataset_name, dataset_subset)
     cols = data["train"].column_names
     text_col = "text" if "text" in cols else cols[0]
+    num_proc = num_proc or multiprocessing.cpu_count()
     tokenized = data.map(lambda ex: tokenizer(ex[text_col]), batched=True, remove_columns=cols,
-                         num_proc=multiprocessing.cpu_count(), load_from_cache_file=True,
+                         num_proc=num_proc, load_from_cache_file=True,
                          desc="Running tokenizer on dataset")
     seq_length = seq_length or tokenizer.model_max_length
     if seq_length > max_position_embeddings:
@@ -57,6 +95,6 @@ def load_text_dataset(dataset_name: str, dataset_subset, tokenizer_name: str, se
         out["labels"] = out["input_ids"].copy()
         return out
 
-    lm = tokenized.map(group, batched=True, num_proc=multiprocessing.cpu_count(), load_from_cache_file=True,
+    lm = tokenized.map(group, batched=True, num_proc=num_proc, load_from_cache_file=True,
                        desc=f"Grouping texts in chunks of {seq_length}")
     return lm["train"].with_format("torch")

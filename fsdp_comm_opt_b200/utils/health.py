@@ -14,15 +14,10 @@ def check_device_status() -> None:
         return
     from ..ops import attention
     from .. import _lib
-    from ..parallel import symm
+    from ..parallel import symm_impl
 
-    try:
-        from ..parallel import symm_impl
-    except ImportError:  # pragma: no cover
-        symm_impl = None
-    if symm_impl is not None:
-        for ch in symm_impl.all_channels():
-            ch.check_status()
+    for ch in symm_impl.all_channels():
+        ch.check_status()
     if attention.status_read_and_clear() != 0:
         raise RuntimeError("an attention kernel reported an expired bounded wait")
     if _lib.cuda().zc_gemm_status_read_and_clear() != 0:

@@ -12,6 +12,15 @@ optimizer / LR step -> zero_grad -> profiler step -> logging -> checkpoint), and
   --steps N                     stop after N optimizer steps
   --transport / --codec         symm | lib | auto,  v1 | v2 | auto
   --master-dtype fp32           keep fp32 master weights (communication stays bf16)
+  --sharding {flat,fsdp2}       the package's flat-shard ZeRO-3 engine (default) or PyTorch FSDP2
+                                (the reference's wrapping; chosen automatically for --cpu-offload)
+
+``-m`` takes a named shape, the hub id of one (``openai-community/gpt2-xl``) or a local directory
+with a HF ``config.json``.  Phases are timed with CUDA events (no synchronisation inside a step);
+every ``--log-freq`` steps the log also carries the device time and bus bandwidth of the
+collectives and the wire bytes per element of the compressed ones.  Expired device-side waits
+are checked next to the loss read of every step and before every checkpoint.
+``ZC_FAULT_INJECT="rank=1,step=3,kind=raise"`` makes a rank fail on the host between steps.
 
 Launch: ``torchrun --nproc-per-node N --master-addr 127.0.0.1 train.py --synthetic ...``.
 """
@@ -29,16 +38,17 @@ from torch.profiler import ProfilerActivity
 from torch.utils.data import DataLoader
 from torch.utils.data.distributed import DistributedSampler
 
-from fsdp_comm_opt_b200.models import build_model, get_config
+from fsdp_comm_opt_b200.engine import EngineConfig, build_sharded
+from fsdp_comm_opt_b200.models import get_config
 from fsdp_comm_opt_b200.ops.adamw import FusedAdamW
-from fsdp_comm_opt_b200.parallel.fsdp import FSDPPlan, apply_fsdp
+from fsdp_comm_opt_b200.parallel.fsdp import comm_report
 from fsdp_comm_opt_b200.utils import checkpoint as ckpt
 from fsdp_comm_opt_b200.utils.data import SyntheticTokens, collate, load_text_dataset
 from fsdp_comm_opt_b200.utils.dist import all_reduce_max, init_distributed, rank0_first
-from fsdp_comm_opt_b200.utils.failure import Heartbeat
+from fsdp_comm_opt_b200.utils.failure import FaultInjector, Heartbeat
 from fsdp_comm_opt_b200.utils.health import check_device_status
 from fsdp_comm_opt_b200.utils.metrics import get_mem_stats, setup_logging
-from fsdp_comm_opt_b200.utils.timing import LocalTimer
+from fsdp_comm_opt_b200.utils.timing import PhaseTimer
 
 
 def _get_parser() -> argparse.ArgumentParser:
@@ -79,7 +89,28 @@ def _get_parser() -> argparse.ArgumentParser:
     p.add_argument("--heartbeat-timeout", default=0.0, type=float,
                    help="> 0: ranks publish a heartbeat each step and abort when a peer is silent that long")
     p.add_argument("--loss-log", default=None, help="rank 0 appends 'step loss' lines to this file")
+    p.add_argument("--sharding", default="flat", choices=["flat", "fsdp2"])
+    p.add_argument("--tokenizer", default=None,
+                   help="tokenizer name or local directory for text data (default: the model name; 'bytes' = built-in byte-level)")
     return p
+
+
+def _comm_metrics(flat, plan, steps: int, device) -> dict:
+    """Per-step device time (max over ranks) and bus GB/s of the collectives since the last log line,
+    and the wire bytes per element of the fused compressed channels (compression ratio = that / 2)."""
+    out: dict = {}
+    if flat is not None:
+        for kind, d in flat.comm_stats().items():
+            out[f"comm/{kind}_ms_per_step"] = all_reduce_max(d["ms"] / max(steps, 1), device)
+            out[f"comm/{kind}_bus_gbs"] = d["bus_gbs"]
+    if device.type == "cuda":
+        rep = comm_report(plan)
+        out["comm/transport"] = {"all_gather": rep["all_gather"], "reduce_scatter": rep["reduce_scatter"]}
+        for kind, ch in rep["channels"].items():
+            if ch["wire_bytes_per_element"] is not None:
+                out[f"comm/{kind}_wire_bytes_per_elem"] = ch["wire_bytes_per_element"]
+                out[f"comm/{kind}_ratio_vs_bf16"] = ch["wire_bytes_per_element"] / 2.0
+    return out
 
 
 @record
@@ -97,21 +128,17 @@ def main(argv=None):
     master_dtype = torch.bfloat16 if args.master_dtype == "bf16" else torch.float32
     torch.manual_seed(args.seed)
 
-    # ---- model on the meta device (no memory), FSDP wrap, then materialise shards -------------
+    # ---- model on the meta device (no memory), shard, then materialise the shards ---------------
     shape_name = args.model_shape or args.model_name
     cfg = get_config(shape_name)
-    with torch.device("meta"):
-        model = build_model(cfg).to(master_dtype)
-    LOGGER.info(f"Training {sum(p.numel() for p in model.parameters())} model parameters")
-
-    plan = FSDPPlan(
-        quantize=args.quantize, zip_ccl=args.zip_ccl, compress_rs=args.compress_rs,
-        cpu_offload=args.cpu_offload, forward_prefetch_distance=args.forward_prefetch_distance,
-        transport=args.transport, codec_version=args.codec, error_feedback=not args.no_error_feedback,
-        act_ckpt=args.act_ckpt)
-    apply_fsdp(model, plan)
-    model.to_empty(device="cpu" if args.cpu_offload else device)
-    model.init_weights()
+    sharding = "fsdp2" if args.cpu_offload else args.sharding
+    ecfg = EngineConfig(model=cfg, lr=args.lr, master_dtype=master_dtype, quantize=args.quantize,
+                        zip_ccl=args.zip_ccl, compress_rs=args.compress_rs, act_ckpt=args.act_ckpt,
+                        forward_prefetch_distance=args.forward_prefetch_distance, transport=args.transport,
+                        codec_version=args.codec, seed=args.seed, sharding=sharding, cpu_offload=args.cpu_offload,
+                        error_feedback=not args.no_error_feedback, time_collectives=True)
+    model, plan, flat = build_sharded(ecfg, device)
+    LOGGER.info(f"Training {cfg.num_params()} model parameters ({sharding} sharding)")
     LOGGER.info(f"Initialized model uses {get_mem_stats(device)['curr_alloc_gb']}gb")
 
     # ---- data ---------------------------------------------------------------------------------
@@ -119,13 +146,14 @@ def main(argv=None):
         train_data = SyntheticTokens(cfg.vocab_size, args.seq_length, args.num_samples, args.seed)
     else:
         with rank0_first():
-            train_data = load_text_dataset(args.dataset_name, args.dataset_subset, args.model_name,
-                                           args.seq_length, cfg.max_seq)
+            train_data = load_text_dataset(args.dataset_name, args.dataset_subset,
+                                           args.tokenizer or args.model_name, args.seq_length, cfg.max_seq,
+                                           vocab_size=cfg.vocab_size)
     dataloader = DataLoader(train_data, batch_size=args.batch_size, collate_fn=collate,
                             sampler=DistributedSampler(train_data, shuffle=True, drop_last=True))
     LOGGER.debug(f"{len(dataloader)} batches per epoch")
 
-    optimizer = FusedAdamW(model.parameters(), lr=args.lr)
+    optimizer = FusedAdamW(flat.parameters_for_optimizer() if flat is not None else model.parameters(), lr=args.lr)
     lr_scheduler = torch.optim.lr_scheduler.CosineAnnealingLR(optimizer, T_max=1000, eta_min=args.lr * 1e-2)
 
     # ---- experiment directory / resume --------------------------------------------------------
@@ -136,7 +164,10 @@ def main(argv=None):
     state = {"epoch": 0, "global_step": 0, "epoch_step": 0, "running_loss": 0}
     resumed = False
     if is_experiment:
-        loaded = ckpt.try_resume(exp_dir, model, optimizer, lr_scheduler, device, plan.rs_hooks)
+        if flat is not None:
+            loaded = ckpt.try_resume_flat(exp_dir, flat, optimizer, lr_scheduler, device, plan.rs_hooks)
+        else:
+            loaded = ckpt.try_resume(exp_dir, model, optimizer, lr_scheduler, device, plan.rs_hooks)
         if loaded is not None:
             state, resumed = loaded, True
         LOGGER.info(f"Resumed={resumed} | {state}")
@@ -147,7 +178,8 @@ def main(argv=None):
     if is_experiment:
         (exp_dir / f"rank-{rank}").mkdir(parents=True, exist_ok=True)
 
-    timers = {k: LocalTimer(device) for k in ["data", "forward", "backward", "update"]}
+    timers = {k: PhaseTimer(device) for k in ["data", "forward", "backward", "update"]}
+    injector = FaultInjector.from_env()
     heartbeat = Heartbeat.from_default_store(rank, world_size, args.heartbeat_timeout) if args.heartbeat_timeout > 0 else None
 
     activities = [ProfilerActivity.CPU] + ([ProfilerActivity.CUDA] if device.type == "cuda" else [])
@@ -159,36 +191,66 @@ def main(argv=None):
         record_shapes=False, with_stack=False, profile_memory=False, with_modules=False,
     ) if args.profiler else contextlib.nullcontext()
 
+    def save_checkpoint():
+        if device.type == "cuda":
+            check_device_status()  # never persist a step whose collectives gave up
+        if flat is not None:
+            ckpt.save_flat_checkpoint(exp_dir, flat, optimizer, lr_scheduler, state, plan.rs_hooks)
+        else:
+            ckpt.save_checkpoint(exp_dir, model, optimizer, lr_scheduler, state, plan.rs_hooks)
+
     done = False
     with prof_ctx as prof:
         for state["epoch"] in range(state["epoch"], args.num_epochs):
             LOGGER.info(f"Begin epoch {state['epoch']} at step {state['epoch_step']}")
             dataloader.sampler.set_epoch(state["epoch"])
             batches = iter(dataloader)
+            progress = None
+            if rank == 0:
+                from tqdm import tqdm
+
+                progress = tqdm(total=len(dataloader), initial=0, disable=None)
             for i_step in range(len(dataloader)):
+                injector.maybe_fail(rank, state["global_step"])  # host-side, nothing in flight
                 if heartbeat is not None:
                     heartbeat.beat_and_check(state["global_step"])
-                model.unshard()  # prefetch the root group's parameters
+                # start gathering the first groups' parameters
+                if flat is not None:
+                    flat.begin_step()
+                else:
+                    model.unshard()
                 with timers["data"], torch.no_grad():
                     batch = next(batches)
                     batch = {k: v.to(device=device, non_blocking=True) for k, v in batch.items()}
                 if i_step < state["epoch_step"]:
+                    if progress is not None:
+                        progress.update(1)
                     continue  # fast-forward when resuming
                 with timers["forward"], torch.profiler.record_function("STEP::forward"):
                     outputs = model(**batch)
                     del batch
                 with timers["backward"], torch.profiler.record_function("STEP::backward"):
-                    outputs.loss.backward()
+                    if flat is not None:
+                        flat.backward(outputs.loss)
+                    else:
+                        outputs.loss.backward()
                 with timers["update"], torch.profiler.record_function("STEP::update"):
-                    optimizer.step()
-                    lr_scheduler.step()
-                    optimizer.zero_grad(set_to_none=not args.cpu_offload)
+                    if flat is not None:
+                        flat.optimizer_step(optimizer, lr_scheduler)
+                    else:
+                        optimizer.step()
+                        lr_scheduler.step()
+                        optimizer.zero_grad(set_to_none=not args.cpu_offload)
                 if prof is not None:
                     prof.step()
+                if progress is not None:
+                    progress.update(1)
 
                 state["global_step"] += 1
                 state["epoch_step"] += 1
-                loss_value = outputs.loss.item()
+                loss_value = outputs.loss.item()  # the one host synchronisation of a step
+                if device.type == "cuda":
+                    check_device_status()  # an expired device-side wait becomes an exception here
                 state["running_loss"] += loss_value
                 if args.loss_log and rank == 0:
                     with open(args.loss_log, "a") as fp:
@@ -210,20 +272,22 @@ def main(argv=None):
                         "time/total": ms_per_step,
                         **{f"time/{k}": t.avg_elapsed_ms() for k, t in timers.items()},
                     }
+                    info.update(_comm_metrics(flat, plan, args.log_freq, device))
                     LOGGER.info(info)
                     if device.type == "cuda":
-                        check_device_status()  # expired device-side waits become exceptions here
                         torch.cuda.reset_peak_memory_stats(device)
                     state["running_loss"] = 0
                     for t in timers.values():
                         t.reset()
 
                 if is_experiment and state["global_step"] % args.ckpt_freq == 0:
-                    ckpt.save_checkpoint(exp_dir, model, optimizer, lr_scheduler, state, plan.rs_hooks)
+                    save_checkpoint()
 
                 if args.steps is not None and state["global_step"] >= args.steps:
                     done = True
                     break
+            if progress is not None:
+                progress.close()
             if done:
                 break
             state["epoch_step"] = 0
