@@ -104,6 +104,10 @@ def parse_args():
     ap.add_argument("--no-compress", action="store_true", help="ours: stock NCCL collectives")
     ap.add_argument("--act-ckpt", action="store_true")
     ap.add_argument("--gemm", default=None, choices=[None, "auto", "tcgen05", "tcgen05_2sm", "cublas"])
+    ap.add_argument("--sharding", default="flat", choices=["flat", "fsdp2"], help="ours: sharding back end")
+    ap.add_argument("--kernel-table", type=int, default=0, metavar="N",
+                    help="after the timed runs, trace two more steps with torch.profiler and print the N "
+                         "kernels with the most device time on rank 0 (shares only: traced steps are not timed)")
     return ap.parse_args()
 
 
@@ -117,9 +121,10 @@ def make_ours(args, device):
         gemm.set_backend(args.gemm)
     comp = not args.no_compress
     eng = TrainEngine(EngineConfig(model=args.model, quantize=comp, zip_ccl=comp, compress_rs=comp,
-                                   transport=args.transport, act_ckpt=args.act_ckpt), device)
-    info = {"gemm_backend": gemm.get_backend(), "native_lib": str(_lib.cuda_lib_path()),
-            "comm": "zip all-gather + compressed reduce-scatter" if comp else "nccl"}
+                                   transport=args.transport, act_ckpt=args.act_ckpt, sharding=args.sharding), device)
+    info = {"gemm_backend": gemm.get_backend(), "native_lib": str(_lib.cuda_lib_path()), "sharding": args.sharding,
+            "comm_requested": "zip all-gather + compressed reduce-scatter" if comp else "nccl"}
+    make_ours.engine = eng
     return eng.step_on_device, eng.step, info, _lib
 
 
@@ -207,6 +212,21 @@ def make_reference(args, device, world):
     return step_on_device, step, {"ref_variant": args.ref_variant}, None
 
 
+def kernel_table(step_fn, batch, top: int, device) -> list:
+    """Device time per kernel name over two traced steps (every rank traces, so collectives match up)."""
+    import torch
+    from torch.profiler import ProfilerActivity, profile
+
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        step_fn(batch)
+        step_fn(batch)
+        torch.cuda.synchronize(device)
+    rows = sorted(prof.key_averages(), key=lambda e: -e.device_time_total)
+    total = sum(e.device_time_total for e in rows) or 1.0
+    return [{"kernel": e.key[:90], "launches_per_step": e.count / 2, "ms_per_step": round(e.device_time_total / 2e3, 3),
+             "share": round(e.device_time_total / total, 4)} for e in rows[:top]]
+
+
 def main():
     args = parse_args()
     try:
@@ -285,15 +305,22 @@ def main():
 
     dev_ms, dev_loss, launches, (d0, d1) = run("device")
     e2e_ms, e2e_loss, _, (x0, x1) = run("e2e")
+    comm = None
     if args.impl == "ours":
         # a bounded device-side wait that expired would have left wrong data behind: fail loudly
-        from fsdp_comm_opt_b200.ops import attention as _attn
-        from fsdp_comm_opt_b200.parallel import symm_impl as _symm
+        from fsdp_comm_opt_b200.utils.health import check_device_status
 
-        for ch in _symm.all_channels():
-            ch.check_status()
-        if _attn.status_read_and_clear() != 0:
-            raise RuntimeError("an attention kernel reported an expired wait")
+        check_device_status()
+        # what the collectives actually ran on (not what the flags asked for)
+        comm = make_ours.engine.comm_report()
+        if world > 1 and not args.no_compress and args.transport != "lib":
+            ran = set(comm["all_gather"]) | set(comm["reduce_scatter"])
+            if ran != {"symm"}:
+                raise RuntimeError(f"compressed collectives were requested but ran on {sorted(ran)}: "
+                                   "the symmetric-memory transport was not available")
+    table = None
+    if args.kernel_table > 0:  # every rank runs the traced steps (they contain collectives)
+        table = kernel_table(step_dev, dev_batches[-1], args.kernel_table, device)
     if rank == 0:
         time.sleep(0.3)
         sampler.stop()
@@ -326,10 +353,13 @@ def main():
                     "api": "TrainEngine.step(pinned host token ids) -> float loss" if args.impl == "ours"
                     else "reference hooks + FSDP2 + HF model step, batch.to(device) then loss.item()"},
             "gpu_launches": launches,
+            "comm": comm,
             "clocks": clocks,
             "loss": {"device_run_last": dev_loss, "e2e_run_last": e2e_loss},
         }
         print(json.dumps(out))
+        if table is not None:
+            print(json.dumps({"kernel_table": table}))
     dist.barrier()
     dist.destroy_process_group()
     return 0

@@ -6,6 +6,9 @@ Two shared objects are produced under ``fsdp_comm_opt_b200/lib``:
 * ``libzc_cuda.so`` - every sm_100a kernel plus its C launchers (nvcc, ``-gencode
   arch=compute_100a,code=sm_100a``).  Plain C ABI, loaded with ctypes, so no libtorch headers
   are compiled and a full rebuild takes seconds.
+* ``libzc_cuda_dbg.so`` - the same sources with ``-DZC_DEBUG_BOUNDS`` (built on demand, loaded when
+  ``ZC_DEBUG_BOUNDS=1``): stores into peer memory are checked against the destination's extent and
+  an offending store is skipped and recorded in the status words instead of being issued.
 
 The reference builds one pybind11/libtorch extension with setuptools
 (reference: zipccl/setup.py:18-71) for sm_90a; there is no sm_100 target there.
@@ -71,25 +74,27 @@ def build_cpu(force: bool = False, verbose: bool = False) -> Path:
     return out
 
 
-def build_cuda(force: bool = False, verbose: bool = False, ptxas_v: bool = False) -> Path | None:
+def build_cuda(force: bool = False, verbose: bool = False, ptxas_v: bool = False,
+               debug_bounds: bool = False) -> Path | None:
     nvcc = _nvcc()
     if nvcc is None:
         return None
     LIB.mkdir(exist_ok=True)
-    OBJ.mkdir(exist_ok=True)
-    out = LIB / "libzc_cuda.so"
+    obj_dir = PKG / "build_dbg" if debug_bounds else OBJ
+    obj_dir.mkdir(exist_ok=True)
+    out = LIB / ("libzc_cuda_dbg.so" if debug_bounds else "libzc_cuda.so")
     names = cuda_sources()
     if not names:
         return None
     hdrs = list(CSRC.glob("*.h")) + list(CSRC.glob("*.cuh"))
-    flags = list(NVCC_FLAGS) + (["-Xptxas", "-v"] if ptxas_v else [])
+    flags = list(NVCC_FLAGS) + (["-Xptxas", "-v"] if ptxas_v else []) + (["-DZC_DEBUG_BOUNDS"] if debug_bounds else [])
     hdr_digest = _digest(hdrs, " ".join(flags))
     objs: list[Path] = []
     jobs = []
     for name in names:
         src = CSRC / name
-        obj = OBJ / (src.stem + ".o")
-        stamp = OBJ / (src.stem + ".stamp")
+        obj = obj_dir / (src.stem + ".o")
+        stamp = obj_dir / (src.stem + ".stamp")
         digest = _digest([src], hdr_digest)
         objs.append(obj)
         if force or not _stamp_ok(stamp, digest, obj):
@@ -111,7 +116,7 @@ def build_cuda(force: bool = False, verbose: bool = False, ptxas_v: bool = False
         with ThreadPoolExecutor(max_workers=min(8, len(jobs))) as ex:
             list(ex.map(_compile, jobs))
     link_digest = _digest(objs, "link-v1")
-    link_stamp = LIB / "libzc_cuda.stamp"
+    link_stamp = LIB / (out.stem + ".stamp")
     if jobs or force or not _stamp_ok(link_stamp, link_digest, out):
         cmd = [nvcc, "-shared", "-o", str(out)] + [str(o) for o in objs] + ["-Xcompiler", "-fPIC", "-lcuda"]
         # libcuda is only needed for the tensor-map encoder; it is resolved at run time through
@@ -125,7 +130,8 @@ def build_cuda(force: bool = False, verbose: bool = False, ptxas_v: bool = False
 
 
 def build_all(force: bool = False, verbose: bool = False) -> dict:
-    return {"cpu": build_cpu(force, verbose), "cuda": build_cuda(force, verbose)}
+    return {"cpu": build_cpu(force, verbose), "cuda": build_cuda(force, verbose),
+            "cuda_dbg": build_cuda(force, verbose, debug_bounds=True)}
 
 
 if __name__ == "__main__":
@@ -135,6 +141,9 @@ if __name__ == "__main__":
     ap.add_argument("--force", action="store_true")
     ap.add_argument("--verbose", action="store_true")
     ap.add_argument("--ptxas-v", action="store_true", help="print registers/spills/smem per kernel")
+    ap.add_argument("--debug-bounds", action="store_true", help="also build libzc_cuda_dbg.so (-DZC_DEBUG_BOUNDS)")
     a = ap.parse_args()
     print(build_cpu(a.force, a.verbose))
     print(build_cuda(a.force, a.verbose, a.ptxas_v))
+    if a.debug_bounds:
+        print(build_cuda(a.force, a.verbose, a.ptxas_v, debug_bounds=True))

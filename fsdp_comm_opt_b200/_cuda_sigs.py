@@ -20,6 +20,7 @@ def declare(lib) -> None:
     # codec
     _sig(lib, "zc_v2_encode", P, L, P, P, P)
     _sig(lib, "zc_v2_decode", P, P, L, P, P)
+    _sig(lib, "zc_v2_decode_ctas", P, P, L, P, I, P)
     _sig(lib, "zc_v1_encode_split", P, L, P, P, I, P, P, P, P, P, L, P)
     _sig(lib, "zc_v1_encode_fused", P, L, P, I, P, P, P, L, P, P, L, P)
     _sig(lib, "zc_v1_decode_split", P, P, P, P, I, L, P, P, P, L, L, P)
@@ -41,6 +42,12 @@ def declare(lib) -> None:
     _sig(lib, "zc_quant_int8", P, L, I, P, P)
     _sig(lib, "zc_dequant_int8", P, L, I, L, I, P, P)
     _sig(lib, "zc_adamw", P, P, P, P, L, I, I, I, F, F, F, F, F, F, F, I, P)
+    _sig(lib, "zc_adamw_guarded", P, P, P, P, L, I, I, I, F, F, F, F, F, F, F, I, P, P)
+    _sig(lib, "zc_health_read_and_clear")
+    _sig(lib, "zc_health_set", I)
+    if hasattr(lib, "zc_health_word"):
+        lib.zc_health_word.restype = P
+        lib.zc_health_word.argtypes = []
     # tensor cores
     _sig(lib, "zc_umma_selftest", P, P, P, I, I, I, P, P)
     _sig(lib, "zc_attn_fwd", P, P, P, P, P, I, I, I, I, I, L, L, L, L, L, L, L, L, L, F, P)

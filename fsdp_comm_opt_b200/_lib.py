@@ -56,14 +56,21 @@ def cuda_available() -> bool:
     return torch.cuda.is_available()
 
 
+def debug_bounds() -> bool:
+    """``ZC_DEBUG_BOUNDS=1`` selects the bounds-checked build of the kernels."""
+    import os
+
+    return os.environ.get("ZC_DEBUG_BOUNDS", "0") == "1"
+
+
 def cuda_lib_path() -> Path:
-    return _build.LIB / "libzc_cuda.so"
+    return _build.LIB / ("libzc_cuda_dbg.so" if debug_bounds() else "libzc_cuda.so")
 
 
 # kernels launched by one call of each C launcher (for the launch counter)
 _KERNELS_PER_CALL = {
     "zc_v1_encode_split": 3, "zc_v1_encode_fused": 3, "zc_v1_base_from_std": 2, "zc_quant_int8": 2,
-    "zc_attn_bwd": 3, "zc_attn_bwd_ws": 3, "zc_attn_bwd_ws_status_read_and_clear": 0, "zc_attn_status_read_and_clear": 0, "zc_attn_ws_status_read_and_clear": 0, "zc_gemm_status_read_and_clear": 0,
+    "zc_health_word": 0, "zc_health_read_and_clear": 0, "zc_health_set": 0, "zc_attn_bwd": 3, "zc_attn_bwd_ws": 3, "zc_attn_bwd_ws_status_read_and_clear": 0, "zc_attn_status_read_and_clear": 0, "zc_attn_ws_status_read_and_clear": 0, "zc_gemm_status_read_and_clear": 0,
 }
 _LAUNCHES = 0
 
@@ -108,7 +115,7 @@ def cuda():
             if _CUDA is None:
                 path = cuda_lib_path()
                 if not path.exists():
-                    built = _build.build_cuda()
+                    built = _build.build_cuda(debug_bounds=debug_bounds())
                     if built is None:
                         raise RuntimeError(
                             "libzc_cuda.so is missing and nvcc was not found; run "

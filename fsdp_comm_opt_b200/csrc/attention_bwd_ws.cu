@@ -452,10 +452,17 @@ __global__ void __launch_bounds__(256) dq_convert_t_kernel(const float* __restri
 namespace bkt {
 using namespace bws;
 
+// Phase stamps for kernel development: compiled in only with -DZC_PHASE_TRACE
+#ifdef ZC_PHASE_TRACE
 #define ZC_BTRACE(slot, i, k)                                                                      \
   do {                                                                                             \
     if (p.trace && blockIdx.x == 0 && (i) < 256) p.trace[((slot) * 256 + (i)) * 8 + (k)] = clock64(); \
   } while (0)
+#else
+#define ZC_BTRACE(slot, i, k) \
+  do {                        \
+  } while (0)
+#endif
 
 constexpr int QB = 64;  // queries per iteration
 
@@ -874,9 +881,11 @@ int zc_attn_bwd_ws(const void* q, const void* k, const void* v, const void* o, c
   return launch_status();
 }
 
-// Profiling aid: a device buffer of 3 * 256 * 8 int64 (or null) that CTA 0 of later key-row launches
-// fills with SM-clock stamps of its phases.
+#ifdef ZC_PHASE_TRACE
+// Development builds only: a device buffer of 3 * 256 * 8 int64 (or null) that CTA 0 of later key-row
+// launches fills with SM-clock stamps of its phases.
 void zc_attn_bwd_kt_set_trace(void* buf) { zc::bws::g_trace = (long long*)buf; }
+#endif
 
 // Same argument list as zc_attn_bwd.  Head dimension 128 runs the key-row kernel; 64 falls back to
 // zc_attn_bwd_ws.

@@ -49,10 +49,17 @@ struct Params {
   int ncb;  // number of 256-query blocks
   long long* trace;  // null, or [2][blocks][8] SM-clock stamps written by CTA 0 (softmax warp 2, MMA thread)
 };
+// Phase stamps for kernel development: compiled in only with -DZC_PHASE_TRACE
+#ifdef ZC_PHASE_TRACE
 #define ZC_TRACE(slot, j, k)                                                          \
   do {                                                                                \
     if (p.trace && blockIdx.x == 0 && (j) < 128) p.trace[((slot) * 128 + (j)) * 8 + (k)] = clock64(); \
   } while (0)
+#else
+#define ZC_TRACE(slot, j, k) \
+  do {                       \
+  } while (0)
+#endif
 
 __global__ void __launch_bounds__(THREADS, 1) attn_fwd_2q_kernel(const __grid_constant__ CUtensorMap mapQ,
                                                                  const __grid_constant__ CUtensorMap mapK,
@@ -341,9 +348,11 @@ int zc_attn_fwd_2q_status_read_and_clear() {
   return v;
 }
 
-// Profiling aid: a device buffer of 2 * 128 * 8 int64 (or null) that CTA 0 of later launches fills
-// with SM-clock stamps of its phases.
+#ifdef ZC_PHASE_TRACE
+// Development builds only: a device buffer of 2 * 128 * 8 int64 (or null) that CTA 0 of later launches
+// fills with SM-clock stamps of its phases.
 void zc_attn_fwd_2q_set_trace(void* buf) { zc::fwd2q::g_trace = (long long*)buf; }
+#endif
 
 // Same argument list as zc_attn_fwd_ws.  Head dimension 128 runs the two-tile kernel; 64 falls back
 // to zc_attn_fwd_ws.

@@ -6,6 +6,7 @@
 // same device functions are reused inside the fused collective kernels.
 #include "codec_v2_dev.cuh"
 #include "launch_util.h"
+#include "nvtx_util.h"
 
 namespace zc {
 
@@ -31,17 +32,29 @@ __global__ void __launch_bounds__(256) v2_encode_kernel(const uint16_t* __restri
 __global__ void __launch_bounds__(256) v2_decode_kernel(const uint8_t* __restrict__ records,
                                                         const uint32_t* __restrict__ headers, int64_t n,
                                                         uint16_t* __restrict__ out, int64_t nc) {
-  const int lane = threadIdx.x & 31;
-  const int64_t warp0 = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+  __shared__ __align__(16) uint8_t esc[8][1024];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int64_t warp0 = (int64_t)blockIdx.x * 8 + warp;
   const int64_t stride = (int64_t)gridDim.x * 8;
   const bool al = (reinterpret_cast<uintptr_t>(out) & 15) == 0;
-  for (int64_t c = warp0; c < nc; c += stride) {
+  // software pipeline: record c + stride is in flight while record c is decoded and stored
+  RecRegs cur, nxt;
+  int64_t c = warp0;
+  if (c < nc) v2_prefetch(records + c * V2_SLOT_BYTES, __ldcg(headers + c), lane, cur);
+  uint32_t hdr_next = (c + stride < nc) ? __ldcg(headers + c + stride) : 0u;
+  for (; c < nc; c += stride) {
+    const int64_t cn = c + stride;
+    if (cn < nc) {
+      v2_prefetch(records + cn * V2_SLOT_BYTES, hdr_next, lane, nxt);
+      if (cn + stride < nc) hdr_next = __ldcg(headers + cn + stride);
+    }
     LaneSplit s;
-    v2_decode_chunk(records + c * V2_SLOT_BYTES, __ldg(headers + c), lane, s);
+    v2_decode_regs(cur, esc[warp], lane, s);
     LaneIn o;
     join_lane(s, o);
     const int64_t e0 = c * V2_CHUNK_ELEMS + lane * 32;
     store_lane(out + e0, n - e0, al, o);
+    cur = nxt;
   }
 }
 
@@ -50,6 +63,7 @@ __global__ void __launch_bounds__(256) v2_decode_kernel(const uint8_t* __restric
 extern "C" {
 
 int zc_v2_encode(const void* in, int64_t n, void* records, void* headers, cudaStream_t stream) {
+  ZC_NVTX_RANGE("zc_v2_encode");
   const int64_t nc = (n + zc::V2_CHUNK_ELEMS - 1) / zc::V2_CHUNK_ELEMS;
   if (nc == 0) return 0;
   const int grid = (int)std::min<int64_t>((nc + 7) / 8, (int64_t)zc::sm_count() * 8);
@@ -58,7 +72,21 @@ int zc_v2_encode(const void* in, int64_t n, void* records, void* headers, cudaSt
   return zc::launch_status();
 }
 
+// `max_ctas` > 0 caps the grid (how the decoder behaves with the SM budget it has inside a fused
+// collective); 0 sizes it to the device.
+int zc_v2_decode_ctas(const void* records, const void* headers, int64_t n, void* out, int max_ctas,
+                      cudaStream_t stream) {
+  const int64_t nc = (n + zc::V2_CHUNK_ELEMS - 1) / zc::V2_CHUNK_ELEMS;
+  if (nc == 0) return 0;
+  int grid = (int)std::min<int64_t>((nc + 7) / 8, (int64_t)zc::sm_count() * 8);
+  if (max_ctas > 0) grid = std::min(grid, max_ctas);
+  zc::v2_decode_kernel<<<grid, 256, 0, stream>>>((const uint8_t*)records, (const uint32_t*)headers, n,
+                                                 (uint16_t*)out, nc);
+  return zc::launch_status();
+}
+
 int zc_v2_decode(const void* records, const void* headers, int64_t n, void* out, cudaStream_t stream) {
+  ZC_NVTX_RANGE("zc_v2_decode");
   const int64_t nc = (n + zc::V2_CHUNK_ELEMS - 1) / zc::V2_CHUNK_ELEMS;
   if (nc == 0) return 0;
   const int grid = (int)std::min<int64_t>((nc + 7) / 8, (int64_t)zc::sm_count() * 8);

@@ -176,4 +176,87 @@ __device__ __forceinline__ void v2_decode_chunk(const uint8_t* rec, uint32_t hdr
     default: decode_lane<4>(planes, base, esc, s.ex); break;
   }
 }
+
+// ---------------------------------------------------------------------------------------------
+// Two-phase decode: `v2_prefetch` issues every global load a lane needs of one record (32 sign +
+// mantissa bytes, its word of up to four planes, its share of the escape bytes) without using the
+// values, `v2_decode_regs` turns them into exponents later.  A decoder that prefetches record i+1
+// before it decodes record i keeps one record's loads in flight per warp at all times, which is what
+// hides the memory latency when few warps per SM are available (inside the fused collectives, next
+// to a GEMM).  Escapes go through 1 KB of shared memory per warp: the lanes store the 16-byte pieces
+// they fetched, then every lane picks its own bytes by prefix position (no serial global loads).
+// Loads use ld.global.cg: records may have been written by another GPU.
+// ---------------------------------------------------------------------------------------------
+struct RecRegs {
+  uint32_t hdr;
+  uint4 sm0, sm1;   // sign+mantissa bytes of this lane (raw mode: e0/e1 hold its exponent bytes)
+  uint32_t pl[4];
+  uint4 e0, e1;     // bytes [16 lane, 16 lane + 16) and [512 + 16 lane, ...) of the escape area
+};
+
+__device__ __forceinline__ void v2_prefetch(const uint8_t* rec, uint32_t hdr, int lane, RecRegs& r) {
+  r.hdr = hdr;
+  const uint4* smp = reinterpret_cast<const uint4*>(rec + lane * 32);
+  r.sm0 = __ldcg(smp);
+  r.sm1 = __ldcg(smp + 1);
+  const int w = v2_hdr_width(hdr);
+  if (w == V2_RAW_WIDTH) {
+    const uint4* ep = reinterpret_cast<const uint4*>(rec + 1024 + lane * 32);
+    r.e0 = __ldcg(ep);
+    r.e1 = __ldcg(ep + 1);
+    return;
+  }
+  if (w == 0) return;
+  const uint32_t* pl = reinterpret_cast<const uint32_t*>(rec + 1024) + lane;
+  r.pl[0] = __ldcg(pl);
+  r.pl[1] = w > 1 ? __ldcg(pl + 32) : 0u;
+  r.pl[2] = w > 2 ? __ldcg(pl + 64) : 0u;
+  r.pl[3] = w > 3 ? __ldcg(pl + 96) : 0u;
+  const int n_esc = v2_hdr_nesc(hdr);
+  const uint4* eb = reinterpret_cast<const uint4*>(rec + 1024 + 128 * w);
+  if (16 * lane < n_esc) r.e0 = __ldcg(eb + lane);
+  if (512 + 16 * lane < n_esc) r.e1 = __ldcg(eb + 32 + lane);
+}
+
+// `esc_smem`: 1024 bytes of shared memory owned by this warp (16-byte aligned).
+__device__ __forceinline__ void v2_decode_regs(const RecRegs& r, uint8_t* esc_smem, int lane, LaneSplit& s) {
+  s.sm[0] = r.sm0.x; s.sm[1] = r.sm0.y; s.sm[2] = r.sm0.z; s.sm[3] = r.sm0.w;
+  s.sm[4] = r.sm1.x; s.sm[5] = r.sm1.y; s.sm[6] = r.sm1.z; s.sm[7] = r.sm1.w;
+  const int w = v2_hdr_width(r.hdr);
+  const int base = v2_hdr_base(r.hdr);
+  if (w == V2_RAW_WIDTH) {
+    s.ex[0] = r.e0.x; s.ex[1] = r.e0.y; s.ex[2] = r.e0.z; s.ex[3] = r.e0.w;
+    s.ex[4] = r.e1.x; s.ex[5] = r.e1.y; s.ex[6] = r.e1.z; s.ex[7] = r.e1.w;
+    return;
+  }
+  if (w == 0) {
+    const uint32_t e4 = rep4((uint32_t)base);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) s.ex[k] = e4;
+    return;
+  }
+  const int n_esc = v2_hdr_nesc(r.hdr);
+  uint32_t planes[4] = {r.pl[0], r.pl[1], r.pl[2], r.pl[3]};
+  uint32_t zm = ~planes[0];
+  if (w > 1) zm &= ~planes[1];
+  if (w > 2) zm &= ~planes[2];
+  if (w > 3) zm &= ~planes[3];
+  int pos = 0;
+  if (n_esc > 0) {  // warp-uniform
+    uint4* es = reinterpret_cast<uint4*>(esc_smem);
+    if (16 * lane < n_esc) es[lane] = r.e0;
+    if (512 + 16 * lane < n_esc) es[32 + lane] = r.e1;
+    int total;
+    pos = warp_excl_scan(__popc(zm), lane, total);
+    __syncwarp();
+  }
+  const uint8_t* esc = esc_smem + pos;
+  switch (w) {
+    case 1: decode_lane<1>(planes, base, esc, s.ex); break;
+    case 2: decode_lane<2>(planes, base, esc, s.ex); break;
+    case 3: decode_lane<3>(planes, base, esc, s.ex); break;
+    default: decode_lane<4>(planes, base, esc, s.ex); break;
+  }
+  if (n_esc > 0) __syncwarp();  // the next record's escapes overwrite esc_smem
+}
 }  // namespace zc

@@ -116,6 +116,76 @@ __global__ void __launch_bounds__(RN_THREADS) rmsnorm_fwd_kernel(
   }
 }
 
+// The same forward with one WARP per row (cols <= NV * 256): no block-wide synchronisation, all of a
+// row's loads issued before the first use, and the row kept packed (bf16) in registers between the
+// sum of squares and the scaling.  One row per CTA leaves the kernel waiting on two barriers per row
+// with a single load batch in flight (0.44 of the copy bandwidth); independent warps keep many rows'
+// loads in flight per SM.
+template <int NV>
+__global__ void __launch_bounds__(128) rmsnorm_fwd_warp_kernel(
+    const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ res,
+    const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ y, __nv_bfloat16* __restrict__ h_out,
+    float* __restrict__ rstd_out, int64_t rows, int cols, float eps) {
+  const int lane = threadIdx.x & 31;
+  const int64_t row = (int64_t)blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int nvec = cols / 8;
+  const __nv_bfloat16* xr = x + row * cols;
+  BF8 hv[NV];
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int v = lane + 32 * i;
+    if (v < nvec) hv[i] = ld8(xr + v * 8);
+  }
+  if (res) {
+    const __nv_bfloat16* rr = res + row * cols;
+    BF8 rv[NV];
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int v = lane + 32 * i;
+      if (v < nvec) rv[i] = ld8(rr + v * 8);
+    }
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int v = lane + 32 * i;
+      if (v < nvec) {
+        float a[8], b[8];
+        unpack8(hv[i], a);
+        unpack8(rv[i], b);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) a[j] += b[j];
+        hv[i] = pack8(a);  // the rounded sum is what gets normalised, as the unfused op order would
+        st8(h_out + row * cols + v * 8, hv[i]);
+      }
+    }
+  }
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    if (lane + 32 * i < nvec) {
+      float a[8];
+      unpack8(hv[i], a);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) ss += a[j] * a[j];
+    }
+  }
+  ss = warp_sum(ss);
+  const float rstd = rsqrtf(ss / (float)cols + eps);
+  if (lane == 0) rstd_out[row] = rstd;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int v = lane + 32 * i;
+    if (v < nvec) {
+      float a[8], wv[8], o[8];
+      unpack8(hv[i], a);
+      unpack8(ld8(w + v * 8), wv);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = a[j] * rstd * wv[j];
+      st8(y + row * cols + v * 8, pack8(o));
+    }
+  }
+}
+
 // dx = rstd * (g - xhat * mean(g * xhat)) (+ dh),  g = dy * w,  xhat = h * rstd
 // dw = sum_rows dy * xhat: every CTA keeps partial sums in registers over its rows and writes them
 // to its row of `partials` ([gridDim.x, cols] fp32), which rmsnorm_dw_reduce_kernel then sums
@@ -426,7 +496,8 @@ __global__ void __launch_bounds__(256) dequant_kernel(const uint8_t* __restrict_
 template <typename TP, typename TG, typename TS>
 __global__ void __launch_bounds__(256) adamw_kernel(TP* __restrict__ p, TG* __restrict__ g, TS* __restrict__ m,
                                                     TS* __restrict__ v, int64_t n, float lr, float b1, float b2,
-                                                    float eps, float wd, float bc1, float rsqrt_bc2, int zero_grad) {
+                                                    float eps, float wd, float bc1, float rsqrt_bc2, int zero_grad, const int* __restrict__ guard) {
+  if (guard && *guard) return;
   for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < n; i += (int64_t)gridDim.x * 256) {
     const float gf = to_f<TG>(g[i]);
     float pf = to_f<TP>(p[i]);
@@ -464,7 +535,8 @@ template <typename TP, typename TG, typename TS>
 __global__ void __launch_bounds__(256) adamw_vec_kernel(TP* __restrict__ p, TG* __restrict__ g, TS* __restrict__ m,
                                                         TS* __restrict__ v, int64_t nvec, float lr, float b1, float b2,
                                                         float eps, float wd, float bc1, float rsqrt_bc2,
-                                                        int zero_grad) {
+                                                        int zero_grad, const int* __restrict__ guard) {
+  if (guard && *guard) return;  // a collective of this step gave up: leave parameters and moments alone
   const float decay = 1.f - lr * wd, step = lr / bc1;
   auto update = [&](float (&pf)[8], const float (&gf)[8], float (&mf)[8], float (&vf)[8]) {
 #pragma unroll
@@ -518,28 +590,28 @@ __global__ void __launch_bounds__(256) adamw_vec_kernel(TP* __restrict__ p, TG* 
 
 template <typename TP, typename TG, typename TS>
 int adamw_launch(void* p, void* g, void* m, void* v, int64_t n, float lr, float b1, float b2, float eps, float wd,
-                 float bc1, float rs, int zg, cudaStream_t st) {
+                 float bc1, float rs, int zg, const int* guard, cudaStream_t st) {
   const bool vec = (n % 8 == 0) && (((reinterpret_cast<uintptr_t>(p) | reinterpret_cast<uintptr_t>(g) |
                                       reinterpret_cast<uintptr_t>(m) | reinterpret_cast<uintptr_t>(v)) & 15) == 0);
   if (vec) {
     const int64_t nvec = n / 8;
     const int grid = (int)std::min<int64_t>((nvec + 255) / 256, (int64_t)sm_count() * 8);
     adamw_vec_kernel<TP, TG, TS><<<grid, 256, 0, st>>>((TP*)p, (TG*)g, (TS*)m, (TS*)v, nvec, lr, b1, b2, eps, wd,
-                                                        bc1, rs, zg);
+                                                        bc1, rs, zg, guard);
   } else {
     const int grid = (int)std::min<int64_t>((n + 255) / 256, (int64_t)sm_count() * 16);
     adamw_kernel<TP, TG, TS><<<grid, 256, 0, st>>>((TP*)p, (TG*)g, (TS*)m, (TS*)v, n, lr, b1, b2, eps, wd, bc1, rs,
-                                                    zg);
+                                                    zg, guard);
   }
   return launch_status();
 }
 
 template <typename TP, typename TG>
 int adamw_dispatch_s(void* p, void* g, void* m, void* v, int64_t n, int sdt, float lr, float b1, float b2, float eps,
-                     float wd, float bc1, float bc2, int zg, cudaStream_t st) {
+                     float wd, float bc1, float bc2, int zg, const int* guard, cudaStream_t st) {
   const float rs = 1.f / sqrtf(bc2);
-  if (sdt == 0) return adamw_launch<TP, TG, __nv_bfloat16>(p, g, m, v, n, lr, b1, b2, eps, wd, bc1, rs, zg, st);
-  if (sdt == 1) return adamw_launch<TP, TG, float>(p, g, m, v, n, lr, b1, b2, eps, wd, bc1, rs, zg, st);
+  if (sdt == 0) return adamw_launch<TP, TG, __nv_bfloat16>(p, g, m, v, n, lr, b1, b2, eps, wd, bc1, rs, zg, guard, st);
+  if (sdt == 1) return adamw_launch<TP, TG, float>(p, g, m, v, n, lr, b1, b2, eps, wd, bc1, rs, zg, guard, st);
   return ERR_UNSUPPORTED;
 }
 
@@ -556,6 +628,17 @@ int zc_rmsnorm_fwd(const void* x, const void* res, const void* w, void* y, void*
   if (cols % 8 || cols > zc::RN_MAX_COLS) return ERR_UNSUPPORTED;
   if (rows == 0) return 0;
   const int nvec = cols / 8;
+  if (nvec <= 32 * 20) {  // one warp per row (wider rows do not fit a warp's registers)
+    const unsigned grid = (unsigned)((rows + 3) / 4);
+#define ZC_RN_FWDW(V)                                                                                             \
+  zc::rmsnorm_fwd_warp_kernel<V><<<grid, 128, 0, st>>>((const bf16*)x, (const bf16*)res, (const bf16*)w, (bf16*)y, \
+                                                       (bf16*)h_out, rstd, rows, cols, eps)
+    if (nvec <= 32 * 4) ZC_RN_FWDW(4);
+    else if (nvec <= 32 * 16) ZC_RN_FWDW(16);
+    else ZC_RN_FWDW(20);
+#undef ZC_RN_FWDW
+    return zc::launch_status();
+  }
 #define ZC_RN_FWD(V)                                                                                              \
   zc::rmsnorm_fwd_kernel<V><<<(unsigned)rows, zc::RN_THREADS, 0, st>>>((const bf16*)x, (const bf16*)res,          \
                                                                        (const bf16*)w, (bf16*)y, (bf16*)h_out,    \
@@ -661,18 +744,58 @@ int zc_dequant_int8(const void* gathered, int64_t stride, int world, int64_t n, 
   return zc::launch_status();
 }
 
-int zc_adamw(void* p, void* g, void* m, void* v, int64_t n, int pdt, int gdt, int sdt, float lr, float b1, float b2,
-             float eps, float wd, float bc1, float bc2, int zero_grad, cudaStream_t st) {
+// The library's health word of the current device (0 = healthy): set by a fused collective whose
+// bounded wait ran out, read on the device by zc_adamw_guarded, read and cleared on the host by
+// zc_health_read_and_clear.  Allocated on first use.
+int* zc_health_word() {
+  static int* words[64] = {nullptr};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) return nullptr;
+  if (!words[dev]) {
+    if (cudaMalloc(&words[dev], sizeof(int)) != cudaSuccess) return nullptr;
+    cudaMemset(words[dev], 0, sizeof(int));
+  }
+  return words[dev];
+}
+
+int zc_health_read_and_clear() {
+  int* w = zc_health_word();
+  if (!w) return -1;
+  int v = 0;
+  cudaMemcpy(&v, w, sizeof(int), cudaMemcpyDeviceToHost);
+  if (v) cudaMemset(w, 0, sizeof(int));
+  return v;
+}
+
+// Host-side injection of a failure (tests, drills): what a collective that gave up would have written.
+int zc_health_set(int value) {
+  int* w = zc_health_word();
+  if (!w) return -1;
+  return cudaMemcpy(w, &value, sizeof(int), cudaMemcpyHostToDevice) == cudaSuccess ? 0 : -1;
+}
+
+// `guard`: device pointer to a word that must be 0 for the update to happen (null: unconditional).
+// With the health word there, an optimizer step that follows a collective which gave up leaves
+// parameters and moments untouched, with no host synchronisation between the two.
+int zc_adamw_guarded(void* p, void* g, void* m, void* v, int64_t n, int pdt, int gdt, int sdt, float lr, float b1,
+                     float b2, float eps, float wd, float bc1, float bc2, int zero_grad, const int* guard,
+                     cudaStream_t st) {
   if (n == 0) return 0;
   if (pdt == 0 && gdt == 0)
-    return zc::adamw_dispatch_s<bf16, bf16>(p, g, m, v, n, sdt, lr, b1, b2, eps, wd, bc1, bc2, zero_grad, st);
+    return zc::adamw_dispatch_s<bf16, bf16>(p, g, m, v, n, sdt, lr, b1, b2, eps, wd, bc1, bc2, zero_grad, guard, st);
   if (pdt == 1 && gdt == 1)
-    return zc::adamw_dispatch_s<float, float>(p, g, m, v, n, sdt, lr, b1, b2, eps, wd, bc1, bc2, zero_grad, st);
+    return zc::adamw_dispatch_s<float, float>(p, g, m, v, n, sdt, lr, b1, b2, eps, wd, bc1, bc2, zero_grad, guard, st);
   if (pdt == 0 && gdt == 1)
-    return zc::adamw_dispatch_s<bf16, float>(p, g, m, v, n, sdt, lr, b1, b2, eps, wd, bc1, bc2, zero_grad, st);
+    return zc::adamw_dispatch_s<bf16, float>(p, g, m, v, n, sdt, lr, b1, b2, eps, wd, bc1, bc2, zero_grad, guard, st);
   if (pdt == 1 && gdt == 0)
-    return zc::adamw_dispatch_s<float, bf16>(p, g, m, v, n, sdt, lr, b1, b2, eps, wd, bc1, bc2, zero_grad, st);
+    return zc::adamw_dispatch_s<float, bf16>(p, g, m, v, n, sdt, lr, b1, b2, eps, wd, bc1, bc2, zero_grad, guard, st);
   return ERR_UNSUPPORTED;
+}
+
+int zc_adamw(void* p, void* g, void* m, void* v, int64_t n, int pdt, int gdt, int sdt, float lr, float b1, float b2,
+             float eps, float wd, float bc1, float bc2, int zero_grad, cudaStream_t st) {
+  return zc_adamw_guarded(p, g, m, v, n, pdt, gdt, sdt, lr, b1, b2, eps, wd, bc1, bc2, zero_grad, nullptr, st);
 }
 
 }  // extern "C"

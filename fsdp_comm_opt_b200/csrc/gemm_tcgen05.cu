@@ -21,6 +21,7 @@
 #include <cstdlib>
 
 #include "launch_util.h"
+#include "nvtx_util.h"
 #include "umma.cuh"
 
 namespace zc {
@@ -280,6 +281,7 @@ int zc_gemm_status_read_and_clear() {
 // C[M,N] (+)= op(A) op(B).  trans_a: A stored [K,M]; trans_b: B stored [N,K] (the nn.Linear weight).
 int zc_gemm_bf16(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K, int trans_a, int trans_b,
                  int accumulate, cudaStream_t st) {
+  ZC_NVTX_RANGE("zc_gemm_bf16");
   using namespace zc;
   if (M <= 0 || N <= 0 || K <= 0 || M % G_BM || N % 128 || K % G_BK) return ERR_UNSUPPORTED;
   if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(C)) & 15)

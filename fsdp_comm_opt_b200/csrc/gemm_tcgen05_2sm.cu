@@ -30,6 +30,7 @@
 #include <mutex>
 
 #include "launch_util.h"
+#include "nvtx_util.h"
 #include "umma.cuh"
 
 namespace zc {
@@ -121,7 +122,7 @@ struct Params {
   int64_t M, N, K;
   int accumulate;
   int group_m;         // tiles are walked in bands of `group_m` m-tiles, n-major inside a band
-  int64_t full_tiles;  // tiles computed whole; the remaining tiles are split along K
+  int full_tiles;      // tiles computed whole; the remaining tiles are split along K
   int split;           // K slices per tail tile (1: no tile is split)
   int* status;
 };
@@ -130,31 +131,31 @@ struct Params {
 // `group_m` m-tiles keeps that set a compact block of the output, so the A rows and B columns it
 // needs together stay in L2 however large K is (a full column of m-tiles does not once M * K
 // outgrows the cache).
-__device__ __forceinline__ void tile_coords(int64_t t, int64_t m_tiles, int64_t n_tiles, int group_m, int64_t& mi,
-                                            int64_t& ni) {
-  const int64_t per_band = (int64_t)group_m * n_tiles;
-  const int64_t band = t / per_band, r = t - band * per_band;
-  const int64_t rows = min((int64_t)group_m, m_tiles - band * group_m);
-  mi = band * group_m + r % rows;
+// (32-bit arithmetic: the issuing thread pays for every instruction between two tiles.)
+__device__ __forceinline__ void tile_coords(int t, int m_tiles, int n_tiles, int group_m, int& mi, int& ni) {
+  const int per_band = group_m * n_tiles;
+  const int band = t / per_band, r = t - band * per_band;
+  const int rows = min(group_m, m_tiles - band * group_m);
   ni = r / rows;
+  mi = band * group_m + (r - ni * rows);
 }
 
 // One unit of work: a tile and a range of its K blocks.
 struct Unit {
-  int64_t mi, ni;
+  int mi, ni;
   int kb0, kb1;
-  int64_t slice;  // index of the fp32 partial slab, or -1 for a whole tile
+  int slice;  // index of the fp32 partial slab, or -1 for a whole tile
 };
-__device__ __forceinline__ Unit unit_of(int64_t u, const Params& p, int64_t m_tiles, int64_t n_tiles, int k_blocks) {
+__device__ __forceinline__ Unit unit_of(int u, const Params& p, int m_tiles, int n_tiles, int k_blocks) {
   Unit w;
-  int64_t t = u;
+  int t = u;
   w.kb0 = 0;
   w.kb1 = k_blocks;
   w.slice = -1;
   if (u >= p.full_tiles) {
-    const int64_t r = u - p.full_tiles;
+    const int r = u - p.full_tiles;
     t = p.full_tiles + r / p.split;
-    const int s = (int)(r % p.split);
+    const int s = r % p.split;
     const int per = (k_blocks + p.split - 1) / p.split;
     w.kb0 = s * per;
     w.kb1 = min(k_blocks, w.kb0 + per);
@@ -198,11 +199,12 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
   cluster_sync_all();  // both CTAs' barriers are initialised before any remote arrival
   tc_fence_after_sync();
   const uint32_t tm = tmem_base;
-  const int64_t m_tiles = p.M / BM, n_tiles = p.N / BN;
-  const int k_blocks = (int)(p.K / BK);
-  const int64_t tiles = m_tiles * n_tiles;
-  const int64_t units = p.full_tiles + (tiles - p.full_tiles) * p.split;
-  const int64_t cluster_id = blockIdx.x >> 1, n_clusters = gridDim.x >> 1;
+  // edge tiles: rows / columns / K blocks past the matrix read as zeros (TMA fill) and are not stored
+  const int m_tiles = (int)((p.M + BM - 1) / BM), n_tiles = (int)((p.N + BN - 1) / BN);
+  const int k_blocks = (int)((p.K + BK - 1) / BK);
+  const int tiles = m_tiles * n_tiles;
+  const int units = p.full_tiles + (tiles - p.full_tiles) * p.split;
+  const int cluster_id = blockIdx.x >> 1, n_clusters = gridDim.x >> 1;
   const uint32_t smem_base = smem_u32(smem);
   const uint32_t full_base = smem_u32(&full[0]), empty_base = smem_u32(&empty[0]);
   bool ok = true;
@@ -211,10 +213,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
     if (lane == 0) {
       const uint32_t full0 = map_to_cta(full_base, 0);  // the even CTA's full[0]; full[s] is 8 s bytes on
       uint32_t s = 0, ph = 0;
-      for (int64_t u = cluster_id; u < units && ok; u += n_clusters) {
+      for (int u = cluster_id; u < units && ok; u += n_clusters) {
         const Unit w = unit_of(u, p, m_tiles, n_tiles, k_blocks);
-        const int m0 = (int)w.mi * BM + (int)rank * BM_CTA;
-        const int n0 = (int)w.ni * BN + (int)rank * BN_CTA;
+        const int m0 = w.mi * BM + (int)rank * BM_CTA;
+        const int n0 = w.ni * BN + (int)rank * BN_CTA;
         for (int kb = w.kb0; kb < w.kb1; ++kb) {
           if (!(ok = wait_bar(empty_base + 8 * s, ph ^ 1, &s_abort))) break;
           const uint32_t sa = smem_base + s * STAGE, sb = sa + A_BYTES;
@@ -253,7 +255,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
       const uint32_t accf_c0 = map_to_cta(smem_u32(&acc_full[0]), 0), accf_c1 = map_to_cta(smem_u32(&acc_full[0]), 1);
       const uint32_t acce = smem_u32(&acc_empty[0]);
       uint32_t s = 0, ph = 0, unit_it = 0;
-      for (int64_t u = cluster_id; u < units && ok; u += n_clusters, ++unit_it) {
+      for (int u = cluster_id; u < units && ok; u += n_clusters, ++unit_it) {
         const Unit w = unit_of(u, p, m_tiles, n_tiles, k_blocks);
         const uint32_t acc = unit_it & 1, acc_ph = (unit_it >> 1) & 1;
         if (!(ok = wait_bar(acce + 8 * acc, acc_ph ^ 1, &s_abort))) break;
@@ -285,7 +287,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
     const uint32_t accf = smem_u32(&acc_full[0]);
     const uint32_t acce_c0 = map_to_cta(smem_u32(&acc_empty[0]), 0);
     uint32_t unit_it = 0;
-    for (int64_t u = cluster_id; u < units && ok; u += n_clusters, ++unit_it) {
+    for (int u = cluster_id; u < units && ok; u += n_clusters, ++unit_it) {
       const Unit w = unit_of(u, p, m_tiles, n_tiles, k_blocks);
       const uint32_t acc = unit_it & 1, acc_ph = (unit_it >> 1) & 1;
       ok = wait_bar(accf + 8 * acc, acc_ph, &s_abort);
@@ -293,8 +295,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
       tc_fence_after_sync();
       const int row_in_tile = (int)rank * BM_CTA + quarter * 32 + lane;
       if (w.slice < 0) {
-        const int64_t row = w.mi * BM + row_in_tile;
-        __nv_bfloat16* crow = p.C + row * p.N + w.ni * BN;
+        const int64_t row = (int64_t)w.mi * BM + row_in_tile;
+        const int64_t col0 = (int64_t)w.ni * BN;
+        __nv_bfloat16* crow = p.C + row * p.N + col0;
+        const bool row_ok = row < p.M;
 #pragma unroll 1
         for (int c = 0; c < BN; c += 32) {
           uint32_t r[32];
@@ -302,6 +306,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
           tmem_ld_wait();
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
+            if (!row_ok || col0 + c + q * 8 >= p.N) continue;
             float f[8];
 #pragma unroll
             for (int j = 0; j < 8; ++j) f[j] = __uint_as_float(r[q * 8 + j]);
@@ -328,7 +333,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
         }
       } else {
         // K slice of a tail tile: fp32 partial sums, added up by gemm_2sm_fixup_kernel
-        float* prow = p.partial + (w.slice * BM + row_in_tile) * BN;
+        float* prow = p.partial + ((int64_t)w.slice * BM + row_in_tile) * BN;
 #pragma unroll 1
         for (int c = 0; c < BN; c += 32) {
           uint32_t r[32];
@@ -354,13 +359,14 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
 }
 
 // C tile (+)= sum over the K slices of its fp32 partials, rounded once to bf16.
-__global__ void __launch_bounds__(256) gemm_2sm_fixup_kernel(const Params p, int64_t m_tiles, int64_t n_tiles) {
-  const int64_t tail = blockIdx.y;  // index among the split tiles
-  int64_t mi, ni;
+__global__ void __launch_bounds__(256) gemm_2sm_fixup_kernel(const Params p, int m_tiles, int n_tiles) {
+  const int tail = blockIdx.y;  // index among the split tiles
+  int mi, ni;
   tile_coords(p.full_tiles + tail, m_tiles, n_tiles, p.group_m, mi, ni);
-  const float* base = p.partial + tail * p.split * (int64_t)(BM * BN);
+  const float* base = p.partial + (int64_t)tail * p.split * (BM * BN);
   for (int i = blockIdx.x * 256 + threadIdx.x; i < BM * BN / 8; i += gridDim.x * 256) {
     const int row = i / (BN / 8), c8 = i % (BN / 8);
+    if ((int64_t)mi * BM + row >= p.M || (int64_t)ni * BN + c8 * 8 >= p.N) continue;
     float f[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
     for (int s = 0; s < p.split; ++s) {
       const float4* src = reinterpret_cast<const float4*>(base + (int64_t)s * (BM * BN) + row * BN + c8 * 8);
@@ -368,7 +374,7 @@ __global__ void __launch_bounds__(256) gemm_2sm_fixup_kernel(const Params p, int
       f[0] += x.x; f[1] += x.y; f[2] += x.z; f[3] += x.w;
       f[4] += y.x; f[5] += y.y; f[6] += y.z; f[7] += y.w;
     }
-    uint4* dst = reinterpret_cast<uint4*>(p.C + (mi * BM + row) * p.N + ni * BN + c8 * 8);
+    uint4* dst = reinterpret_cast<uint4*>(p.C + ((int64_t)mi * BM + row) * p.N + (int64_t)ni * BN + c8 * 8);
     if (p.accumulate) {
       const uint4 old = *dst;
       const __nv_bfloat162* ob = reinterpret_cast<const __nv_bfloat162*>(&old);
@@ -462,13 +468,17 @@ extern "C" {
 
 int* zc_gemm_status_word();  // gemm_tcgen05.cu: the current device's GEMM status word
 
-// Same contract as zc_gemm_bf16, for M % 256 == 0, N % 256 == 0, K % 64 == 0; shares its status word
-// (zc_gemm_status_read_and_clear; code 8 = a bounded wait of this kernel expired).
+// Same contract as zc_gemm_bf16, for M, N and K multiples of 8 (edge tiles are zero-filled on load and
+// masked on store); shares its status word (zc_gemm_status_read_and_clear; code 8 = a bounded wait of
+// this kernel expired).
 int zc_gemm_bf16_2sm(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K, int trans_a, int trans_b,
                      int accumulate, cudaStream_t st) {
+  ZC_NVTX_RANGE("zc_gemm_bf16_2sm");
   using namespace zc;
   using namespace zc::g2;
-  if (M <= 0 || N <= 0 || K <= 0 || M % BM || N % BN || K % BK) return ERR_UNSUPPORTED;
+  if (M <= 0 || N <= 0 || K <= 0 || M % 8 || N % 8 || K % 8) return ERR_UNSUPPORTED;
+  const int64_t m_tiles = (M + BM - 1) / BM, n_tiles = (N + BN - 1) / BN;
+  if (m_tiles * n_tiles > (1 << 28)) return ERR_UNSUPPORTED;
   int* status = zc_gemm_status_word();
   if (!status) return ERR_BAD_ARG;
   if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(C)) & 15)
@@ -506,8 +516,8 @@ int zc_gemm_bf16_2sm(const void* A, const void* B, void* C, int64_t M, int64_t N
   static const int forced_split = getenv("ZC_GEMM_SPLIT") ? atoi(getenv("ZC_GEMM_SPLIT")) : -1;
   p.group_m = forced_gm > 0 ? forced_gm : 8;
   p.status = status;
-  const int64_t tiles = (M / BM) * (N / BN);
-  const int64_t k_blocks = K / BK;
+  const int64_t tiles = m_tiles * n_tiles;
+  const int64_t k_blocks = (K + BK - 1) / BK;
   const int clusters = (int)std::min<int64_t>(tiles, ds.clusters);
   // Tail: the tiles of the last, partial wave are cut into K slices so that every cluster has one
   // unit of about the same length to finish with.
@@ -519,7 +529,7 @@ int zc_gemm_bf16_2sm(const void* A, const void* B, void* C, int64_t M, int64_t N
     if (split < 2 || rem * 10 > (int64_t)clusters * 8) split = 1;  // a nearly full last wave is left alone
   }
   p.split = split;
-  p.full_tiles = split > 1 ? tiles - rem : tiles;
+  p.full_tiles = (int)(split > 1 ? tiles - rem : tiles);
   p.partial = nullptr;
   if (split > 1) {
     const size_t need = (size_t)rem * split * BM * BN;
@@ -531,7 +541,7 @@ int zc_gemm_bf16_2sm(const void* A, const void* B, void* C, int64_t M, int64_t N
       if (cudaMalloc(&ds.partial, want * sizeof(float)) != cudaSuccess) {
         cudaGetLastError();
         p.split = 1;
-        p.full_tiles = tiles;
+        p.full_tiles = (int)tiles;
       } else {
         ds.partial_elems = want;
       }
@@ -544,7 +554,7 @@ int zc_gemm_bf16_2sm(const void* A, const void* B, void* C, int64_t M, int64_t N
   else gemm_2sm_kernel<MAJOR_MN, MAJOR_MN><<<grid, THREADS, smem, st>>>(mapA, mapB, p);
   int rc = launch_status();
   if (rc == 0 && p.split > 1) {
-    gemm_2sm_fixup_kernel<<<dim3(16, (unsigned)rem), 256, 0, st>>>(p, M / BM, N / BN);
+    gemm_2sm_fixup_kernel<<<dim3(16, (unsigned)rem), 256, 0, st>>>(p, (int)m_tiles, (int)n_tiles);
     rc = launch_status();
   }
   return rc;

@@ -8,10 +8,14 @@
 //   [0, 4096)                 control: done[world] (uint32), local counters
 //   [4096, 4096 + flag_bytes) flags[2 parities][world sources][max_groups] (uint32)
 //   data                      2 parities x world source slots; slot = header table + records
-// A "group" is 64 chunks (65536 elements).  The pusher CTAs encode group after group and, after a
-// system-scope fence, release-store flag[parity][me][group] = seq on the receivers.  The decoder
-// CTAs acquire-load their local flags and decode as groups arrive, so push, transfer and decode
-// overlap inside one launch.  Buffers alternate by call parity; before pushing call `seq` a rank
+// A "group" is 8 to 64 chunks (the launcher picks the size so that small messages still spread over
+// many CTAs; the flag area is sized for groups of 64).  The pusher CTAs encode group after group and,
+// after a system-scope fence, release-store flag[parity][me][group] = seq on the receivers.  The
+// decoder warps (each on its own slice of eight chunks) acquire-load their local flags and decode as
+// groups arrive, so push, transfer and decode overlap inside one launch.  A decoder warp keeps the
+// next record's loads in flight while it decodes the current one (v2_prefetch / v2_decode_regs):
+// beside a GEMM only a few warps per SM are available, and it is the loads in flight that set the
+// decode rate.  Buffers alternate by call parity; before pushing call `seq` a rank
 // waits until every peer has reported done >= seq - 2 (it finished reading that parity).
 // Waits are bounded by wall time; on expiry the kernel records {code, peer, group} in the status
 // words of its own control block and returns normally, leaving the context usable.
@@ -22,6 +26,7 @@
 
 #include "codec_v2_dev.cuh"
 #include "launch_util.h"
+#include "nvtx_util.h"
 
 namespace zc {
 
@@ -73,13 +78,31 @@ __device__ __forceinline__ bool wait_ge(const uint32_t* p, uint32_t want, unsign
     __nanosleep(64);
   }
 }
+// (the last control word holds the device pointer of the library's health word, written by the launcher)
+constexpr int CW_HEALTH_PTR = 72;  // two words: 64-bit device address or 0
 __device__ __forceinline__ void set_status(uint8_t* local, int code, int peer, long long group) {
   uint32_t* c = ctrl(local);
+  int* health = *reinterpret_cast<int**>(c + CW_HEALTH_PTR);
+  if (health) atomicCAS(health, 0, code);
   if (atomicCAS(c + CW_STATUS, 0u, (uint32_t)code) == 0u) {
     c[CW_STATUS_PEER] = (uint32_t)peer;
     c[CW_STATUS_GROUP] = (uint32_t)group;
   }
 }
+
+// Debug-bounds build (-DZC_DEBUG_BOUNDS; compute-sanitizer's stand-in for stores into peer memory):
+// every record store is checked against the extent of the destination slot and every header store
+// against the header table before it is issued.  A store that would leave its slot is skipped and
+// recorded in the status words as code 3 with the peer and the chunk; nothing traps.
+#ifdef ZC_DEBUG_BOUNDS
+#define ZC_SLOT_OK(L, c, used, local, peer)                                                            \
+  (((c) >= 0 && (c) < (L).nc_max && (L).hdr_bytes + ((c) + 1) * (long long)V2_SLOT_BYTES <= (L).slot_bytes && \
+    (used) >= 0 && (used) <= V2_SLOT_BYTES)                                                             \
+       ? true                                                                                          \
+       : (set_status((local), 3, (peer), (c)), false))
+#else
+#define ZC_SLOT_OK(L, c, used, local, peer) true
+#endif
 
 // copy `bytes` (rounded up to 16) from shared memory to global/peer memory, warp-cooperative
 __device__ __forceinline__ void warp_copy16(uint8_t* dst, const uint8_t* src, int bytes, int lane) {
@@ -113,18 +136,30 @@ struct AgArgs {
   long long n;
   uint32_t seq;
   int push_ctas;
+  int gc;                 // chunks per group in this call: 8, 16, 32 or 64
   unsigned long long timeout_ns;
   SymmLayout L;
 };
 
+// lane 0 waits for *fl >= want; every lane learns the outcome and is ordered after the flag
+__device__ __forceinline__ bool warp_wait_flag(const uint32_t* fl, uint32_t want, unsigned long long limit_ns,
+                                               int lane) {
+  int ok = 1;
+  if (lane == 0) ok = wait_ge(fl, want, limit_ns) ? 1 : 0;
+  ok = __shfl_sync(FULL, ok, 0);
+  __syncwarp();
+  return ok != 0;
+}
+
 __global__ void __launch_bounds__(256) symm_all_gather_kernel(const AgArgs a) {
-  __shared__ __align__(16) uint8_t srec[8][V2_SLOT_BYTES];
+  __shared__ __align__(16) uint8_t srec[8][V2_SLOT_BYTES];  // pushers: record staging; decoders: escape staging
   __shared__ int s_ok;
   const SymmLayout& L = a.L;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int parity = a.seq & 1;
   const long long nc = (a.n + V2_CHUNK_ELEMS - 1) / V2_CHUNK_ELEMS;
-  const long long ngroups = (nc + GROUP_CHUNKS - 1) / GROUP_CHUNKS;
+  const int gc = a.gc;
+  const long long ngroups = (nc + gc - 1) / gc;
   if (tid == 0) s_ok = 1;
   __syncthreads();
 
@@ -146,8 +181,8 @@ __global__ void __launch_bounds__(256) symm_all_gather_kernel(const AgArgs a) {
     uint32_t hint = 0xFFFFFFFFu;  // window of the previous chunk this warp encoded
     int hint_esc = 0;
     for (long long g = blockIdx.x; g < ngroups; g += a.push_ctas) {
-      for (int it = 0; it < GROUP_CHUNKS / 8; ++it) {
-        const long long c = g * GROUP_CHUNKS + it * 8 + warp;
+      for (int it = 0; it < gc / 8; ++it) {
+        const long long c = g * gc + it * 8 + warp;
         if (c >= nc) break;
         const long long e0 = c * V2_CHUNK_ELEMS + lane * 32;
         LaneIn li;
@@ -158,6 +193,10 @@ __global__ void __launch_bounds__(256) symm_all_gather_kernel(const AgArgs a) {
         const uint32_t hdr = v2_encode_chunk_hint(s, srec[warp], lane, hint, hint_esc);
         __syncwarp();
         const int used = v2_record_bytes(hdr);
+        if (!ZC_SLOT_OK(L, c, used, a.local, L.rank)) {
+          __syncwarp();
+          continue;
+        }
         if (a.mc) {
           uint8_t* slot = slot_ptr(a.mc, L, parity, L.rank);
           warp_copy16_mc(slot + L.hdr_bytes + c * V2_SLOT_BYTES, srec[warp], used, lane);
@@ -180,34 +219,47 @@ __global__ void __launch_bounds__(256) symm_all_gather_kernel(const AgArgs a) {
     if (lane == 0 && pushed) atomicAdd(reinterpret_cast<unsigned long long*>(ctrl(a.local) + CW_WIRE_LO), pushed);
     return;
   }
-  // ---- decoder ---------------------------------------------------------------------------------
+  // ---- decoder: each warp takes items (group, source, slice of eight chunks) -----------------------
   const int dec_ctas = gridDim.x - a.push_ctas;
-  const long long items = ngroups * (L.world - 1);
-  for (long long i = (long long)blockIdx.x - a.push_ctas; i < items; i += dec_ctas) {
-    const long long g = i / (L.world - 1);
-    int src = (int)(i % (L.world - 1));
+  const int subs = gc / 8;
+  const long long items = ngroups * (L.world - 1) * subs;
+  const long long wstride = (long long)dec_ctas * 8;
+  volatile int* okp = &s_ok;
+  uint8_t* esc = srec[warp];
+  for (long long i = ((long long)blockIdx.x - a.push_ctas) * 8 + warp; i < items && *okp; i += wstride) {
+    const int sub = (int)(i % subs);
+    const long long gi = i / subs;
+    int src = (int)(gi % (L.world - 1));
+    const long long g = gi / (L.world - 1);
     if (src >= L.rank) ++src;
-    uint32_t* fl = flag_ptr(a.local, L, parity, src, g);
-    if (tid == 0 && !wait_ge(fl, a.seq, a.timeout_ns)) {
-      set_status(a.local, 2, src, g);
-      s_ok = 0;
+    const long long c0 = g * gc + sub * 8;
+    if (c0 >= nc) continue;
+    const int cnt = (int)min((long long)8, nc - c0);
+    if (!warp_wait_flag(flag_ptr(a.local, L, parity, src, g), a.seq, a.timeout_ns, lane)) {
+      if (lane == 0) {
+        set_status(a.local, 2, src, g);
+        *okp = 0;
+      }
+      break;
     }
-    __syncthreads();
-    if (!s_ok) break;
-    (void)ld_acquire_sys(fl);  // every thread orders its own reads of the staged bytes after the flag
     const uint8_t* slot = slot_ptr(a.local, L, parity, src);
+    const uint8_t* recs = slot + L.hdr_bytes + c0 * V2_SLOT_BYTES;
     uint16_t* dst = a.out + (long long)src * a.n;
     const bool al = (reinterpret_cast<uintptr_t>(dst) & 15) == 0;
-    for (int it = 0; it < GROUP_CHUNKS / 8; ++it) {
-      const long long c = g * GROUP_CHUNKS + it * 8 + warp;
-      if (c >= nc) break;
-      const uint32_t hdr = __ldcg(reinterpret_cast<const uint32_t*>(slot) + c);
+    // the item's eight headers in one load, then record k+1 in flight while record k is decoded
+    const uint32_t myhdr = lane < cnt ? __ldcg(reinterpret_cast<const uint32_t*>(slot) + c0 + lane) : 0u;
+    RecRegs cur, nxt;
+    v2_prefetch(recs, __shfl_sync(FULL, myhdr, 0), lane, cur);
+    for (int k = 0; k < cnt; ++k) {
+      const uint32_t hn = __shfl_sync(FULL, myhdr, (k + 1) & 7);
+      if (k + 1 < cnt) v2_prefetch(recs + (long long)(k + 1) * V2_SLOT_BYTES, hn, lane, nxt);
       LaneSplit s;
-      v2_decode_chunk(slot + L.hdr_bytes + c * V2_SLOT_BYTES, hdr, lane, s);
+      v2_decode_regs(cur, esc, lane, s);
       LaneIn o;
       join_lane(s, o);
-      const long long e0 = c * V2_CHUNK_ELEMS + lane * 32;
+      const long long e0 = (c0 + k) * V2_CHUNK_ELEMS + lane * 32;
       store_lane(dst + e0, a.n - e0, al, o);
+      cur = nxt;
     }
   }
   // last decoder CTA of this call tells every peer that this rank is done with the parity buffer
@@ -237,6 +289,7 @@ struct RsArgs {
   long long shard;
   uint32_t seq;
   int push_ctas, in_fp32, out_fp32;
+  int gc;                 // chunks per group in this call: 8, 16, 32 or 64
   float scale;
   unsigned long long timeout_ns;
   SymmLayout L;
@@ -273,14 +326,15 @@ __device__ __forceinline__ void load_lane_f32(const void* base, bool fp32, long 
   }
 }
 
-__global__ void __launch_bounds__(256) symm_reduce_scatter_kernel(const RsArgs a) {
-  __shared__ __align__(16) uint8_t srec[8][V2_SLOT_BYTES];
+__global__ void __launch_bounds__(256, 2) symm_reduce_scatter_kernel(const RsArgs a) {
+  __shared__ __align__(16) uint8_t srec[8][V2_SLOT_BYTES];  // pushers: record staging; decoders: escape staging
   __shared__ int s_ok;
   const SymmLayout& L = a.L;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int parity = a.seq & 1;
   const long long nc = (a.shard + V2_CHUNK_ELEMS - 1) / V2_CHUNK_ELEMS;
-  const long long ngroups = (nc + GROUP_CHUNKS - 1) / GROUP_CHUNKS;
+  const int gc = a.gc;
+  const long long ngroups = (nc + gc - 1) / gc;
   if (tid == 0) s_ok = 1;
   __syncthreads();
 
@@ -303,8 +357,8 @@ __global__ void __launch_bounds__(256) symm_reduce_scatter_kernel(const RsArgs a
       int q = (int)(i % (L.world - 1));
       q = (L.rank + 1 + q) % L.world;  // start with the next rank: spreads traffic over peers
       uint8_t* slot = slot_ptr(a.peers[q], L, parity, L.rank);
-      for (int it = 0; it < GROUP_CHUNKS / 8; ++it) {
-        const long long c = g * GROUP_CHUNKS + it * 8 + warp;
+      for (int it = 0; it < gc / 8; ++it) {
+        const long long c = g * gc + it * 8 + warp;
         if (c >= nc) break;
         const long long e0 = c * V2_CHUNK_ELEMS + lane * 32;
         const long long valid = a.shard - e0;
@@ -334,6 +388,10 @@ __global__ void __launch_bounds__(256) symm_reduce_scatter_kernel(const RsArgs a
         const uint32_t hdr = v2_encode_chunk_hint(s, srec[warp], lane, hint, hint_esc);
         __syncwarp();
         const int used = v2_record_bytes(hdr);
+        if (!ZC_SLOT_OK(L, c, used, a.local, q)) {
+          __syncwarp();
+          continue;
+        }
         warp_copy16(slot + L.hdr_bytes + c * V2_SLOT_BYTES, srec[warp], used, lane);
         if (lane == 0) {
           reinterpret_cast<uint32_t*>(slot)[c] = hdr;
@@ -348,65 +406,87 @@ __global__ void __launch_bounds__(256) symm_reduce_scatter_kernel(const RsArgs a
     if (lane == 0 && pushed) atomicAdd(reinterpret_cast<unsigned long long*>(ctrl(a.local) + CW_WIRE_LO), pushed);
     return;
   }
-  // ---- decoder + reduce ------------------------------------------------------------------------
+  // ---- decoder + reduce: each warp takes items (group, slice of eight chunks) -----------------------
   const int dec_ctas = gridDim.x - a.push_ctas;
-  for (long long g = (long long)blockIdx.x - a.push_ctas; g < ngroups; g += dec_ctas) {
-    if (tid < L.world && tid != L.rank) {
-      if (!wait_ge(flag_ptr(a.local, L, parity, tid, g), a.seq, a.timeout_ns)) {
-        set_status(a.local, 2, tid, g);
-        s_ok = 0;
-      }
+  const int subs = gc / 8;
+  const long long items = ngroups * subs;
+  const long long wstride = (long long)dec_ctas * 8;
+  volatile int* okp = &s_ok;
+  uint8_t* esc = srec[warp];
+  const bool is_src = lane < L.world && lane != L.rank;   // lane l looks after source rank l
+  const int p0 = L.rank == 0 ? 1 : 0;                     // first source in rank order
+  for (long long i = ((long long)blockIdx.x - a.push_ctas) * 8 + warp; i < items && *okp; i += wstride) {
+    const int sub = (int)(i % subs);
+    const long long g = i / subs;
+    const long long c0 = g * gc + sub * 8;
+    if (c0 >= nc) continue;
+    const int cnt = (int)min((long long)8, nc - c0);
+    int ok = 1;
+    if (is_src && !wait_ge(flag_ptr(a.local, L, parity, lane, g), a.seq, a.timeout_ns)) {
+      set_status(a.local, 2, lane, g);
+      ok = 0;
     }
-    __syncthreads();
-    if (!s_ok) break;
-    for (int q = 0; q < L.world; ++q)
-      if (q != L.rank) (void)ld_acquire_sys(flag_ptr(a.local, L, parity, q, g));
-    for (int it = 0; it < GROUP_CHUNKS / 8; ++it) {
-      const long long c = g * GROUP_CHUNKS + it * 8 + warp;
-      if (c >= nc) break;
+    ok = __all_sync(FULL, ok);
+    __syncwarp();
+    if (!ok) {
+      if (lane == 0) *okp = 0;
+      break;
+    }
+    const uint8_t* myslot = slot_ptr(a.local, L, parity, is_src ? lane : p0);
+    uint32_t myhdr = is_src ? __ldcg(reinterpret_cast<const uint32_t*>(myslot) + c0) : 0u;
+    RecRegs cur, nxt;
+    v2_prefetch(slot_ptr(a.local, L, parity, p0) + L.hdr_bytes + c0 * V2_SLOT_BYTES, __shfl_sync(FULL, myhdr, p0), lane,
+                cur);
+    for (int k = 0; k < cnt; ++k) {
+      const long long c = c0 + k;
       const long long e0 = c * V2_CHUNK_ELEMS + lane * 32;
       const long long valid = a.shard - e0;
+      const uint32_t nexthdr = (is_src && k + 1 < cnt) ? __ldcg(reinterpret_cast<const uint32_t*>(myslot) + c + 1) : 0u;
+      // fixed order (this rank's own row, then the sources by rank): a deterministic sum
       float acc[32];
-#pragma unroll
-      for (int k = 0; k < 32; ++k) acc[k] = 0.f;
-      for (int p = 0; p < L.world; ++p) {  // fixed rank order: deterministic sum
-        if (p == L.rank) {
-          float v[32];
-          load_lane_f32(a.in, a.in_fp32, (long long)p * a.shard + e0, valid, v);
-#pragma unroll
-          for (int k = 0; k < 32; ++k) acc[k] += v[k];
-        } else {
-          const uint8_t* slot = slot_ptr(a.local, L, parity, p);
-          const uint32_t hdr = __ldcg(reinterpret_cast<const uint32_t*>(slot) + c);
-          LaneSplit s;
-          v2_decode_chunk(slot + L.hdr_bytes + c * V2_SLOT_BYTES, hdr, lane, s);
-          LaneIn o;
-          join_lane(s, o);
-#pragma unroll
-          for (int k = 0; k < 16; ++k) {
-            acc[2 * k] += bf16_bits_to_f(o.w[k] & 0xFFFFu);
-            acc[2 * k + 1] += bf16_bits_to_f(o.w[k] >> 16);
-          }
+      load_lane_f32(a.in, a.in_fp32, (long long)L.rank * a.shard + e0, valid, acc);
+      for (int p = 0; p < L.world; ++p) {
+        if (p == L.rank) continue;
+        // the record decoded after this one: the next source of this chunk, else the first source of the next
+        int pn = p + 1;
+        if (pn == L.rank) ++pn;
+        if (pn < L.world) {
+          v2_prefetch(slot_ptr(a.local, L, parity, pn) + L.hdr_bytes + c * V2_SLOT_BYTES, __shfl_sync(FULL, myhdr, pn),
+                      lane, nxt);
+        } else if (k + 1 < cnt) {
+          v2_prefetch(slot_ptr(a.local, L, parity, p0) + L.hdr_bytes + (c + 1) * V2_SLOT_BYTES,
+                      __shfl_sync(FULL, nexthdr, p0), lane, nxt);
         }
+        LaneSplit s;
+        v2_decode_regs(cur, esc, lane, s);
+        LaneIn o;
+        join_lane(s, o);
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          acc[2 * j] += bf16_bits_to_f(o.w[j] & 0xFFFFu);
+          acc[2 * j + 1] += bf16_bits_to_f(o.w[j] >> 16);
+        }
+        cur = nxt;
       }
+      myhdr = nexthdr;
       if (valid <= 0) continue;
       if (a.out_fp32) {
         float* dst = reinterpret_cast<float*>(a.out) + e0;
         if (valid >= 32 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
 #pragma unroll
-          for (int k = 0; k < 8; ++k)
-            reinterpret_cast<float4*>(dst)[k] = make_float4(acc[4 * k] * a.scale, acc[4 * k + 1] * a.scale,
-                                                            acc[4 * k + 2] * a.scale, acc[4 * k + 3] * a.scale);
+          for (int j = 0; j < 8; ++j)
+            reinterpret_cast<float4*>(dst)[j] = make_float4(acc[4 * j] * a.scale, acc[4 * j + 1] * a.scale,
+                                                            acc[4 * j + 2] * a.scale, acc[4 * j + 3] * a.scale);
         } else {
 #pragma unroll
-          for (int k = 0; k < 32; ++k)
-            if (k < valid) dst[k] = acc[k] * a.scale;
+          for (int j = 0; j < 32; ++j)
+            if (j < valid) dst[j] = acc[j] * a.scale;
         }
       } else {
         LaneIn o;
 #pragma unroll
-        for (int k = 0; k < 16; ++k)
-          o.w[k] = f_to_bf16_bits(acc[2 * k] * a.scale) | (f_to_bf16_bits(acc[2 * k + 1] * a.scale) << 16);
+        for (int j = 0; j < 16; ++j)
+          o.w[j] = f_to_bf16_bits(acc[2 * j] * a.scale) | (f_to_bf16_bits(acc[2 * j + 1] * a.scale) << 16);
         uint16_t* dst = reinterpret_cast<uint16_t*>(a.out) + e0;
         store_lane(dst, valid, (reinterpret_cast<uintptr_t>(dst) & 15) == 0, o);
       }
@@ -580,6 +660,16 @@ __global__ void __launch_bounds__(256) symm_all_gather_int8_kernel(const AgArgs 
   }
 }
 
+// Chunks per group for a message of `nc` chunks per source: the largest of 64, 32, 16, 8 that still
+// gives every pusher CTA about two groups, subject to the flag area (one flag per 64 chunks of nc_max).
+// Every rank must arrive at the same value, so it depends on the message and the device only
+// (`push_ctas` is the SM count here, not the caller's CTA budget).
+static int pick_group_chunks(long long nc, int push_ctas, int max_groups) {
+  int gc = 64;
+  while (gc > 8 && (nc + gc - 1) / gc < 2LL * push_ctas && (nc + gc / 2 - 1) / (gc / 2) <= max_groups) gc >>= 1;
+  return gc;
+}
+
 static SymmLayout make_layout(int world, int rank, long long nc_max) {
   SymmLayout L;
   L.world = world;
@@ -608,15 +698,26 @@ long long zc_symm_buffer_bytes(int world, long long nc_max) {
 int zc_symm_all_gather(const void* in, void* out, void* const* peers, void* local, void* mc, long long n, int rank,
                        int world, long long nc_max, unsigned seq, int push_ctas, int dec_ctas, double timeout_s,
                        cudaStream_t st) {
+  ZC_NVTX_RANGE("zc_symm_all_gather");
   using namespace zc;
   const long long nc = (n + V2_CHUNK_ELEMS - 1) / V2_CHUNK_ELEMS;
-  if (world < 2 || world > 64 || nc > nc_max || nc == 0 || push_ctas < 1 || dec_ctas < 1) return ERR_BAD_ARG;
+  // push_ctas == 0 (decode what has already arrived) or dec_ctas == 0 (encode and push only) run one
+  // half of the collective: the halves of different ranks can then be run one after the other on a
+  // single GPU, pushers first, without any kernel waiting for another launch
+  if (world < 2 || world > 64 || nc > nc_max || nc == 0 || push_ctas < 0 || dec_ctas < 0 || push_ctas + dec_ctas < 1)
+    return ERR_BAD_ARG;
   AgArgs a;
   a.in = (const uint16_t*)in; a.out = (uint16_t*)out; a.peers = (uint8_t* const*)peers; a.local = (uint8_t*)local;
-  a.mc = (uint8_t*)mc; a.n = n; a.seq = seq; a.push_ctas = push_ctas;
+  a.mc = (uint8_t*)mc; a.n = n; a.seq = seq;
   a.timeout_ns = (unsigned long long)(timeout_s * 1e9);
   a.L = make_layout(world, rank, nc_max);
-  symm_all_gather_kernel<<<push_ctas + dec_ctas, 256, 0, st>>>(a);
+  a.gc = pick_group_chunks(nc, sm_count(), a.L.max_groups);
+  // no more CTAs than there is work: small messages pay for the launch, not for idle CTAs
+  const long long ngroups = (nc + a.gc - 1) / a.gc;
+  a.push_ctas = (int)std::min<long long>(push_ctas, ngroups);
+  const long long dec_items = ngroups * (world - 1) * (a.gc / 8);
+  const int dec = (int)std::min<long long>(dec_ctas, (dec_items + 7) / 8);
+  symm_all_gather_kernel<<<a.push_ctas + dec, 256, 0, st>>>(a);
   return launch_status();
 }
 
@@ -624,16 +725,25 @@ int zc_symm_reduce_scatter(const void* in, void* out, void* residual, void* cons
                            long long shard, int rank, int world, long long nc_max, unsigned seq, int in_fp32,
                            int out_fp32, float scale, int push_ctas, int dec_ctas, double timeout_s,
                            cudaStream_t st) {
+  ZC_NVTX_RANGE("zc_symm_reduce_scatter");
   using namespace zc;
   const long long nc = (shard + V2_CHUNK_ELEMS - 1) / V2_CHUNK_ELEMS;
-  if (world < 2 || world > 64 || nc > nc_max || nc == 0 || push_ctas < 1 || dec_ctas < 1) return ERR_BAD_ARG;
+  if (world < 2 || world > 32 || nc > nc_max || nc == 0 || push_ctas < 0 || dec_ctas < 0 || push_ctas + dec_ctas < 1)
+    return ERR_BAD_ARG;
   RsArgs a;
   a.in = in; a.out = out; a.residual = (uint16_t*)residual; a.peers = (uint8_t* const*)peers;
-  a.local = (uint8_t*)local; a.shard = shard; a.seq = seq; a.push_ctas = push_ctas; a.in_fp32 = in_fp32;
+  a.local = (uint8_t*)local; a.shard = shard; a.seq = seq; a.in_fp32 = in_fp32;
   a.out_fp32 = out_fp32; a.scale = scale;
   a.timeout_ns = (unsigned long long)(timeout_s * 1e9);
   a.L = make_layout(world, rank, nc_max);
-  symm_reduce_scatter_kernel<<<push_ctas + dec_ctas, 256, 0, st>>>(a);
+  // a pusher item is (destination, group): world - 1 times as many items as groups
+  a.gc = pick_group_chunks(nc * (world - 1), sm_count(), a.L.max_groups * (world - 1));
+  while (a.gc < 64 && (nc + a.gc - 1) / a.gc > a.L.max_groups) a.gc <<= 1;
+  const long long ngroups = (nc + a.gc - 1) / a.gc;
+  a.push_ctas = (int)std::min<long long>(push_ctas, ngroups * (world - 1));
+  const long long dec_items = ngroups * (a.gc / 8);
+  const int dec = (int)std::min<long long>(dec_ctas, (dec_items + 7) / 8);
+  symm_reduce_scatter_kernel<<<a.push_ctas + dec, 256, 0, st>>>(a);
   return launch_status();
 }
 
@@ -642,12 +752,13 @@ int zc_symm_reduce_scatter(const void* in, void* out, void* residual, void* cons
 int zc_symm_all_gather_int8(const void* in, void* out, void* const* peers, void* local, void* mc, long long n,
                             int rank, int world, long long nc_max, unsigned seq, int push_ctas, int dec_ctas,
                             double timeout_s, cudaStream_t st) {
+  ZC_NVTX_RANGE("zc_symm_all_gather_int8");
   using namespace zc;
   const long long nc = (n + V2_CHUNK_ELEMS - 1) / V2_CHUNK_ELEMS;
   if (world < 2 || world > 64 || nc > nc_max || nc == 0 || push_ctas < 1 || dec_ctas < 1) return ERR_BAD_ARG;
   AgArgs a;
   a.in = (const uint16_t*)in; a.out = (uint16_t*)out; a.peers = (uint8_t* const*)peers; a.local = (uint8_t*)local;
-  a.mc = (uint8_t*)mc; a.n = n; a.seq = seq; a.push_ctas = push_ctas;
+  a.mc = (uint8_t*)mc; a.n = n; a.seq = seq; a.push_ctas = push_ctas; a.gc = GROUP_CHUNKS;
   a.timeout_ns = (unsigned long long)(timeout_s * 1e9);
   a.L = make_layout(world, rank, nc_max);
   uint32_t* word = reinterpret_cast<uint32_t*>(local) + CW_ABSMAX;
@@ -656,6 +767,15 @@ int zc_symm_all_gather_int8(const void* in, void* out, void* const* peers, void*
   absmax_bf16_kernel<<<grid, 256, 0, st>>>((const uint16_t*)in, n, word);
   symm_all_gather_int8_kernel<<<push_ctas + dec_ctas, 256, 0, st>>>(a);
   return launch_status();
+}
+
+// 1 when this library was compiled with -DZC_DEBUG_BOUNDS
+int zc_debug_bounds_build() {
+#ifdef ZC_DEBUG_BOUNDS
+  return 1;
+#else
+  return 0;
+#endif
 }
 
 }  // extern "C"

@@ -37,8 +37,12 @@ class RMSNorm(nn.Module):
     def reset_parameters(self):
         nn.init.ones_(self.weight)
 
-    def forward(self, x):
-        return norm.rms_norm(x, self.weight, self.eps)
+    def forward(self, x, residual=None):
+        """``rms_norm(x)``, or ``rms_norm(x + residual)`` from one kernel when a pending residual
+        branch is handed over."""
+        if residual is None:
+            return norm.rms_norm(x, self.weight, self.eps)
+        return norm.add_rms_norm(residual, x, self.weight, self.eps)[0]
 
 
 class Embedding(nn.Embedding):
@@ -79,19 +83,25 @@ class LlamaBlock(nn.Module):
         self.attn_norm = RMSNorm(d, cfg.norm_eps)
         self.mlp_norm = RMSNorm(d, cfg.norm_eps)
 
-    def forward(self, x):
+    def forward(self, x, delta=None):
+        """The residual stream is ``x + delta``: a block hands its MLP output to the next block
+        unadded, and the next block's first normalisation kernel does the add (so no stand-alone
+        elementwise add runs between blocks).  Returns ``(x, delta)``."""
         cfg = self.cfg
         B, S, d = x.shape
         hd, Hq, Hkv = cfg.head_dim, cfg.n_heads, cfg.n_kv_heads
         cos, sin = rope.cached_tables(S, hd, cfg.rope_theta, x.device)
-        h = self.attn_norm(x)
+        if delta is None:
+            h = self.attn_norm(x)
+        else:
+            h, x = norm.add_rms_norm(delta, x, self.attn_norm.weight, self.attn_norm.eps)
         qkv = self.wqkv(h).view(B, S, Hq + 2 * Hkv, hd)
         o = attn_ops.causal_attention(qkv, Hq, Hkv, None, cos, sin)
         a = self.wo(o.view(B, S, Hq * hd))
         h2, x = norm.add_rms_norm(a, x, self.mlp_norm.weight, self.mlp_norm.eps)
         gu = self.wgu(h2).view(B * S, 2 * cfg.ffn)
         m = self.wd(swiglu.swiglu(gu)).view(B, S, d)
-        return x + m
+        return x, m
 
 
 class LlamaBackbone(nn.Module):
@@ -120,13 +130,13 @@ class LlamaForCausalLM(nn.Module):
     def forward(self, input_ids: torch.Tensor, labels: Optional[torch.Tensor] = None,
                 return_logits: bool = False, **_ignored) -> CausalLMOutput:
         B, S = input_ids.shape
-        x = self.model.embed_tokens(input_ids)
+        x, delta = self.model.embed_tokens(input_ids), None
         for layer in self.model.layers:
             if self.activation_checkpointing and torch.is_grad_enabled():
-                x = checkpoint(layer, x, use_reentrant=False)
+                x, delta = checkpoint(layer, x, delta, use_reentrant=False)
             else:
-                x = layer(x)
-        x = self.model.norm(x)
+                x, delta = layer(x, delta)
+        x = self.model.norm(x, delta)
         logits = self.lm_head(x)
         loss = None
         if labels is not None:

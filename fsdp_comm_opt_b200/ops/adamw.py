@@ -8,7 +8,10 @@ and checkpoints are interchangeable with the reference's optimizer
 
 On CUDA each shard is updated by one launch of ``zc_adamw`` (one read of p, g, m, v and one write
 of p, m, v; bias correction and decoupled weight decay folded in; optional gradient zeroing in the
-same pass).  CPU tensors use the same arithmetic in PyTorch.
+same pass).  The launch is guarded by the library's health word: when a fused collective of the step
+ran into its bounded wait (and therefore left wrong data behind) the kernel returns without
+touching parameters or moments, so the bad step is never applied even though the host only learns
+of it at its next synchronisation.  CPU tensors use the same arithmetic in PyTorch.
 """
 from __future__ import annotations
 
@@ -76,11 +79,14 @@ class FusedAdamW(torch.optim.Optimizer):
                 if pl.is_cuda:
                     if not (pl.is_contiguous() and gl.is_contiguous()):
                         raise ValueError("FusedAdamW needs contiguous shards")
-                    _lib.check(_lib.cuda().zc_adamw(
+                    lib = _lib.cuda()
+                    with torch.cuda.device(pl.device):
+                        guard = lib.zc_health_word()
+                    _lib.check(lib.zc_adamw_guarded(
                         pl.data_ptr(), gl.data_ptr(), ml.data_ptr(), vl.data_ptr(), pl.numel(),
                         _DT[pl.dtype], _DT[gl.dtype], _DT[ml.dtype], float(lr), float(b1), float(b2),
                         float(eps), float(wd), float(bc1), float(bc2), int(self.zero_grad_in_step),
-                        _lib.stream_ptr(pl.device)), "zc_adamw")
+                        guard, _lib.stream_ptr(pl.device)), "zc_adamw")
                     self.kernel_launches += 1
                 else:
                     g = gl.float()

@@ -87,28 +87,45 @@ def main():
                  frac=round(ours / tf, 3) if ours else None, frac_of=tag, l2="flushed between launches")
     if "attn" in only:
         for B, S, Hq, Hkv, D in [(1, 4096, 32, 8, 128), (2, 4096, 40, 40, 128), (1, 8192, 32, 8, 128)]:
+            if args.case not in f"B{B} S{S} H{Hq}/{Hkv}":
+                continue
             qkv = (torch.randn(B, S, Hq + 2 * Hkv, D, device=dev) * 0.5).bfloat16().requires_grad_()
             o = attention.causal_attention(qkv, Hq, Hkv)
             g = torch.randn_like(o)
             fl = 4.0 * B * Hq * S * S * D / 2
-            ms_f = _time(lambda: attention.causal_attention(qkv.detach(), Hq, Hkv), args.iters, flush=flush)
+            ms_f = _time(lambda: attention.causal_attention(qkv.detach(), Hq, Hkv), args.iters, args.warmup, flush=flush)
             ms_b = _time(lambda: torch.autograd.grad(attention.causal_attention(qkv, Hq, Hkv), qkv, g), args.iters,
-                         flush=flush) - ms_f
-            q, k, v = (t.transpose(1, 2) for t in qkv.detach().split([Hq, Hkv, Hkv], dim=2))
-            ms_sdpa = _time(lambda: torch.nn.functional.scaled_dot_product_attention(q, k, v, is_causal=True,
-                                                                                     enable_gqa=True),
-                            args.iters, flush=flush)
+                         args.warmup, flush=flush) - ms_f
+            # the library attention the reference's model gets (PyTorch SDPA), forward and backward
+            q, k, v = (t.transpose(1, 2).contiguous().requires_grad_() for t in
+                       qkv.detach().split([Hq, Hkv, Hkv], dim=2))
+            sdpa = lambda: torch.nn.functional.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=True)
+            with torch.no_grad():
+                ms_sdpa = _time(sdpa, args.iters, args.warmup, flush=flush)
+            go = torch.randn_like(sdpa())
+            ms_sdpa_fb = _time(lambda: torch.autograd.grad(sdpa(), (q, k, v), go), args.iters, args.warmup, flush=flush)
+            ms_sdpa_b = ms_sdpa_fb - ms_sdpa
             emit(kernel="attn", B=B, S=S, Hq=Hq, Hkv=Hkv, D=D, fwd_tflops=round(fl / ms_f / 1e9, 1),
                  bwd_tflops=round(2.5 * fl / max(ms_b, 1e-6) / 1e9, 1), sdpa_fwd_tflops=round(fl / ms_sdpa / 1e9, 1),
+                 sdpa_bwd_tflops=round(2.5 * fl / max(ms_sdpa_b, 1e-6) / 1e9, 1),
+                 ms=dict(fwd=round(ms_f, 4), bwd=round(ms_b, 4), sdpa_fwd=round(ms_sdpa, 4), sdpa_bwd=round(ms_sdpa_b, 4)),
                  frac_fwd=round(fl / ms_f / 1e9 / tf, 3), frac_of=tag, l2="flushed between launches")
     if "codec" in only:
-        n = 1 << 28  # 512 MB of bf16 > L2
+        n = 1 << (27 if args.case == "2^27" else 28)  # 256 / 512 MB of bf16 > L2
         x = (torch.randn(n, device=dev) * 0.02).bfloat16()
         rec, hdr = codec.v2_encode(x)
         out = torch.empty_like(x)
         used = int(codec.v2_record_bytes(hdr).sum().item()) + 4 * hdr.numel()
-        ms_e = _time(lambda: codec.v2_encode(x, rec, hdr), args.iters)
-        ms_d = _time(lambda: codec.v2_decode(rec, hdr, n, out), args.iters)
+        ms_e = _time(lambda: codec.v2_encode(x, rec, hdr), args.iters, args.warmup)
+        ms_d = _time(lambda: codec.v2_decode(rec, hdr, n, out), args.iters, args.warmup)
+        # the decoder with the CTA budget it has inside a fused collective (one 8-warp CTA per SM)
+        lib = _lib.cuda()
+        nsm = torch.cuda.get_device_properties(dev).multi_processor_count
+        for ctas in (nsm, nsm // 2):
+            ms_c = _time(lambda: lib.zc_v2_decode_ctas(rec.data_ptr(), hdr.data_ptr(), n, out.data_ptr(), ctas,
+                                                       _lib.stream_ptr()), args.iters, args.warmup)
+            emit(kernel="v2_decode_capped", ctas=ctas, elems=n, gbs=round((2 * n + used) / ms_c / 1e6, 1),
+                 frac=round((2 * n + used) / ms_c / 1e6 / hbm, 3), frac_of=tag, gelems_per_s=round(n / ms_c / 1e6, 1))
         emit(kernel="v2_encode", elems=n, gbs=round((2 * n + used) / ms_e / 1e6, 1),
              frac=round((2 * n + used) / ms_e / 1e6 / hbm, 3), frac_of=tag, bytes_per_elem=round(used / n, 4),
              l2="input larger than L2")
@@ -129,6 +146,57 @@ def main():
              frac=round((2 * n + b1 + 2 * cnt) / ms_e1 / 1e6 / hbm, 3), frac_of=tag, bytes_per_elem=round(b1 / n, 4))
         emit(kernel="v1_decode_split", elems=n, gbs=round((2 * n + b1) / ms_d1 / 1e6, 1),
              frac=round((2 * n + b1) / ms_d1 / 1e6 / hbm, 3), frac_of=tag)
+    if "refcodec" in only:
+        # the reference's own kernels (built from its sources under baseline/_ref) on the same input,
+        # beside this package's v1 and v2 kernels: encode = its K3 + K4 launches, decode = its K9
+        import glob
+        import importlib.util
+
+        root = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+        hits = glob.glob(os.path.join(root, "baseline", "_ref", "zipccl", "hopper_fastzip2*.so"))
+        if not hits:
+            emit(kernel="reference_codec", unavailable="baseline/_ref/zipccl/hopper_fastzip2*.so not found")
+        else:
+            spec = importlib.util.spec_from_file_location("hopper_fastzip2", hits[0])
+            ref = importlib.util.module_from_spec(spec)
+            spec.loader.exec_module(ref)
+            n = 1 << 27
+            x = (torch.randn(n, device=dev) * 0.02).bfloat16()
+            n_8 = torch.full((1,), n, dtype=torch.int32, device=dev)
+            bases = torch.full((256,), 116, dtype=torch.int32, device=dev)
+            det = torch.empty(codec.v1_det_bytes(n), dtype=torch.uint8, device=dev)
+            scr = torch.empty(codec.align128(n), dtype=torch.uint8, device=dev)
+            esc = torch.empty(codec.align128(n), dtype=torch.uint8, device=dev)
+            gc = torch.zeros(1, dtype=torch.int32, device=dev)
+            out = torch.empty_like(x)
+
+            def enc(fn):
+                gc.zero_()
+                fn(x, n_8, bases, det, scr, esc, gc, 1)
+
+            ms_re = _time(lambda: enc(ref.compress_split_store), args.iters, args.warmup)
+            cnt = int(gc[0])
+            stride = codec.align128(cnt)
+            nbytes = torch.full((1,), stride, dtype=torch.int32, device=dev)
+            escv = esc[:stride]
+            ms_rd = _time(lambda: ref.decompress_split_store_unpad(det, escv, n_8, nbytes, out, n, 1), args.iters,
+                          args.warmup)
+            ok_ref = bool(torch.equal(out.view(torch.int16), x.view(torch.int16)))
+            ms_oe = _time(lambda: enc(codec.v1_compress_split_store), args.iters, args.warmup)
+            ms_od = _time(lambda: codec.v1_decompress_split_store_unpad(det, escv, n_8, nbytes, out, n, 1),
+                          args.iters, args.warmup)
+            ok_ours = bool(torch.equal(out.view(torch.int16), x.view(torch.int16)))
+            rec, hdr = codec.v2_encode(x)
+            ms_2e = _time(lambda: codec.v2_encode(x, rec, hdr), args.iters, args.warmup)
+            ms_2d = _time(lambda: codec.v2_decode(rec, hdr, n, out), args.iters, args.warmup)
+            b1 = det.numel() + cnt
+            emit(kernel="codec_vs_reference", elems=n, ms_encode=dict(reference=round(ms_re, 4), v1=round(ms_oe, 4),
+                                                                      v2=round(ms_2e, 4)),
+                 ms_decode=dict(reference=round(ms_rd, 4), v1=round(ms_od, 4), v2=round(ms_2d, 4)),
+                 gbs_encode=dict(reference=round((2 * n + b1 + 2 * cnt) / ms_re / 1e6, 1),
+                                 v1=round((2 * n + b1 + 2 * cnt) / ms_oe / 1e6, 1)),
+                 gbs_decode=dict(reference=round((2 * n + b1) / ms_rd / 1e6, 1), v1=round((2 * n + b1) / ms_od / 1e6, 1)),
+                 roundtrip_exact=dict(reference=ok_ref, v1=ok_ours), l2="input larger than L2")
     if "elt" in only:
         T, d, F_, V = 16384, 4096, 14336, 128256
         x = torch.randn(T, d, device=dev).bfloat16()

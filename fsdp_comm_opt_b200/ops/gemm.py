@@ -1,22 +1,16 @@
 """bf16 linear layers: ``linear(x, w) = x @ w^T`` with the three GEMMs of training.
 
 Backends (``set_backend``):
-  ``"tcgen05"``  the hand-written sm_100a kernel in ``csrc/gemm_tcgen05.cu``: TMA loads into
-                 128B-swizzled shared memory, ``tcgen05.mma`` with TMEM accumulators issued by one
-                 elected thread, warp-specialised producer / MMA / epilogue, persistent over tiles.
-                 Forward uses K-major operands; dgrad and wgrad use the MN-major descriptor forms,
-                 so no transposed copy of the weight or the activations is made.
-  ``"tcgen05_2sm"``  the two-SM variant in ``csrc/gemm_tcgen05_2sm.cu`` (clusters of two CTAs,
-                 ``tcgen05.mma.cta_group::2`` on 256 x 256 tiles, B operand split between the pair) for
-                 shapes with M and N multiples of 256; other shapes fall back to ``"tcgen05"``.
-                 Compiled, not yet timed or verified on a GPU: never chosen by ``"auto"``.
-  ``"cublas"``   ``torch.matmul`` (cuBLASLt), the plain library GEMM.
-  ``"auto"``     cuBLAS.  The linear layers are plain GEMMs with nothing fused into them, and on
-                 B200 the library's 2-SM kernels are 10-25 % faster than the 1-SM tcgen05 kernel
-                 here (which is limited by the operand bandwidth a single SM can pull from L2), so
-                 the library is the default and ``ZC_GEMM_BACKEND=tcgen05`` / ``set_backend`` selects
-                 the hand-written kernel.
-CPU tensors always use ``torch.matmul``.
+  ``"tcgen05_2sm"``  the hand-written sm_100a kernel in ``csrc/gemm_tcgen05_2sm.cu``: clusters of two
+                 CTAs, ``tcgen05.mma.cta_group::2`` on 256 x 256 tiles with the B operand split between
+                 the pair, TMA loads into 128B-swizzled shared memory, TMEM accumulators, persistent
+                 over tiles with a split-K tail.  Any M, N, K that are multiples of 8.
+  ``"tcgen05"``  the one-SM kernel in ``csrc/gemm_tcgen05.cu`` (128 x 256 tiles; M % 128, N % 128,
+                 K % 64).
+  ``"cublas"``   ``torch.matmul`` (cuBLASLt), kept as the comparison column of the benchmarks.
+  ``"auto"``     the two-SM kernel whenever the shape allows it, else the library.
+Forward uses K-major operands; dgrad and wgrad use the MN-major descriptor forms, so no transposed
+copy of the weight or the activations is made.  CPU tensors always use ``torch.matmul``.
 """
 from __future__ import annotations
 
@@ -40,14 +34,22 @@ def get_backend() -> str:
     return _BACKEND
 
 
-def _tc_ok(M: int, N: int, K: int) -> bool:
-    return M % 128 == 0 and N % 128 == 0 and K % 64 == 0 and M > 0 and N > 0 and K > 0
-
-
-def _use_tc(a: torch.Tensor, M: int, N: int, K: int) -> bool:
-    if not a.is_cuda or a.dtype != torch.bfloat16 or _BACKEND not in ("tcgen05", "tcgen05_2sm"):
-        return False
-    return _tc_ok(M, N, K)
+def _kernel_for(a: torch.Tensor, b: torch.Tensor, M: int, N: int, K: int, trans_a: bool, trans_b: bool):
+    """The C launcher that will run this GEMM, or None for the library."""
+    if (not a.is_cuda or a.dtype != torch.bfloat16 or b.dtype != torch.bfloat16 or _BACKEND == "cublas"
+            or min(M, N, K) <= 0 or not (a.is_contiguous() and b.is_contiguous())):
+        return None
+    if (a.data_ptr() | b.data_ptr()) & 15:
+        return None
+    two_sm_ok = (M % 8 == 0 and N % 8 == 0 and K % 8 == 0 and M >= 128 and N >= 128 and K >= 64
+                 and not (trans_a and trans_b))
+    one_sm_ok = M % 128 == 0 and N % 128 == 0 and K % 64 == 0
+    lib = _lib.cuda()
+    if _BACKEND in ("auto", "tcgen05_2sm") and two_sm_ok:
+        return lib.zc_gemm_bf16_2sm
+    if _BACKEND in ("tcgen05", "tcgen05_2sm") and one_sm_ok:
+        return lib.zc_gemm_bf16
+    return None
 
 
 def gemm(a: torch.Tensor, b: torch.Tensor, trans_a: bool, trans_b: bool,
@@ -59,12 +61,11 @@ def gemm(a: torch.Tensor, b: torch.Tensor, trans_a: bool, trans_b: bool,
     """
     M, K = (a.shape[1], a.shape[0]) if trans_a else (a.shape[0], a.shape[1])
     N = b.shape[0] if trans_b else b.shape[1]
-    if _use_tc(a, M, N, K) and a.is_contiguous() and b.is_contiguous():
+    fn = _kernel_for(a, b, M, N, K, trans_a, trans_b)
+    if fn is not None and (out is None or (out.is_contiguous() and out.data_ptr() % 16 == 0)):
         if out is None:
             out = torch.empty(M, N, dtype=a.dtype, device=a.device)
             accumulate = False
-        lib = _lib.cuda()
-        fn = lib.zc_gemm_bf16_2sm if (_BACKEND == "tcgen05_2sm" and M % 256 == 0 and N % 256 == 0) else lib.zc_gemm_bf16
         _lib.check(fn(
             a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, int(trans_a), int(trans_b),
             int(accumulate), _lib.stream_ptr(a.device)), "zc_gemm_bf16")

@@ -39,14 +39,21 @@ _WHY: dict = {}
 LOGGER = logging.getLogger("fsdp_comm_opt_b200.symm")
 
 CTRL_WORDS = 1024
-CW_STATUS, CW_STATUS_PEER, CW_STATUS_GROUP, CW_WIRE_LO = 65, 66, 67, 68
+CW_STATUS, CW_STATUS_PEER, CW_STATUS_GROUP, CW_WIRE_LO, CW_HEALTH_PTR = 65, 66, 67, 68, 72
+GUARD = 4096          # canary bytes in front of and behind every symmetric buffer
+CANARY = 0xA5
+
+
+class SymmCorruption(RuntimeError):
+    """A canary region next to a symmetric buffer was overwritten, or a bounds-checked store was refused."""
 
 
 class SymmTimeout(RuntimeError):
     """A bounded device-side wait expired (peer did not arrive in time)."""
 
     def __init__(self, code: int, peer: int, group: int):
-        what = {1: "waiting for a peer to release the staging buffer", 2: "waiting for a peer's data"}.get(code, "?")
+        what = {1: "waiting for a peer to release the staging buffer", 2: "waiting for a peer's data",
+                3: "refusing a store outside the destination slot (bounds-checked build)"}.get(code, "?")
         super().__init__(f"fused collective timed out {what}: peer rank {peer}, group {group}")
         self.code, self.peer, self.group = code, peer, group
 
@@ -144,24 +151,35 @@ class Channel:
             dist.barrier(group=self.group)  # nobody may still be pushing into the old buffer
         nc_max = max(nc, 1024)
         nbytes = int(self._lib._lib.zc_symm_buffer_bytes(self.world, nc_max))
-        buf = symm_mem.empty(nbytes, dtype=torch.uint8, device=self.device)
-        buf[: CTRL_WORDS * 4 + 0].zero_()
+        # [guard | buffer the kernels see | guard]: the guards carry a fixed pattern that no kernel may
+        # touch; check_canaries() reads them back (peers write into this allocation over NVLink, so a
+        # wrong offset on ANY rank shows up here)
+        raw = symm_mem.empty(nbytes + 2 * GUARD, dtype=torch.uint8, device=self.device)
+        raw[:GUARD].fill_(CANARY)
+        raw[GUARD + nbytes:].fill_(CANARY)
+        buf = raw[GUARD:GUARD + nbytes]
         # flags must start below any sequence number; zero the control block and the flag area
         flag_bytes = (2 * self.world * ((nc_max + 63) // 64) * 4 + 127) // 128 * 128
         buf[: CTRL_WORDS * 4 + flag_bytes].zero_()
+        # where the kernels report a wait that ran out besides the status words: the library's health
+        # word, which the fused optimizer step reads on the device
+        with torch.cuda.device(self.device):
+            health = int(self._lib.zc_health_word() or 0)
+        buf[CW_HEALTH_PTR * 4:CW_HEALTH_PTR * 4 + 8].view(torch.int64).fill_(health)
         torch.cuda.synchronize(self.device)
-        hdl = symm_mem.rendezvous(buf, self.group)
+        hdl = symm_mem.rendezvous(raw, self.group)
         dist.barrier(group=self.group)
-        self.buf, self.hdl, self.nc_max, self.seq = buf, hdl, nc_max, 0
-        self.peers_dev = hdl.buffer_ptrs_dev
-        self.local_ptr = hdl.buffer_ptrs[self.rank]
+        self.raw, self.buf, self.hdl, self.nc_max, self.seq = raw, buf, hdl, nc_max, 0
+        self._peer_table = torch.tensor([int(p) + GUARD for p in hdl.buffer_ptrs], dtype=torch.int64, device=self.device)
+        self.peers_dev = self._peer_table.data_ptr()
+        self.local_ptr = int(hdl.buffer_ptrs[self.rank]) + GUARD
         # NVSwitch multicast mapping of the buffer (0 when the fabric or the driver has none): the
         # all-gather then stores its payload once instead of once per peer.  Measured at 2^28
         # elements: 387 against 471 GB/s bus on two ranks (the store also lands in the sender's own
         # copy) and 459 against 460 on eight (the receiving side's decode is the limit, not the
         # bytes leaving the GPU), so it is opt-in: ZC_SYMM_MULTICAST=1 turns it on.
         mc = int(getattr(hdl, "multicast_ptr", 0) or 0)
-        self.mc_ptr = mc if os.environ.get("ZC_SYMM_MULTICAST", "0") == "1" else 0
+        self.mc_ptr = (mc + GUARD) if (mc and os.environ.get("ZC_SYMM_MULTICAST", "0") == "1") else 0
 
     def _next_seq(self) -> int:
         self.seq += 1
@@ -178,7 +196,22 @@ class Channel:
         c = self._ctrl()[CW_STATUS:CW_STATUS + 3].tolist()
         if c[0] != 0:
             self._ctrl()[CW_STATUS:CW_STATUS + 3].zero_()
+            with torch.cuda.device(self.device):
+                self._lib.zc_health_read_and_clear()  # this report consumes the failure
+            if c[0] == 3:
+                raise SymmCorruption(f"a store outside its slot was refused: peer rank {c[1]}, chunk {c[2]}")
             raise SymmTimeout(c[0], c[1], c[2])
+
+    def check_canaries(self) -> None:
+        """Synchronises and raises ``SymmCorruption`` when a guard region around the buffer changed."""
+        if self.buf is None:
+            return
+        n = self.buf.numel()
+        front, back = self.raw[:GUARD], self.raw[GUARD + n:]
+        bad = int((front != CANARY).sum().item()) + int((back != CANARY).sum().item())
+        if bad:
+            raise SymmCorruption(f"{bad} canary bytes around the {self.kind!r} staging buffer of rank {self.rank} "
+                                 "were overwritten")
 
     def wire_bytes(self) -> int:
         """Bytes this rank has pushed over NVLink on this channel so far (synchronises)."""

@@ -487,3 +487,25 @@ def test_device_status_check_is_clean_after_kernels():
     attention.causal_attention(qkv, 4, 1).sum().backward()
     torch.cuda.synchronize()
     check_device_status()
+
+
+def test_adamw_is_skipped_while_the_health_word_is_set():
+    """A step that follows a collective which gave up must not be applied: the guarded AdamW launch
+    reads the library's health word on the device and leaves parameters and moments alone."""
+    from fsdp_comm_opt_b200.ops.adamw import FusedAdamW
+
+    lib = _lib.cuda()
+    p = torch.nn.Parameter(torch.randn(1 << 16, device=DEV).bfloat16())
+    p.grad = torch.randn_like(p)
+    opt = FusedAdamW([p], lr=1e-2)
+    before = p.detach().clone()
+    assert lib.zc_health_set(2) == 0          # what an expired wait writes
+    opt.step()
+    torch.cuda.synchronize()
+    assert torch.equal(p.detach(), before)
+    assert float(opt.state[p]["exp_avg"].float().abs().sum()) == 0.0
+    assert lib.zc_health_read_and_clear() == 2
+    opt.step()
+    torch.cuda.synchronize()
+    assert not torch.equal(p.detach(), before)
+    assert lib.zc_health_read_and_clear() == 0

@@ -57,6 +57,7 @@ def _ag_case(rank, world, transport):
 
         for ch in symm_impl.all_channels():
             ch.check_status()
+            ch.check_canaries()
             pushed = ch.wire_bytes()
             raw = 2 * sum(sizes) * (world - 1)
             assert 0.6 * raw < pushed < 0.8 * raw, (pushed, raw)   # ~1.4 of 2 bytes per element
@@ -152,6 +153,7 @@ def _rs_case(rank, world, transport):
 
         for ch in symm_impl.all_channels():
             ch.check_status()
+            ch.check_canaries()
 
 
 @pytest.mark.parametrize("transport", ["symm", "lib"])
@@ -211,3 +213,46 @@ def test_fsdp_two_gpus_symm_vs_lib_vs_uncompressed(tmp_path):
     assert len(a) == len(b) == len(c) == 4
     assert a == b, "lossless all-gather: identical loss curve"
     assert all(abs(x - y) / x < 0.01 for x, y in zip(a, c)), (a, c)
+
+
+def test_fsdp2_back_end_two_gpus_compressed_vs_uncompressed(tmp_path):
+    """The same hooks through PyTorch FSDP2 (``--sharding fsdp2``), which is how the reference wires them."""
+    logs = {k: str(tmp_path / f"{k}.log") for k in ("none", "symm")}
+    run_ranks(_train, 2, init_pg=False, backend="nccl", args=(["--sharding", "fsdp2"], logs["none"]))
+    run_ranks(_train, 2, init_pg=False, backend="nccl",
+              args=(["--sharding", "fsdp2", "-q", "--zip-ccl", "--compress-rs", "--transport", "symm"], logs["symm"]))
+    a, c = _losses(logs["none"]), _losses(logs["symm"])
+    assert len(a) == len(c) == 4
+    assert all(abs(x - y) / x < 0.01 for x, y in zip(a, c)), (a, c)
+
+
+def _side_stream_case(rank, world):
+    """The Work of an async fused all-gather launched on a side stream orders the *default* stream
+    after the kernel (c10d semantics: ``wait()`` blocks the current stream, not the host)."""
+    import torch.distributed as dist
+    from fsdp_comm_opt_b200.parallel.hooks import ZipCCLAllGather
+
+    dev = torch.device("cuda", rank)
+    hook = ZipCCLAllGather(transport="symm")
+    n = 1 << 22
+    side = torch.cuda.Stream(dev)
+    for it in range(3):
+        g = torch.Generator().manual_seed(5 * it + rank)
+        x = (torch.randn(n, generator=g) * 0.02).to(torch.bfloat16).to(dev)
+        ref = torch.zeros(world * n, dtype=torch.bfloat16, device=dev)
+        dist.all_gather_into_tensor(ref, x)
+        out = torch.zeros(world * n, dtype=torch.bfloat16, device=dev)
+        torch.cuda.synchronize()
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):
+            work = hook(out, x, dist.group.WORLD, async_op=True)
+        assert work is not None
+        work.wait()                      # called on the default stream
+        got = out.clone()                # default-stream read: must see the gathered data
+        torch.cuda.synchronize()
+        assert work.is_completed()
+        assert torch.equal(_bits(got), _bits(ref)), it
+
+
+def test_async_work_orders_another_stream_after_the_kernel():
+    run_ranks(_side_stream_case, 2, backend="nccl")

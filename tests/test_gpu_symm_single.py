@@ -1,0 +1,128 @@
+"""The fused collective kernels on ONE GPU: the ranks of a world of W are run one after the other
+(every other rank's pusher half first, then rank 0's whole kernel), each on its own staging buffer
+in this GPU's memory.  Pushers never wait for another launch and rank 0's decoders find every flag
+already set, so no kernel waits for a kernel that has not run.  This checks the encode -> staging
+layout -> flag -> pipelined decode (-> reduce) path bit for bit without a second device."""
+import ctypes
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+from fsdp_comm_opt_b200 import _lib
+from fsdp_comm_opt_b200.ops import codec
+
+DEV = torch.device("cuda", 0)
+
+
+GUARD, CANARY = 4096, 0xA5
+
+
+class _World:
+    def __init__(self, world: int, numel_per_source: int):
+        lib = _lib.cuda()
+        raw = lib._lib
+        raw.zc_symm_buffer_bytes.restype = ctypes.c_int64
+        raw.zc_symm_buffer_bytes.argtypes = [ctypes.c_int, ctypes.c_int64]
+        self.lib, self.world = lib, world
+        self.nc_max = max(1024, codec.v2_num_chunks(numel_per_source))
+        nbytes = int(raw.zc_symm_buffer_bytes(world, self.nc_max))
+        # every staging buffer sits between two canary regions that no kernel may touch
+        self.raw = [torch.full((nbytes + 2 * GUARD,), CANARY, dtype=torch.uint8, device=DEV) for _ in range(world)]
+        self.bufs = [r[GUARD:GUARD + nbytes] for r in self.raw]
+        for b in self.bufs:
+            b.zero_()
+        self.ptrs = torch.tensor([b.data_ptr() for b in self.bufs], dtype=torch.int64, device=DEV)
+
+    def canaries_intact(self):
+        return all(bool((r[:GUARD] == CANARY).all()) and bool((r[-GUARD:] == CANARY).all()) for r in self.raw)
+
+    def status(self, r):
+        return self.bufs[r][:4096].view(torch.int32)[65:68].tolist()
+
+    def all_gather(self, rank, x, out, push, dec, seq=1):
+        _lib.check(self.lib.zc_symm_all_gather(
+            x.data_ptr(), out.data_ptr(), self.ptrs.data_ptr(), self.bufs[rank].data_ptr(), None, x.numel(), rank,
+            self.world, self.nc_max, seq, push, dec, 1.0, _lib.stream_ptr(DEV)), "zc_symm_all_gather")
+
+    def reduce_scatter(self, rank, x, out, push, dec, seq=1, scale=1.0):
+        shard = x.numel() // self.world
+        _lib.check(self.lib.zc_symm_reduce_scatter(
+            x.data_ptr(), out.data_ptr(), None, self.ptrs.data_ptr(), self.bufs[rank].data_ptr(), shard, rank,
+            self.world, self.nc_max, seq, int(x.dtype == torch.float32), int(out.dtype == torch.float32), scale,
+            push, dec, 1.0, _lib.stream_ptr(DEV)), "zc_symm_reduce_scatter")
+
+
+def _params(n, seed, outliers=False):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    x = torch.randn(n, device=DEV, generator=g) * 0.02
+    if outliers:
+        m = torch.rand(n, device=DEV, generator=g) < 0.01
+        x = torch.where(m, x * 100, x)
+    return x.bfloat16()
+
+
+@pytest.mark.parametrize("world,n", [(2, 1 << 20), (4, 300_001), (8, 1 << 18), (8, 5000)])
+def test_fused_all_gather_ranks_in_sequence(world, n):
+    w = _World(world, n)
+    shards = [_params(n, 10 + r, outliers=(r % 2 == 1)) for r in range(world)]
+    scratch = torch.empty(world * n, dtype=torch.bfloat16, device=DEV)
+    for r in range(1, world):                      # the other ranks: encode and push only
+        w.all_gather(r, shards[r], scratch, push=32, dec=0)
+    out = torch.zeros(world * n, dtype=torch.bfloat16, device=DEV)
+    w.all_gather(0, shards[0], out, push=32, dec=64)   # rank 0: push, then decode what has arrived
+    torch.cuda.synchronize()
+    assert w.status(0) == [0, 0, 0] and w.canaries_intact()
+    assert torch.equal(out.view(torch.int16), torch.cat(shards).view(torch.int16))
+
+
+@pytest.mark.parametrize("world,shard,dtype", [(2, 1 << 19, torch.bfloat16), (4, 70_000, torch.float32),
+                                               (8, 1 << 16, torch.bfloat16), (8, 3000, torch.bfloat16)])
+def test_fused_reduce_scatter_ranks_in_sequence(world, shard, dtype):
+    w = _World(world, shard)
+    rows = [(_params(world * shard, 40 + r, outliers=True).float() * 0.05).bfloat16().to(dtype) for r in range(world)]
+    dummy = torch.empty(shard, dtype=torch.float32, device=DEV)
+    for r in range(1, world):
+        w.reduce_scatter(r, rows[r], dummy, push=48, dec=0)
+    out = torch.zeros(shard, dtype=torch.float32, device=DEV)
+    w.reduce_scatter(0, rows[0], out, push=48, dec=64, scale=1.0 / world)
+    torch.cuda.synchronize()
+    assert w.status(0) == [0, 0, 0] and w.canaries_intact()
+    # the kernel adds its own row first, then the sources by rank, in fp32
+    ref = rows[0][:shard].float()
+    for r in range(1, world):
+        ref = ref + rows[r][:shard].float()
+    ref = ref * (1.0 / world)
+    assert torch.equal(out, ref)
+
+
+def test_decoder_reports_a_flag_that_never_comes():
+    """Nothing pushed for source 1: rank 0's decoders give up after the (1 s) limit, record which source
+    and group they waited for, and the kernel returns normally."""
+    w = _World(2, 1 << 14)
+    x = _params(1 << 14, 3)
+    out = torch.zeros(2 << 14, dtype=torch.bfloat16, device=DEV)
+    w.all_gather(0, x, out, push=4, dec=4)
+    torch.cuda.synchronize()
+    code, peer, _group = w.status(0)
+    assert code == 2 and peer == 1
+    torch.cuda.synchronize()  # the context is still usable
+    assert torch.equal(out[: 1 << 14].view(torch.int16), x.view(torch.int16))
+
+
+def test_same_cases_on_the_bounds_checked_build():
+    """The small cases above once more in a fresh process on ``libzc_cuda_dbg.so`` (every store into a
+    staging slot checked against the slot's extent before it is issued; an offending store would be
+    skipped and show up as status code 3)."""
+    import os
+    import subprocess
+    import sys
+
+    if os.environ.get("ZC_DEBUG_BOUNDS") == "1":
+        assert _lib.cuda()._lib.zc_debug_bounds_build() == 1
+        return
+    env = dict(os.environ, ZC_DEBUG_BOUNDS="1")
+    r = subprocess.run([sys.executable, "-m", "pytest", __file__, "-x", "-q", "-k", "sequence or bounds_checked"],
+                       env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]

@@ -113,3 +113,48 @@ def test_fault_injector_env_parsing(monkeypatch):
     inj.maybe_fail(0, 3)
     with pytest.raises(RuntimeError):
         inj.maybe_fail(1, 3)
+
+
+def _train_with_env(rank, world, extra, loss_log, env):
+    os.environ.update(env)
+    _train(rank, world, extra, loss_log)
+
+
+def _spawn_exit_codes(fn, world, args):
+    """Like ``run_ranks`` but for runs that are expected to die: returns the ranks' exit codes."""
+    import torch.multiprocessing as mp
+
+    from mp_util import _entry, _free_port
+
+    ctx = mp.get_context("spawn")
+    errq, port = ctx.SimpleQueue(), _free_port()
+    procs = [ctx.Process(target=_entry, args=(r, world, port, fn, args, errq, False, "gloo")) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(180)
+    for p in procs:
+        if p.is_alive():
+            p.kill()
+    return [p.exitcode for p in procs]
+
+
+def test_rank_failure_then_resume_from_last_checkpoint(tmp_path):
+    """Rank 1 raises on the host before step 5 (the injector runs between steps, nothing in flight);
+    rank 0's next collective runs into the process-group timeout, so the whole job ends with an
+    error instead of hanging.  Starting the same command again resumes from the checkpoint written
+    after step 4 and continues the loss curve of an uninterrupted run (the recovery path of the
+    reference: rerun with the same ``-e``, train.py:168-190)."""
+    full, part = str(tmp_path / "full.log"), str(tmp_path / "part.log")
+    common = ["--save-dir", str(tmp_path), "--ckpt-freq", "2", "-q", "--zip-ccl", "--compress-rs", "--steps", "8",
+              "--dist-timeout", "8"]
+    run_ranks(_train, 2, init_pg=False, args=(common + ["-e", "full"], full))
+    codes = _spawn_exit_codes(_train_with_env, 2, (common + ["-e", "part"], part,
+                                                   {"ZC_FAULT_INJECT": "rank=1,step=4,kind=raise"}))
+    assert all(c != 0 for c in codes), codes                       # both ranks ended with an error
+    assert json.load(open(tmp_path / "part" / "state.json"))["global_step"] == 4
+    assert len(_losses(part)) == 4
+    run_ranks(_train, 2, init_pg=False, args=(common + ["-e", "part"], part))    # no fault this time
+    lf, lp = _losses(full), _losses(part)
+    assert len(lp) == 8
+    assert all(abs(x - y) < 2e-3 for x, y in zip(lf, lp)), (lf, lp)

@@ -90,6 +90,9 @@ def _get_parser() -> argparse.ArgumentParser:
                    help="> 0: ranks publish a heartbeat each step and abort when a peer is silent that long")
     p.add_argument("--loss-log", default=None, help="rank 0 appends 'step loss' lines to this file")
     p.add_argument("--sharding", default="flat", choices=["flat", "fsdp2"])
+    p.add_argument("--dist-timeout", default=None, type=float,
+                   help="seconds after which a collective whose peer never joins fails instead of waiting "
+                        "(process-group timeout; the default is the backend's)")
     p.add_argument("--tokenizer", default=None,
                    help="tokenizer name or local directory for text data (default: the model name; 'bytes' = built-in byte-level)")
     return p
@@ -119,7 +122,7 @@ def main(argv=None):
     if not args.synthetic and (args.dataset_name is None or args.model_name is None):
         raise SystemExit("either --synthetic with --model-shape, or -d/--dataset-name and -m/--model-name")
 
-    rank, world_size, device = init_distributed(args.device)
+    rank, world_size, device = init_distributed(args.device, timeout_s=args.dist_timeout)
     local_rank = device.index or 0
     LOGGER = setup_logging(rank)
     LOGGER.debug(os.environ)
@@ -193,7 +196,7 @@ def main(argv=None):
 
     def save_checkpoint():
         if device.type == "cuda":
-            check_device_status()  # never persist a step whose collectives gave up
+            check_device_status(deep=True)  # never persist a step whose collectives gave up or strayed
         if flat is not None:
             ckpt.save_flat_checkpoint(exp_dir, flat, optimizer, lr_scheduler, state, plan.rs_hooks)
         else:
@@ -275,6 +278,7 @@ def main(argv=None):
                     info.update(_comm_metrics(flat, plan, args.log_freq, device))
                     LOGGER.info(info)
                     if device.type == "cuda":
+                        check_device_status(deep=True)
                         torch.cuda.reset_peak_memory_stats(device)
                     state["running_loss"] = 0
                     for t in timers.values():
