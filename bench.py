@@ -104,6 +104,12 @@ def parse_args():
     ap.add_argument("--no-compress", action="store_true", help="ours: stock NCCL collectives")
     ap.add_argument("--act-ckpt", action="store_true")
     ap.add_argument("--gemm", default=None, choices=[None, "auto", "tcgen05", "tcgen05_2sm", "cublas"])
+    ap.add_argument("--comm-stats", action="store_true",
+                    help="ours: bracket every collective with CUDA events and report per-step device time, bus "
+                         "GB/s and the time compute stood still waiting for communication (a few events per "
+                         "collective; off for the headline runs)")
+    ap.add_argument("--strict-comm", action="store_true",
+                    help="fail instead of warning when compressed collectives did not run on the fused transport")
     ap.add_argument("--sharding", default="flat", choices=["flat", "fsdp2"], help="ours: sharding back end")
     ap.add_argument("--kernel-table", type=int, default=0, metavar="N",
                     help="after the timed runs, trace two more steps with torch.profiler and print the N "
@@ -121,7 +127,8 @@ def make_ours(args, device):
         gemm.set_backend(args.gemm)
     comp = not args.no_compress
     eng = TrainEngine(EngineConfig(model=args.model, quantize=comp, zip_ccl=comp, compress_rs=comp,
-                                   transport=args.transport, act_ckpt=args.act_ckpt, sharding=args.sharding), device)
+                                   transport=args.transport, act_ckpt=args.act_ckpt, sharding=args.sharding,
+                                   time_collectives=args.comm_stats), device)
     info = {"gemm_backend": gemm.get_backend(), "native_lib": str(_lib.cuda_lib_path()), "sharding": args.sharding,
             "comm_requested": "zip all-gather + compressed reduce-scatter" if comp else "nccl"}
     make_ours.engine = eng
@@ -313,11 +320,24 @@ def main():
         check_device_status()
         # what the collectives actually ran on (not what the flags asked for)
         comm = make_ours.engine.comm_report()
+        if args.comm_stats and make_ours.engine.flat is not None:
+            n_steps = 2 * (args.warmup + args.steps)
+            comm["per_step"] = {k: {"calls": v["calls"] / n_steps, "ms": round(v["ms"] / n_steps, 3),
+                                    "bus_gbs": None if v["bus_gbs"] is None else round(v["bus_gbs"], 1)}
+                                for k, v in make_ours.engine.flat.comm_stats().items()}
         if world > 1 and not args.no_compress and args.transport != "lib":
             ran = set(comm["all_gather"]) | set(comm["reduce_scatter"])
             if ran != {"symm"}:
-                raise RuntimeError(f"compressed collectives were requested but ran on {sorted(ran)}: "
-                                   "the symmetric-memory transport was not available")
+                from fsdp_comm_opt_b200.parallel import symm_impl as _symm
+
+                why = _symm.why_unavailable(dist.group.WORLD)
+                comm["fused_transport_unavailable"] = why
+                msg = (f"compressed collectives were requested but ran on {sorted(ran)}: the fused "
+                       f"symmetric-memory transport was not available ({why})")
+                if args.strict_comm:
+                    raise RuntimeError(msg)
+                if rank == 0:
+                    print("WARNING: " + msg, file=sys.stderr)
     table = None
     if args.kernel_table > 0:  # every rank runs the traced steps (they contain collectives)
         table = kernel_table(step_dev, dev_batches[-1], args.kernel_table, device)

@@ -17,7 +17,12 @@
 // and the operand layouts are template parameters; per MMA the loop adds a constant to the
 // descriptors and nothing else.
 //
-// Work is cut into units: whole tiles first, then the tiles of the last, partial wave are split
+// Work is handed out dynamically.  The clusters take units from a global counter (the even CTA's
+// producer thread fetches the next index and publishes it to every role of both CTAs through a small
+// ring in shared memory), so a cluster that starts late, or not at all for a while, because another
+// kernel (a collective running beside the GEMM) holds its SMs simply takes fewer units; with a
+// static round-robin the whole GEMM would wait for that cluster's share.
+// Units: whole tiles first, then the tiles of the last, partial wave are split
 // along K into `split` slices each, so that all clusters stay busy to the end.  A slice writes its
 // fp32 partial sums to a workspace and a small second kernel adds the slices and rounds to bf16.
 // Every wait is bounded; on expiry the status word is set and both CTAs reach the teardown.
@@ -48,6 +53,8 @@ constexpr int A_BYTES = BM_CTA * BK * 2;  // 16 KB
 constexpr int B_BYTES = BN_CTA * BK * 2;  // 16 KB
 constexpr int STAGE = A_BYTES + B_BYTES;
 constexpr int MAX_SPLIT = 4;
+constexpr int SCHED = 4;       // slots of the unit-index ring
+constexpr int COUNTER_SLOTS = 256;
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;
@@ -106,6 +113,31 @@ __device__ __forceinline__ uint32_t mbar_addr_try_wait(uint32_t bar, uint32_t pa
       : "memory");
   return ok;
 }
+__device__ __forceinline__ uint32_t mbar_addr_try_wait_cluster(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok;
+}
+// the same wait with cluster-scope acquire: the arrival (and the data it publishes) came from the other CTA
+__device__ __forceinline__ bool wait_bar_cluster(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  if (mbar_addr_try_wait_cluster(bar, parity)) return true;
+  const unsigned long long t0 = globaltimer_ns();
+  for (uint32_t it = 0;; ++it) {
+    if (mbar_addr_try_wait_cluster(bar, parity)) return true;
+    if ((it & 255u) == 255u && (*abort_flag || globaltimer_ns() - t0 > 2000000000ull)) return false;
+  }
+}
+__device__ __forceinline__ void st_shared_cluster_u32(uint32_t cluster_addr, uint32_t v) {
+  asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
+}
 // bounded spin on a barrier given by its shared::cta address; the limit is only looked at on the slow path
 __device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
   if (mbar_addr_try_wait(bar, parity)) return true;
@@ -125,6 +157,7 @@ struct Params {
   int full_tiles;      // tiles computed whole; the remaining tiles are split along K
   int split;           // K slices per tail tile (1: no tile is split)
   int* status;
+  unsigned* counter;   // [0] units handed out beyond the first round, [1] clusters finished; both 0 at launch
 };
 
 // Tile order.  The clusters running at one time work on consecutive tile indices; walking bands of
@@ -171,6 +204,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   __shared__ uint64_t full[STAGES], empty[STAGES], acc_full[2], acc_empty[2];
+  __shared__ uint64_t sched_full[SCHED], sched_empty[SCHED];
+  __shared__ int sched_u[SCHED];
   __shared__ uint32_t tmem_base;
   __shared__ volatile int s_abort;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -183,6 +218,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
     for (int a = 0; a < 2; ++a) {
       mbar_init(&acc_full[a], 1);   // one commit per unit, on both CTAs
       mbar_init(&acc_empty[a], 8);  // used on the even CTA: four epilogue warps of each CTA
+    }
+    for (int q = 0; q < SCHED; ++q) {
+      mbar_init(&sched_full[q], 1);    // the even CTA's producer publishes a unit index (in both CTAs)
+      mbar_init(&sched_empty[q], 10);  // used on the even CTA: every other role of both CTAs has read it
     }
     mbar_fence_init();
     s_abort = 0;
@@ -207,13 +246,42 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
   const int cluster_id = blockIdx.x >> 1, n_clusters = gridDim.x >> 1;
   const uint32_t smem_base = smem_u32(smem);
   const uint32_t full_base = smem_u32(&full[0]), empty_base = smem_u32(&empty[0]);
+  const uint32_t sfull_base = smem_u32(&sched_full[0]);
+  const uint32_t sempty_c0 = map_to_cta(smem_u32(&sched_empty[0]), 0);  // the even CTA's sched_empty[0]
   bool ok = true;
+  // Every role walks the same sequence of units, i = 0, 1, ...: slot i % SCHED of the ring holds the
+  // i-th unit of this cluster (an index >= units ends the sequence).
+  auto next_unit = [&](uint32_t i, bool& good) -> int {
+    const uint32_t slot = i & (SCHED - 1), sph = (i / SCHED) & 1;
+    good = rank == 0 ? wait_bar(sfull_base + 8 * slot, sph, &s_abort)
+                     : wait_bar_cluster(sfull_base + 8 * slot, sph, &s_abort);
+    return good ? sched_u[slot] : 0x7fffffff;
+  };
+  auto release_unit = [&](uint32_t i) { mbar_arrive_cluster(sempty_c0 + 8 * (i & (SCHED - 1))); };
 
   if (warp == 0) {
     if (lane == 0) {
       const uint32_t full0 = map_to_cta(full_base, 0);  // the even CTA's full[0]; full[s] is 8 s bytes on
+      const uint32_t sfull_c1 = map_to_cta(sfull_base, 1);
+      const uint32_t su_c1 = map_to_cta(smem_u32(&sched_u[0]), 1);
       uint32_t s = 0, ph = 0;
-      for (int u = cluster_id; u < units && ok; u += n_clusters) {
+      for (uint32_t i = 0; ok; ++i) {
+        int u;
+        if (rank == 0) {
+          // fetch the i-th unit and publish it to both CTAs
+          const uint32_t slot = i & (SCHED - 1), sph = (i / SCHED) & 1;
+          if (!(ok = wait_bar_cluster(smem_u32(&sched_empty[slot]), sph ^ 1, &s_abort))) break;
+          u = (i == 0) ? cluster_id : n_clusters + (int)atomicAdd(p.counter, 1u);
+          sched_u[slot] = u;
+          st_shared_cluster_u32(su_c1 + 4 * slot, (uint32_t)u);
+          mbar_arrive(&sched_full[slot]);
+          mbar_arrive_cluster(sfull_c1 + 8 * slot);  // release.cluster: orders the store above
+        } else {
+          u = next_unit(i, ok);
+          if (!ok) break;
+          release_unit(i);
+        }
+        if (u >= units) break;
         const Unit w = unit_of(u, p, m_tiles, n_tiles, k_blocks);
         const int m0 = w.mi * BM + (int)rank * BM_CTA;
         const int n0 = w.ni * BN + (int)rank * BN_CTA;
@@ -254,11 +322,15 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
       const uint32_t empty_c0 = map_to_cta(empty_base, 0), empty_c1 = map_to_cta(empty_base, 1);
       const uint32_t accf_c0 = map_to_cta(smem_u32(&acc_full[0]), 0), accf_c1 = map_to_cta(smem_u32(&acc_full[0]), 1);
       const uint32_t acce = smem_u32(&acc_empty[0]);
-      uint32_t s = 0, ph = 0, unit_it = 0;
-      for (int u = cluster_id; u < units && ok; u += n_clusters, ++unit_it) {
+      uint32_t s = 0, ph = 0;
+      for (uint32_t unit_it = 0; ok; ++unit_it) {
+        const int u = next_unit(unit_it, ok);
+        if (!ok) break;
+        release_unit(unit_it);
+        if (u >= units) break;
         const Unit w = unit_of(u, p, m_tiles, n_tiles, k_blocks);
         const uint32_t acc = unit_it & 1, acc_ph = (unit_it >> 1) & 1;
-        if (!(ok = wait_bar(acce + 8 * acc, acc_ph ^ 1, &s_abort))) break;
+        if (!(ok = wait_bar_cluster(acce + 8 * acc, acc_ph ^ 1, &s_abort))) break;
         tc_fence_after_sync();
         const uint32_t d = tm + acc * BN;
         uint32_t accum = 0;
@@ -286,11 +358,15 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
     const int quarter = warp & 3;
     const uint32_t accf = smem_u32(&acc_full[0]);
     const uint32_t acce_c0 = map_to_cta(smem_u32(&acc_empty[0]), 0);
-    uint32_t unit_it = 0;
-    for (int u = cluster_id; u < units && ok; u += n_clusters, ++unit_it) {
+    for (uint32_t unit_it = 0; ok; ++unit_it) {
+      const int u = next_unit(unit_it, ok);
+      if (__any_sync(0xffffffffu, !ok)) { ok = false; break; }
+      __syncwarp();
+      if (lane == 0) release_unit(unit_it);
+      if (u >= units) break;
       const Unit w = unit_of(u, p, m_tiles, n_tiles, k_blocks);
       const uint32_t acc = unit_it & 1, acc_ph = (unit_it >> 1) & 1;
-      ok = wait_bar(accf + 8 * acc, acc_ph, &s_abort);
+      ok = wait_bar_cluster(accf + 8 * acc, acc_ph, &s_abort);
       if (__any_sync(0xffffffffu, !ok)) { ok = false; break; }
       tc_fence_after_sync();
       const int row_in_tile = (int)rank * BM_CTA + quarter * 32 + lane;
@@ -356,6 +432,13 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
   // neither CTA may leave (or free its TMEM) while the pair's MMAs can still touch its memory
   cluster_sync_all();
   if (warp == 1) tmem_dealloc(tm, 2 * BN);
+  if (tid == 0 && rank == 0) {
+    // the last cluster to finish puts the counters back to zero for the next launch that uses this slot
+    if (atomicAdd(p.counter + 1, 1u) == (unsigned)n_clusters - 1u) {
+      p.counter[0] = 0u;
+      p.counter[1] = 0u;
+    }
+  }
 }
 
 // C tile (+)= sum over the K slices of its fp32 partials, rounded once to bf16.
@@ -435,6 +518,8 @@ struct DeviceState {
   int clusters = 0;
   float* partial = nullptr;
   size_t partial_elems = 0;
+  unsigned* counters = nullptr;  // COUNTER_SLOTS pairs, all zero between launches; launches take slots in turn
+  unsigned next_slot = 0;
 };
 static DeviceState g_state[64];
 static std::mutex g_mutex;
@@ -506,6 +591,8 @@ int zc_gemm_bf16_2sm(const void* A, const void* B, void* C, int64_t M, int64_t N
       c = std::min(c, max_clusters<MAJOR_K, MAJOR_MN>(smem));
       c = std::min(c, max_clusters<MAJOR_MN, MAJOR_MN>(smem));
       ds.clusters = c;
+      if (cudaMalloc(&ds.counters, 2 * COUNTER_SLOTS * sizeof(unsigned)) != cudaSuccess) return ERR_BAD_ARG;
+      cudaMemset(ds.counters, 0, 2 * COUNTER_SLOTS * sizeof(unsigned));
       ds.ready = true;
     }
   }
@@ -516,6 +603,10 @@ int zc_gemm_bf16_2sm(const void* A, const void* B, void* C, int64_t M, int64_t N
   static const int forced_split = getenv("ZC_GEMM_SPLIT") ? atoi(getenv("ZC_GEMM_SPLIT")) : -1;
   p.group_m = forced_gm > 0 ? forced_gm : 8;
   p.status = status;
+  {
+    std::lock_guard<std::mutex> lock(g_mutex);
+    p.counter = ds.counters + 2 * (ds.next_slot++ % COUNTER_SLOTS);
+  }
   const int64_t tiles = m_tiles * n_tiles;
   const int64_t k_blocks = (K + BK - 1) / BK;
   const int clusters = (int)std::min<int64_t>(tiles, ds.clusters);

@@ -18,8 +18,14 @@
 // Contract.
 //   * Same inputs and outputs as zc_v1_encode_split(), minus the scratch pointer; the bytes written
 //     to `det`, `esc_final` and `counts` are identical to that entry point's.
+//   * Every n_8[i] (device memory) must be a multiple of 4096 and total_blocks must equal
+//     sum(n_8) / 4096: block b stages its outliers at scratch offset 4096 * b, so with whole blocks
+//     per work the staging never leaves the first total_blocks * 4096 bytes of the array.
 //   * total_blocks * 4096 must not exceed ZC_NOALLOC_MAX_ELEMS; larger requests are refused with
 //     ZC_ERR_TOO_LARGE and a message on stderr, nothing is launched.
+//   * Return value: 0 on success (also for total_blocks <= 0: nothing to do); -1 for n_works <= 0;
+//     ZC_ERR_TOO_LARGE (-3); ZC_ERR_SYMBOL (-4) when the array's device address cannot be resolved;
+//     a positive cudaError_t when a launch was refused.
 //   * The call allocates nothing: no cudaMalloc, cudaFree or any allocating library routine.
 //   * First call on a device: it resolves the device address of the scratch array once (with that
 //     device current) and caches it.  Make that first call before any stream capture begins.

@@ -22,6 +22,7 @@ import torch.distributed as dist
 
 from .models import ModelConfig, build_model, get_config, shard_groups
 from .ops.adamw import FusedAdamW
+from .ops.loss import unit_loss_grad
 from .parallel.flat_shard import FlatShardEngine, FlatShardPlan
 from .parallel.fsdp import FSDPPlan, apply_fsdp, make_hook_factories
 
@@ -100,7 +101,8 @@ class TrainEngine:
         else:
             self.model.unshard()
             out = self.model(input_ids=input_ids, labels=input_ids)
-            out.loss.backward()
+            with unit_loss_grad():
+                out.loss.backward()
             self.optimizer.step()
             self.lr_scheduler.step()
             self.optimizer.zero_grad(set_to_none=True)

@@ -13,6 +13,24 @@ from .. import _lib
 
 IGNORE_INDEX = -100
 
+# Set (by the training engines, around ``loss.backward()``) when the loss is the root of the backward
+# pass and its incoming gradient is therefore exactly 1: the [T, V] gradient buffer is then handed on
+# as it is instead of being multiplied by one (a full read + write of the logits-sized tensor).
+_UNIT_GRAD = False
+
+
+class unit_loss_grad:
+    """Context manager: promise that d(total)/d(loss) == 1 for backward passes started inside."""
+
+    def __enter__(self):
+        global _UNIT_GRAD
+        self._prev, _UNIT_GRAD = _UNIT_GRAD, True
+        return self
+
+    def __exit__(self, *exc):
+        global _UNIT_GRAD
+        _UNIT_GRAD = self._prev
+
 
 class _CrossEntropy(torch.autograd.Function):
     @staticmethod
@@ -46,8 +64,10 @@ class _CrossEntropy(torch.autograd.Function):
     def backward(ctx, dloss):
         grad = ctx.grad_logits
         ctx.grad_logits = None
+        if _UNIT_GRAD:
+            return grad, None, None
         if grad.is_cuda:
-            # dloss is 1.0 in the training loop; scale in place to keep one [T, V] buffer
+            # scale in place to keep one [T, V] buffer
             return grad.mul_(dloss.to(grad.dtype)), None, None
         return grad * dloss.to(grad.dtype), None, None
 

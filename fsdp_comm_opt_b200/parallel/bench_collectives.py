@@ -119,10 +119,30 @@ def main():
                               "wire_bytes_per_elem": None if wire_pe is None else round(wire_pe, 4),
                               "frac_of_nvlink_roofline": None if roof_ms is None else round(roof_ms / ms_z, 3),
                               "max_abs_err": err}), flush=True)
-        del rows, scratch, out, ref
+        # ---------------- reduce-scatter of bf16 rows (what the flat-shard engine hands over) --------
+        rows16 = [r.to(torch.bfloat16) for r in rows]
+        del rows, scratch
+        out16 = torch.empty(shard, dtype=torch.bfloat16, device=device)
+        ref16 = torch.empty_like(out16)
+        rs(out16, rows16[0], group, dist.ReduceOp.AVG)
+        torch.cuda.synchronize(device)
+        err = float((out16.float() - ref).abs().max().item())   # against the fp32 NCCL result above
+        ms_z = _timed(lambda i: rs(out16, rows16[i & 1], group, dist.ReduceOp.AVG), args.iters, device)
+        scratch = [r.clone() for r in rows16]
+        ms_n = _timed(lambda i: dist.reduce_scatter_tensor(ref16, scratch[i & 1], op=dist.ReduceOp.AVG), args.iters, device)
+        payload = 2.0 * shard * world
+        if rank == 0:
+            print(json.dumps({"op": "reduce_scatter_bf16", "elements": total, "world": world,
+                              "data": "same gradients as bf16 rows; NCCL column = bf16 reduce-scatter (bf16 accumulation)",
+                              "zip_ms": round(ms_z, 4), "nccl_ms": round(ms_n, 4),
+                              "zip_bus_gbs": round(payload * (world - 1) / world / ms_z / 1e6, 1),
+                              "nccl_bus_gbs": round(payload * (world - 1) / world / ms_n / 1e6, 1),
+                              "max_abs_err_vs_fp32_sum": err}), flush=True)
+        del rows16, scratch, out, ref, out16, ref16
         torch.cuda.empty_cache()
     for ch in symm_impl.all_channels():
         ch.check_status()
+        ch.check_canaries()
     dist.barrier()
     dist.destroy_process_group()
 

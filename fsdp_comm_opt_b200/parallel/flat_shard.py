@@ -99,22 +99,30 @@ class _Slot:
 
 
 class _Pool:
-    """Fixed-layout buffers handed out and taken back with the event after which they are free."""
+    """Fixed-layout buffers handed out and taken back with the event after which they are free.
 
-    def __init__(self, device, dtype):
-        self.device, self.dtype = device, dtype
+    A buffer that has just been released is free only once its last reader has finished on the
+    device (a reduce-scatter still running, a layer still computing), and the host runs many layers
+    ahead of the device, so handing the newest release straight back would make the next user wait
+    for exactly the work it is meant to overlap.  The pool therefore grows to ``depth`` buffers per
+    layout before it reuses any, and then reuses the one released longest ago."""
+
+    def __init__(self, device, dtype, depth: int):
+        self.device, self.dtype, self.depth = device, dtype, depth
         self._free: dict = {}
+        self._count: dict = {}
         self.allocated = 0
 
     def get(self, key, numel, stream):
         lst = self._free.get(key)
-        if lst:
-            t, ev = lst.pop(0)
-            if ev is not None and stream is not None:
-                stream.wait_event(ev)
-            return t
-        self.allocated += 1
-        return torch.zeros(numel, dtype=self.dtype, device=self.device)  # padding stays zero for good
+        if self._count.get(key, 0) < self.depth or not lst:
+            self._count[key] = self._count.get(key, 0) + 1
+            self.allocated += 1
+            return torch.zeros(numel, dtype=self.dtype, device=self.device)  # padding stays zero for good
+        t, ev = lst.pop(0)
+        if ev is not None and stream is not None:
+            stream.wait_event(ev)
+        return t
 
     def put(self, key, tensor, event):
         self._free.setdefault(key, []).append((tensor, event))
@@ -233,8 +241,10 @@ class FlatShardEngine:
         self.master_param = nn.Parameter(self.master, requires_grad=True)
         self.master_param.grad = self.grad_master
 
-        self._param_pool = _Pool(device, cd)
-        self._grad_pool = _Pool(device, cd)
+        # parameters: the group computing, the one being gathered, one draining; gradients: the group
+        # being written, the one being reduce-scattered
+        self._param_pool = _Pool(device, cd, depth=3)
+        self._grad_pool = _Pool(device, cd, depth=2)
         if self.cuda:
             self.ag_stream = torch.cuda.Stream(device, priority=-1)
             self.rs_stream = torch.cuda.Stream(device, priority=-1)
@@ -325,7 +335,9 @@ class FlatShardEngine:
         """Device time of the collectives logged since the last call (needs ``time_collectives``):
         per kind the number of calls, the summed milliseconds on this rank and the bus bandwidth
         ``payload * (W-1)/W / time`` in GB/s, with the payload counted uncompressed (what a plain
-        collective would move), as nccl-tests does.  Synchronises on the last logged event."""
+        collective would move), as nccl-tests does.  The ``*_exposed`` kinds are the time the compute
+        stream stood still waiting for a gather / for the last reduce-scatters, i.e. the part of the
+        communication that nothing overlapped.  Synchronises on the last logged event."""
         out: dict = {}
         if not self._comm_log:
             return out
@@ -338,14 +350,16 @@ class FlatShardEngine:
             d["ms"] += a.elapsed_time(b)
             d["bytes"] += nbytes
         for d in out.values():
-            d["bus_gbs"] = d["bytes"] * (self.world - 1) / self.world / max(d["ms"], 1e-9) / 1e6
+            d["bus_gbs"] = d["bytes"] * (self.world - 1) / self.world / max(d["ms"], 1e-9) / 1e6 if d["bytes"] else None
         if reset:
             self._comm_log.clear()
         return out
 
-    def _issue_unshard(self, g: ShardGroup) -> None:
+    def _issue_unshard(self, g: ShardGroup, urgent: bool = False) -> None:
         if g.state != SHARDED or self.world == 1:
             return
+        if hasattr(g.ag_hook, "urgent"):
+            g.ag_hook.urgent = urgent
         buf = self._param_pool.get(g.layout_key, g.padded, self.ag_stream)
         if self.cuda:
             self.ag_stream.wait_event(self._shards_ready)
@@ -364,10 +378,14 @@ class FlatShardEngine:
 
     def _wait_unshard(self, g: ShardGroup) -> None:
         if g.state == SHARDED:
-            self._issue_unshard(g)
+            self._issue_unshard(g, urgent=True)  # nobody prefetched it: the step is waiting
         if g.state == PENDING:
             if g.ag_event is not None:
-                self._current().wait_event(g.ag_event)
+                cur = self._current()
+                t0 = self._stamp(cur)
+                cur.wait_event(g.ag_event)
+                if t0 is not None:   # how long compute stood still for this gather
+                    self._comm_log.append(("all_gather_exposed", t0, self._stamp(cur), 0))
                 g.ag_event = None
             g.state = UNSHARDED
 
@@ -430,6 +448,9 @@ class FlatShardEngine:
             ev = torch.cuda.Event()
             ev.record(self._current())
             self.rs_stream.wait_event(ev)
+            if hasattr(g.rs_hook, "urgent"):
+                # backward of the groups before this one is still to come, except at the very end
+                g.rs_hook.urgent = not self.in_backward or g.index <= 1
             with torch.cuda.stream(self.rs_stream):
                 t0 = self._stamp(self.rs_stream)
                 g.rs_hook(g.grad_shard, g.full_grad, self.pg, op=dist.ReduceOp.AVG)
@@ -512,10 +533,10 @@ class FlatShardEngine:
             return
         for g in self.groups:
             if g.spec.persistent:
-                self._issue_unshard(g)
+                self._issue_unshard(g, urgent=True)
         n = 1 + max(0, self.plan.forward_prefetch_distance)
         for g in self.groups[:n]:
-            self._issue_unshard(g)
+            self._issue_unshard(g, urgent=True)  # nothing to hide behind at the start of a step
 
     def backward(self, loss: torch.Tensor) -> None:
         self.in_backward = True
@@ -523,7 +544,10 @@ class FlatShardEngine:
             for g in self.groups:
                 if g.spec.persistent:
                     self._pre_backward(g)
-            loss.backward()
+            from ..ops.loss import unit_loss_grad
+
+            with unit_loss_grad():   # the loss is the root of this backward pass
+                loss.backward()
         finally:
             self.in_backward = False
         # groups whose inputs carry no gradient (embedding) and persistent groups finish here
@@ -536,8 +560,11 @@ class FlatShardEngine:
     def wait_for_gradients(self) -> None:
         if self.cuda:
             cur = self._current()
+            t0 = self._stamp(cur) if self._rs_events else None
             for ev in self._rs_events:
                 cur.wait_event(ev)
+            if t0 is not None:       # how long the optimizer waited for the last reduce-scatters
+                self._comm_log.append(("reduce_scatter_exposed", t0, self._stamp(cur), 0))
         self._rs_events.clear()
 
     def optimizer_step(self, optimizer, lr_scheduler=None) -> None:

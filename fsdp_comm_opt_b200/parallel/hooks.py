@@ -53,7 +53,13 @@ def _resolve_transport(transport: str, device: torch.device, group) -> str:
 
 
 class _CommBase:
-    """Shared ``allocate`` (plain caching-allocator buffers, like the reference hooks)."""
+    """Shared ``allocate`` (plain caching-allocator buffers, like the reference hooks).
+
+    ``urgent`` (read at call time; the sharding engine sets it per call): False when the collective
+    runs in the shadow of compute and may take a small share of the SMs, True when the step waits
+    for it.  Only the fused symmetric-memory transport looks at it."""
+
+    urgent = True
 
     def allocate(self, size, *, dtype, device):
         return torch.empty(size, dtype=dtype, device=device)
@@ -93,7 +99,7 @@ class QuantizedAllGather(_CommBase):
 
             self.last_transport = "symm"
             return symm.channel_for(group, x.device, "ag-int8").all_gather(
-                output_tensor, x, mode="int8", async_op=async_op)
+                output_tensor, x, mode="int8", async_op=async_op, urgent=self.urgent)
         self.last_transport = "lib"
         rank = dist.get_rank(group)
         n = x.numel()
@@ -193,7 +199,7 @@ class ZipCCLAllGather(_CommBase):
             from . import symm_impl as symm
 
             return symm.channel_for(group, x.device, "ag").all_gather(
-                output_tensor, x, mode="zip", async_op=async_op)
+                output_tensor, x, mode="zip", async_op=async_op, urgent=self.urgent)
         if version == "v2":
             return self._lib_v2(output_tensor, x, group, world, async_op)
         return self._lib_v1(output_tensor, x, group, world, async_op)
@@ -343,7 +349,7 @@ class ZipCCLReduceScatter(_CommBase):
             from . import symm_impl as symm
 
             return symm.channel_for(group, x.device, "rs").reduce_scatter(
-                output_tensor, x, scale=scale, residual=self._residual_for(x), async_op=async_op)
+                output_tensor, x, scale=scale, residual=self._residual_for(x), async_op=async_op, urgent=self.urgent)
         return self._lib(output_tensor, x, group, world, scale, async_op)
 
     def _lib(self, output_tensor, x, group, world, scale, async_op):

@@ -134,6 +134,12 @@ class Channel:
         # every rank, whatever order the ranks scheduled the two kernels in.
         self.push_ctas = int(os.environ.get("ZC_SYMM_PUSH_CTAS", str(sm)))
         self.dec_ctas = int(os.environ.get("ZC_SYMM_DEC_CTAS", str(max(8, sm - 20))))
+        # Budget of a collective that runs in the shadow of a layer's GEMMs (``urgent=False``): it has
+        # milliseconds to finish, and every CTA it holds slows the GEMM it shares SMs with, so it gets
+        # a fraction of the machine.  A collective nothing can overlap with (the first gathers of a
+        # step, the last reduce-scatter) keeps the full budget above.
+        self.bg_push_ctas = int(os.environ.get("ZC_SYMM_BG_PUSH_CTAS", "32"))
+        self.bg_dec_ctas = int(os.environ.get("ZC_SYMM_BG_DEC_CTAS", "48"))
         self._lib = _lib.cuda()
         self._lib._lib.zc_symm_buffer_bytes.restype = ctypes.c_int64
         self._lib._lib.zc_symm_buffer_bytes.argtypes = [ctypes.c_int, ctypes.c_int64]
@@ -220,7 +226,12 @@ class Channel:
         return int(self._ctrl()[CW_WIRE_LO:CW_WIRE_LO + 2].view(torch.int64).item())
 
     # -- collectives -----------------------------------------------------------------------------
-    def all_gather(self, output_tensor: torch.Tensor, x: torch.Tensor, mode: str = "zip", async_op: bool = False):
+    def _budget(self, urgent: bool):
+        return (self.push_ctas, self.dec_ctas) if urgent else (min(self.push_ctas, self.bg_push_ctas),
+                                                                min(self.dec_ctas, self.bg_dec_ctas))
+
+    def all_gather(self, output_tensor: torch.Tensor, x: torch.Tensor, mode: str = "zip", async_op: bool = False,
+                   urgent: bool = True):
         """``mode="zip"``: lossless v2 codec.  ``mode="int8"``: per-shard absmax int8 (every rank,
         the source included, ends up with the dequantised values)."""
         if mode not in ("zip", "int8"):
@@ -231,9 +242,10 @@ class Channel:
         self.reserve(n)
         seq = self._next_seq()
         fn = self._lib.zc_symm_all_gather if mode == "zip" else self._lib.zc_symm_all_gather_int8
+        push, dec = self._budget(urgent)
         _lib.check(fn(
             x.data_ptr(), output_tensor.data_ptr(), self.peers_dev, self.local_ptr, self.mc_ptr or None, n, self.rank,
-            self.world, self.nc_max, seq, self.push_ctas, self.dec_ctas, self.timeout_s,
+            self.world, self.nc_max, seq, push, dec, self.timeout_s,
             _lib.stream_ptr(self.device)), "zc_symm_all_gather")
         self.calls += 1
         self.elements += n * (self.world - 1)
@@ -244,7 +256,8 @@ class Channel:
         ev.record(torch.cuda.current_stream(self.device))
         return AggregatedWork([], ready_event=ev)
 
-    def reduce_scatter(self, output_tensor: torch.Tensor, x: torch.Tensor, scale: float, residual, async_op=False):
+    def reduce_scatter(self, output_tensor: torch.Tensor, x: torch.Tensor, scale: float, residual, async_op=False,
+                       urgent: bool = True):
         shard = x.numel() // self.world
         if output_tensor.numel() != shard or output_tensor.dtype not in (torch.float32, torch.bfloat16):
             raise ValueError("output must hold numel/world fp32 or bf16 elements")
@@ -252,10 +265,11 @@ class Channel:
             raise TypeError("the fused reduce-scatter keeps its residual in bf16")
         self.reserve(shard)
         seq = self._next_seq()
+        push, dec = self._budget(urgent)
         _lib.check(self._lib.zc_symm_reduce_scatter(
             x.data_ptr(), output_tensor.data_ptr(), _lib.ptr(residual), self.peers_dev, self.local_ptr, shard,
             self.rank, self.world, self.nc_max, seq, int(x.dtype == torch.float32),
-            int(output_tensor.dtype == torch.float32), float(scale), self.push_ctas, self.dec_ctas,
+            int(output_tensor.dtype == torch.float32), float(scale), push, dec,
             self.timeout_s, _lib.stream_ptr(self.device)), "zc_symm_reduce_scatter")
         self.calls += 1
         self.elements += shard * (self.world - 1)

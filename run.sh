@@ -12,7 +12,7 @@ BATCH=${BATCH:-2}
 SEQ=${SEQ:-1024}
 export TORCHELASTIC_ERROR_FILE=${TORCHELASTIC_ERROR_FILE:-./error.json}
 if [ "${1:-synthetic}" = "hf" ]; then
-  DATA=(-d tatsu-lab/alpaca -m gpt2-xl)
+  DATA=(-d tatsu-lab/alpaca -m openai-community/gpt2-xl)   # the hub id of the reference's launch line
 else
   DATA=(--synthetic --model-shape "${MODEL_SHAPE:-gpt2-xl}")
 fi

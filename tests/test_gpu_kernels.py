@@ -400,13 +400,19 @@ def test_bias_gelu_fwd_bwd(rows, cols):
 
 
 # ------------------------------------------------------------------ GEMM
-@pytest.mark.parametrize("M,N,K", [(128, 128, 128), (256, 512, 384), (4096, 1536, 1024), (384, 256, 4096), (128, 384, 128),
-                                   (4096, 4096, 14336)])
-def test_tcgen05_gemm_three_forms(M, N, K):
+@pytest.mark.parametrize("backend,M,N,K", [
+    ("tcgen05", 128, 128, 128), ("tcgen05", 256, 512, 384), ("tcgen05", 4096, 1536, 1024), ("tcgen05", 384, 256, 4096),
+    ("tcgen05", 128, 384, 128), ("tcgen05", 4096, 4096, 14336),
+    # the two-SM kernel (the default backend): whole tiles, a split-K tail (4096 x 6144: 384 tiles on 74
+    # clusters), and edge tiles in M, N and K
+    ("tcgen05_2sm", 256, 256, 128), ("tcgen05_2sm", 512, 768, 256), ("tcgen05_2sm", 4096, 6144, 1024),
+    ("tcgen05_2sm", 4096, 4096, 14336), ("tcgen05_2sm", 384, 640, 192), ("tcgen05_2sm", 2048, 1600, 1608),
+    ("tcgen05_2sm", 136, 128, 136)])
+def test_tcgen05_gemm_three_forms(backend, M, N, K):
     from fsdp_comm_opt_b200.ops import gemm
 
     torch.manual_seed(9)
-    gemm.set_backend("tcgen05")
+    gemm.set_backend(backend)
     try:
         x = (torch.randn(M, K, device=DEV) * 0.5).bfloat16()
         w = (torch.randn(N, K, device=DEV) * 0.5).bfloat16()
@@ -415,7 +421,7 @@ def test_tcgen05_gemm_three_forms(M, N, K):
         y = gemm.gemm(x, w, False, True)            # forward
         dx = gemm.gemm(dy, w, False, False)         # dgrad:  [M,N] @ [N,K]
         dw = gemm.gemm(dy, x, True, False)          # wgrad:  [M,N]^T @ [M,K]  (needs N % 128 == 0 as "M")
-        assert _lib.launch_count() - before == 3, "tcgen05 path must have been taken"
+        assert _lib.launch_count() - before == 3, "the hand-written kernel must have been taken"
         torch.cuda.synchronize()
         assert _lib.cuda().zc_gemm_status_read_and_clear() == 0
         for got, ref in ((y, x.float() @ w.float().t()), (dx, dy.float() @ w.float()), (dw, dy.float().t() @ x.float())):

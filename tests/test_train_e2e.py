@@ -158,3 +158,50 @@ def test_rank_failure_then_resume_from_last_checkpoint(tmp_path):
     lf, lp = _losses(full), _losses(part)
     assert len(lp) == 8
     assert all(abs(x - y) < 2e-3 for x, y in zip(lf, lp)), (lf, lp)
+
+
+def _train_plain(rank, world, argv):
+    import train
+
+    train.main(argv)
+
+
+def test_text_file_dataset_with_byte_tokenizer(tmp_path):
+    """The reference's data path (tokenise everything, concatenate, cut into blocks, labels = ids;
+    reference: train.py:316-371) on a local text file with the built-in byte-level tokenizer."""
+    text = tmp_path / "corpus.txt"
+    text.write_text("\n".join(f"line {i}: the quick brown fox jumps over the lazy dog {i * 7919}" for i in range(400)))
+    log = str(tmp_path / "t.log")
+    run_ranks(_train_plain, 2, init_pg=False, args=([
+        "-d", str(text), "-m", "tiny", "--tokenizer", "bytes", "--device", "cpu", "-b", "2", "-s", "32",
+        "--lr", "1e-3", "--log-freq", "100", "--steps", "4", "-q", "--zip-ccl", "--loss-log", log],))
+    ls = _losses(log)
+    assert len(ls) == 4 and ls[-1] < ls[0]          # byte text is learnable, unlike random tokens
+
+    from fsdp_comm_opt_b200.utils.data import load_text_dataset
+
+    ds = load_text_dataset(str(text), None, "bytes", 32, 4096, vocab_size=8192, num_proc=1)
+    item = ds[0]
+    assert item["input_ids"].shape == (32,) and torch.equal(item["input_ids"], item["labels"])
+    assert int(item["input_ids"].max()) < 256
+
+
+def test_model_names_resolve_like_the_reference_launch_line(tmp_path):
+    from fsdp_comm_opt_b200.models import get_config
+
+    assert get_config("openai-community/gpt2-xl") is get_config("gpt2-xl")       # reference: run.sh:1
+    hf = {"model_type": "llama", "vocab_size": 1000, "hidden_size": 64, "num_hidden_layers": 2,
+          "num_attention_heads": 4, "num_key_value_heads": 2, "intermediate_size": 128, "rope_theta": 5e5}
+    (tmp_path / "config.json").write_text(json.dumps(hf))
+    cfg = get_config(str(tmp_path))                                               # a local HF directory
+    assert (cfg.d_model, cfg.n_kv_heads, cfg.ffn, cfg.rope_theta) == (64, 2, 128, 5e5)
+    with pytest.raises(KeyError):
+        get_config("no-such/model")
+
+
+def test_profiler_flag_writes_a_trace(tmp_path):
+    run_ranks(_train_plain, 1, init_pg=False, args=(COMMON + [
+        "--steps", "3", "-p", "--profiler-wait", "0", "--profiler-warmup", "1", "--profiler-active", "1",
+        "-e", "prof", "--save-dir", str(tmp_path)],))
+    traces = list((tmp_path / "prof" / "log" / "rank-0").glob("*"))
+    assert traces, "the tensorboard trace handler wrote nothing"

@@ -73,6 +73,11 @@ def test_noalloc_encode_matches_regular_entry_point_twice():
     _run_pair(fn, 8 * 12288, 8, seed=2, base=118)             # smaller, multi-work, over stale scratch
 
 
+def test_noalloc_at_exactly_the_size_of_its_scratch():
+    """Two works that together fill the built-in scratch to the last byte (4096 blocks of 4096)."""
+    _run_pair(_symbol(), MAX_ELEMS, 2, seed=3, base=116)
+
+
 def test_noalloc_rejects_requests_beyond_its_scratch():
     fn = _symbol()
     dev = torch.device("cuda")

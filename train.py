@@ -41,6 +41,7 @@ from torch.utils.data.distributed import DistributedSampler
 from fsdp_comm_opt_b200.engine import EngineConfig, build_sharded
 from fsdp_comm_opt_b200.models import get_config
 from fsdp_comm_opt_b200.ops.adamw import FusedAdamW
+from fsdp_comm_opt_b200.ops.loss import unit_loss_grad
 from fsdp_comm_opt_b200.parallel.fsdp import comm_report
 from fsdp_comm_opt_b200.utils import checkpoint as ckpt
 from fsdp_comm_opt_b200.utils.data import SyntheticTokens, collate, load_text_dataset
@@ -105,7 +106,8 @@ def _comm_metrics(flat, plan, steps: int, device) -> dict:
     if flat is not None:
         for kind, d in flat.comm_stats().items():
             out[f"comm/{kind}_ms_per_step"] = all_reduce_max(d["ms"] / max(steps, 1), device)
-            out[f"comm/{kind}_bus_gbs"] = d["bus_gbs"]
+            if d["bus_gbs"] is not None:
+                out[f"comm/{kind}_bus_gbs"] = d["bus_gbs"]
     if device.type == "cuda":
         rep = comm_report(plan)
         out["comm/transport"] = {"all_gather": rep["all_gather"], "reduce_scatter": rep["reduce_scatter"]}
@@ -236,7 +238,8 @@ def main(argv=None):
                     if flat is not None:
                         flat.backward(outputs.loss)
                     else:
-                        outputs.loss.backward()
+                        with unit_loss_grad():
+                            outputs.loss.backward()
                 with timers["update"], torch.profiler.record_function("STEP::update"):
                     if flat is not None:
                         flat.optimizer_step(optimizer, lr_scheduler)
