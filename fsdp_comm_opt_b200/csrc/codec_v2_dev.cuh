@@ -63,13 +63,19 @@ __device__ __forceinline__ uint32_t v2_choose_warp(const LaneSplit& s, int lane)
 }
 
 // Encode the chunk whose split fields are in `s` into `rec`; returns the final header.
+// STORE_SM = false leaves out the first 1024 bytes of the record (the sign+mantissa bytes, which a
+// caller that pushes them straight from registers does not need staged): only rec[1024 ...) is
+// written, so `rec` may then point 1024 bytes before a buffer that holds just the record's tail.
+template <bool STORE_SM = true>
 __device__ __forceinline__ uint32_t v2_encode_chunk(const LaneSplit& s, uint8_t* rec, int lane) {
   uint32_t hdr = v2_choose_warp(s, lane);
   int w = v2_hdr_width(hdr);
   const int base = v2_hdr_base(hdr);
-  uint4* smp = reinterpret_cast<uint4*>(rec + lane * 32);
-  smp[0] = make_uint4(s.sm[0], s.sm[1], s.sm[2], s.sm[3]);
-  smp[1] = make_uint4(s.sm[4], s.sm[5], s.sm[6], s.sm[7]);
+  if (STORE_SM) {
+    uint4* smp = reinterpret_cast<uint4*>(rec + lane * 32);
+    smp[0] = make_uint4(s.sm[0], s.sm[1], s.sm[2], s.sm[3]);
+    smp[1] = make_uint4(s.sm[4], s.sm[5], s.sm[6], s.sm[7]);
+  }
   if (w != V2_RAW_WIDTH && w > 0) {
     uint32_t code[8];
     codes_lane(s, base, (1u << w) - 1u, code);
@@ -102,6 +108,7 @@ __device__ __forceinline__ uint32_t v2_encode_chunk(const LaneSplit& s, uint8_t*
 // close to the count it had when it was chosen; otherwise the window is chosen afresh.  Any valid
 // choice decodes correctly, so this only trades a little compression for skipping the histogram.
 // Returns the header; `hint` / `hint_esc` are updated for the next chunk.
+template <bool STORE_SM = true>
 __device__ __forceinline__ uint32_t v2_encode_chunk_hint(const LaneSplit& s, uint8_t* rec, int lane, uint32_t& hint,
                                                          int& hint_esc) {
   if (hint != 0xFFFFFFFFu) {
@@ -112,9 +119,11 @@ __device__ __forceinline__ uint32_t v2_encode_chunk_hint(const LaneSplit& s, uin
     int n_esc;
     const int pos = warp_excl_scan(__popc(zm), lane, n_esc);
     if (n_esc <= hint_esc + (hint_esc >> 1) + 16 && 128 * w + n_esc <= V2_CHUNK_ELEMS) {
-      uint4* smp = reinterpret_cast<uint4*>(rec + lane * 32);
-      smp[0] = make_uint4(s.sm[0], s.sm[1], s.sm[2], s.sm[3]);
-      smp[1] = make_uint4(s.sm[4], s.sm[5], s.sm[6], s.sm[7]);
+      if (STORE_SM) {
+        uint4* smp = reinterpret_cast<uint4*>(rec + lane * 32);
+        smp[0] = make_uint4(s.sm[0], s.sm[1], s.sm[2], s.sm[3]);
+        smp[1] = make_uint4(s.sm[4], s.sm[5], s.sm[6], s.sm[7]);
+      }
       uint32_t* pl = reinterpret_cast<uint32_t*>(rec + 1024) + lane;
       pl[0] = plane_word<0>(code);
       if (w > 1) pl[32] = plane_word<1>(code);
@@ -124,7 +133,7 @@ __device__ __forceinline__ uint32_t v2_encode_chunk_hint(const LaneSplit& s, uin
       return v2_header(base, w, n_esc);
     }
   }
-  const uint32_t hdr = v2_encode_chunk(s, rec, lane);
+  const uint32_t hdr = v2_encode_chunk<STORE_SM>(s, rec, lane);
   const int w = v2_hdr_width(hdr);
   if (w >= 1 && w <= 4) {
     hint = hdr & 0xFFFFu;

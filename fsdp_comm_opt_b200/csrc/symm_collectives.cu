@@ -111,6 +111,13 @@ __device__ __forceinline__ void warp_copy16(uint8_t* dst, const uint8_t* src, in
     reinterpret_cast<uint4*>(dst)[i] = reinterpret_cast<const uint4*>(src)[i];
 }
 
+// the 32 sign+mantissa bytes of one lane, straight from registers to (peer) memory
+__device__ __forceinline__ void store_sm32(uint8_t* rec, int lane, const LaneSplit& s) {
+  uint4* p = reinterpret_cast<uint4*>(rec + lane * 32);
+  p[0] = make_uint4(s.sm[0], s.sm[1], s.sm[2], s.sm[3]);
+  p[1] = make_uint4(s.sm[4], s.sm[5], s.sm[6], s.sm[7]);
+}
+
 // NVSwitch multicast stores: one store to the multicast mapping of the symmetric buffer lands at the
 // same offset in every rank's copy (this rank's included), so an all-gather leaves the GPU once
 // instead of once per peer.  Values are moved as raw bits.
@@ -152,7 +159,9 @@ __device__ __forceinline__ bool warp_wait_flag(const uint32_t* fl, uint32_t want
 }
 
 __global__ void __launch_bounds__(256) symm_all_gather_kernel(const AgArgs a) {
-  __shared__ __align__(16) uint8_t srec[8][V2_SLOT_BYTES];  // pushers: record staging; decoders: escape staging
+  // pushers: the record's tail (planes, escapes, raw exponents), its first 1024 bytes go out straight
+  // from registers; decoders: escape staging.  8 KB, so that two collective CTAs fit beside a GEMM CTA.
+  __shared__ __align__(16) uint8_t srec[8][V2_SLOT_BYTES / 2];
   __shared__ int s_ok;
   const SymmLayout& L = a.L;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -190,7 +199,7 @@ __global__ void __launch_bounds__(256) symm_all_gather_kernel(const AgArgs a) {
         if (copy_own) store_lane(own + e0, a.n - e0, own_al, li);
         LaneSplit s;
         split_lane(li, s);
-        const uint32_t hdr = v2_encode_chunk_hint(s, srec[warp], lane, hint, hint_esc);
+        const uint32_t hdr = v2_encode_chunk_hint<false>(s, srec[warp] - 1024, lane, hint, hint_esc);
         __syncwarp();
         const int used = v2_record_bytes(hdr);
         if (!ZC_SLOT_OK(L, c, used, a.local, L.rank)) {
@@ -198,14 +207,18 @@ __global__ void __launch_bounds__(256) symm_all_gather_kernel(const AgArgs a) {
           continue;
         }
         if (a.mc) {
-          uint8_t* slot = slot_ptr(a.mc, L, parity, L.rank);
-          warp_copy16_mc(slot + L.hdr_bytes + c * V2_SLOT_BYTES, srec[warp], used, lane);
-          if (lane == 0) mc_st32(reinterpret_cast<uint32_t*>(slot) + c, hdr);
+          uint8_t* rec = slot_ptr(a.mc, L, parity, L.rank) + L.hdr_bytes + c * V2_SLOT_BYTES;
+          mc_st128(rec + lane * 32, make_uint4(s.sm[0], s.sm[1], s.sm[2], s.sm[3]));
+          mc_st128(rec + lane * 32 + 16, make_uint4(s.sm[4], s.sm[5], s.sm[6], s.sm[7]));
+          warp_copy16_mc(rec + 1024, srec[warp], used - 1024, lane);
+          if (lane == 0) mc_st32(reinterpret_cast<uint32_t*>(slot_ptr(a.mc, L, parity, L.rank)) + c, hdr);
         } else {
           for (int q = 0; q < L.world; ++q) {
             if (q == L.rank) continue;
             uint8_t* slot = slot_ptr(a.peers[q], L, parity, L.rank);
-            warp_copy16(slot + L.hdr_bytes + c * V2_SLOT_BYTES, srec[warp], used, lane);
+            uint8_t* rec = slot + L.hdr_bytes + c * V2_SLOT_BYTES;
+            store_sm32(rec, lane, s);
+            warp_copy16(rec + 1024, srec[warp], used - 1024, lane);
             if (lane == 0) reinterpret_cast<uint32_t*>(slot)[c] = hdr;
           }
         }
@@ -327,7 +340,9 @@ __device__ __forceinline__ void load_lane_f32(const void* base, bool fp32, long 
 }
 
 __global__ void __launch_bounds__(256, 2) symm_reduce_scatter_kernel(const RsArgs a) {
-  __shared__ __align__(16) uint8_t srec[8][V2_SLOT_BYTES];  // pushers: record staging; decoders: escape staging
+  // pushers: the record's tail (planes, escapes, raw exponents), its first 1024 bytes go out straight
+  // from registers; decoders: escape staging.  8 KB, so that two collective CTAs fit beside a GEMM CTA.
+  __shared__ __align__(16) uint8_t srec[8][V2_SLOT_BYTES / 2];
   __shared__ int s_ok;
   const SymmLayout& L = a.L;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -385,14 +400,15 @@ __global__ void __launch_bounds__(256, 2) symm_reduce_scatter_kernel(const RsArg
         }
         LaneSplit s;
         split_lane(li, s);
-        const uint32_t hdr = v2_encode_chunk_hint(s, srec[warp], lane, hint, hint_esc);
+        const uint32_t hdr = v2_encode_chunk_hint<false>(s, srec[warp] - 1024, lane, hint, hint_esc);
         __syncwarp();
         const int used = v2_record_bytes(hdr);
         if (!ZC_SLOT_OK(L, c, used, a.local, q)) {
           __syncwarp();
           continue;
         }
-        warp_copy16(slot + L.hdr_bytes + c * V2_SLOT_BYTES, srec[warp], used, lane);
+        store_sm32(slot + L.hdr_bytes + c * V2_SLOT_BYTES, lane, s);
+        warp_copy16(slot + L.hdr_bytes + c * V2_SLOT_BYTES + 1024, srec[warp], used - 1024, lane);
         if (lane == 0) {
           reinterpret_cast<uint32_t*>(slot)[c] = hdr;
           pushed += (unsigned long long)(used + 4);
