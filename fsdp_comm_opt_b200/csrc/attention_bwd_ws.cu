@@ -579,9 +579,17 @@ __global__ void __launch_bounds__(352, 1) attn_bwd_kt_kernel(const __grid_consta
       const uint32_t id_dq = idesc_bf16(128, QB, MAJOR_MN, MAJOR_MN);   // dQ^T
       const uint32_t aK = smem_u32(sK), aV = smem_u32(sV), aQ = smem_u32(sQ), adO = smem_u32(sdO), aP = smem_u32(sP),
                      adS = smem_u32(sdS);
-      // K-major views: 128-row tile (slab stride 16 KB) and 64-row tile (slab stride 8 KB)
-      auto k128 = [](uint32_t base, int k) { return smem_desc(base + (k >> 2) * 16384 + (k & 3) * 32, 16, 1024); };
-      auto k64 = [](uint32_t base, int k) { return smem_desc(base + (k >> 2) * 8192 + (k & 3) * 32, 16, 1024); };
+      // Operand descriptors at offset 0, built once; an MMA adds (byte offset >> 4) to the start-address
+      // field (shared memory is below 256 KB, the 14-bit field never carries).  The S^T / dP^T / dQ^T
+      // MMAs are 32 clocks of tensor work each: the issuing thread cannot afford to build two
+      // descriptors between them.
+      const uint64_t dK_k = smem_desc(aK, 16, 1024), dV_k = smem_desc(aV, 16, 1024);       // K-major, 16 KB slabs
+      const uint64_t dQ_k = smem_desc(aQ, 16, 1024), ddO_k = smem_desc(adO, 16, 1024);     // K-major, 8 KB slabs
+      const uint64_t dP_k = smem_desc(aP, 16, 1024), ddS_k = smem_desc(adS, 16, 1024);     // K-major A operands
+      const uint64_t ddO_mn = smem_desc(adO, 8192, 1024), dQ_mn = smem_desc(aQ, 8192, 1024);  // MN-major B operands
+      const uint64_t dK_mn = smem_desc(aK, 16384, 1024), ddS_mn = smem_desc(adS, 8192, 1024);
+      auto off128 = [](int k) { return (uint64_t)(((k >> 2) * 16384 + (k & 3) * 32) >> 4); };
+      auto off64 = [](int k) { return (uint64_t)(((k >> 2) * 8192 + (k & 3) * 32) >> 4); };
       bool ok = role_wait(&kv_full, 0);
       // Two issuers: a tcgen05.mma takes about a hundred cycles to issue whatever its width, so the
       // 32 MMAs of an iteration are split between warp 1 (S^T, dP^T) and warp 10 (dV, dK, dQ^T).
@@ -594,11 +602,11 @@ __global__ void __launch_bounds__(352, 1) attn_bwd_kt_kernel(const __grid_consta
           if (i > 0 && !(ok = role_wait(&sdp_empty, (i - 1) & 1))) break;
           tc_fence_after_sync();
           ZC_BTRACE(1, i, 2);
-          const uint32_t q = aQ + st * 16384, d_o = adO + st * 16384;
+          const uint64_t stg = (uint64_t)(st * (16384 >> 4));
 #pragma unroll
-          for (int k = 0; k < D / 16; ++k) mma_bf16(tm_st, k128(aK, k), k64(q, k), id_st, k != 0);
+          for (int k = 0; k < D / 16; ++k) mma_bf16(tm_st, dK_k + off128(k), dQ_k + stg + off64(k), id_st, k != 0);
 #pragma unroll
-          for (int k = 0; k < D / 16; ++k) mma_bf16(tm_dp, k128(aV, k), k64(d_o, k), id_st, k != 0);
+          for (int k = 0; k < D / 16; ++k) mma_bf16(tm_dp, dV_k + off128(k), ddO_k + stg + off64(k), id_st, k != 0);
           mma_commit(&sdp_full);
           ZC_BTRACE(1, i, 3);
         }
@@ -613,19 +621,21 @@ __global__ void __launch_bounds__(352, 1) attn_bwd_kt_kernel(const __grid_consta
           if (!(ok = role_wait(&dq_empty[st], ph ^ 1))) break;
           tc_fence_after_sync();
           ZC_BTRACE(2, i, 2);
-          const uint32_t pT = aP + st * 16384, dsT = adS + st * 16384, q = aQ + st * 16384, d_o = adO + st * 16384;
+          const uint64_t stg = (uint64_t)(st * (16384 >> 4));
           // dV += P^T dO and dK += dS^T Q: A = [128 keys x 64 queries] K-major, B = [64 queries x 128] MN-major
 #pragma unroll
           for (int k = 0; k < QB / 16; ++k)
-            mma_bf16(tm_dv, smem_desc(pT + k * 32, 16, 1024), smem_desc(d_o + k * 2048, 8192, 1024), id_kv, (i | k) != 0);
+            mma_bf16(tm_dv, dP_k + stg + (uint64_t)((k * 32) >> 4), ddO_mn + stg + (uint64_t)((k * 2048) >> 4), id_kv,
+                     (i | k) != 0);
 #pragma unroll
           for (int k = 0; k < QB / 16; ++k)
-            mma_bf16(tm_dk, smem_desc(dsT + k * 32, 16, 1024), smem_desc(q + k * 2048, 8192, 1024), id_kv, (i | k) != 0);
+            mma_bf16(tm_dk, ddS_k + stg + (uint64_t)((k * 32) >> 4), dQ_mn + stg + (uint64_t)((k * 2048) >> 4), id_kv,
+                     (i | k) != 0);
           // dQ^T = K^T dS^T: A = K read MN-major (M = head dim), B = dS^T read MN-major (N = queries)
 #pragma unroll
           for (int k = 0; k < 8; ++k)
-            mma_bf16(tm_dq + st * QB, smem_desc(aK + k * 2048, 16384, 1024), smem_desc(dsT + k * 2048, 8192, 1024), id_dq,
-                     k != 0);
+            mma_bf16(tm_dq + st * QB, dK_mn + (uint64_t)((k * 2048) >> 4), ddS_mn + stg + (uint64_t)((k * 2048) >> 4),
+                     id_dq, k != 0);
           mma_commit(&dq_full[st]);
           mma_commit(&pds_empty[st]);
           mma_commit(&qdo_empty[st]);

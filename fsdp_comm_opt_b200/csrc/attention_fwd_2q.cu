@@ -133,8 +133,9 @@ __global__ void __launch_bounds__(THREADS, 1) attn_fwd_2q_kernel(const __grid_co
       }
     }
   } else if (warp == 1 || warp == 10) {
-    // one MMA issuer per query tile (warp 1: tile 0, warp 10: tile 1): a tcgen05.mma takes about a
-    // hundred cycles to issue whatever its width, so one thread cannot feed the tensor core alone
+    // one MMA issuer per query tile (warp 1: tile 0, warp 10: tile 1).  The S MMAs are 32 clocks of
+    // tensor work each, so the issuing thread must not spend more than that between two of them:
+    // the operand descriptors are built once and an MMA adds a constant to their address field.
     if (lane == 0) {
       const int t = warp == 1 ? 0 : 1;
       const uint32_t id_s = idesc_bf16(128, KB, MAJOR_K, MAJOR_K);
@@ -142,6 +143,12 @@ __global__ void __launch_bounds__(THREADS, 1) attn_fwd_2q_kernel(const __grid_co
       const uint32_t aQ = smem_u32(sQ) + t * 32768, aKV = smem_u32(sKV), aP = smem_u32(sP) + t * 32768;
       const uint32_t tm_s = tm + t * 64, tm_o = tm + 128 + t * 128;
       const int nbt = nb[t];
+      // descriptors at offset 0 of each operand; byte offsets are added to the start-address field as
+      // offset >> 4 (shared memory is below 256 KB, the 14-bit field never carries)
+      const uint64_t dQ0 = smem_desc(aQ, 16, 1024);               // Q tile, K-major, 16 KB slabs
+      const uint64_t dK0 = smem_desc(aKV, 16, 1024);              // K block of stage 0, K-major, 8 KB slabs
+      const uint64_t dV0 = smem_desc(aKV + 16384, 8192, 1024);    // V block of stage 0, MN-major
+      const uint64_t dP0 = smem_desc(aP, 16, 1024);               // P tile of parity 0, K-major
       bool ok = role_wait(&q_full, 0, &s_abort);
       // S_t(j) = Q_t K_j^T: A = Q tile (K-major, 16 KB slabs), B = K block (K-major, 8 KB slabs)
       auto issue_s = [&](int j) -> bool {
@@ -149,11 +156,11 @@ __global__ void __launch_bounds__(THREADS, 1) attn_fwd_2q_kernel(const __grid_co
         if (!role_wait(&kv_full[s], (j / STAGES) & 1, &s_abort)) return false;
         if (j > 0 && !role_wait(&s_empty[t], (j - 1) & 1, &s_abort)) return false;
         tc_fence_after_sync();
-        const uint32_t ka = aKV + s * 32768;
+        const uint64_t dK = dK0 + (uint64_t)(s * (32768 >> 4));
 #pragma unroll
         for (int k = 0; k < D / 16; ++k)
-          mma_bf16(tm_s, smem_desc(aQ + (k >> 2) * 16384 + (k & 3) * 32, 16, 1024),
-                   smem_desc(ka + (k >> 2) * 8192 + (k & 3) * 32, 16, 1024), id_s, k != 0);
+          mma_bf16(tm_s, dQ0 + (uint64_t)(((k >> 2) * 16384 + (k & 3) * 32) >> 4),
+                   dK + (uint64_t)(((k >> 2) * 8192 + (k & 3) * 32) >> 4), id_s, k != 0);
         mma_commit(&s_full[t]);
         return true;
       };
@@ -173,11 +180,11 @@ __global__ void __launch_bounds__(THREADS, 1) attn_fwd_2q_kernel(const __grid_co
         tc_fence_after_sync();
         if (t == 0) ZC_TRACE(1, j, 2);
         // O_t += P_t V_j: A = P tile [128 x 64 keys] K-major, B = V block [64 keys x 128] MN-major
-        const uint32_t va = aKV + (j % STAGES) * 32768 + 16384;
+        const uint64_t dV = dV0 + (uint64_t)((j % STAGES) * (32768 >> 4));
+        const uint64_t dP = dP0 + (uint64_t)((j & 1) * (16384 >> 4));
 #pragma unroll
         for (int k = 0; k < KB / 16; ++k)
-          mma_bf16(tm_o, smem_desc(aP + (j & 1) * 16384 + k * 32, 16, 1024), smem_desc(va + k * 2048, 8192, 1024), id_o,
-                   (j | k) != 0);
+          mma_bf16(tm_o, dP + (uint64_t)((k * 32) >> 4), dV + (uint64_t)((k * 2048) >> 4), id_o, (j | k) != 0);
         mma_commit(&o_full[2 * t + (j & 1)]);
         mma_commit(&kv_empty[j % STAGES]);  // this tile's readers of the stage have been issued
         if (t == 0) ZC_TRACE(1, j, 3);
