@@ -101,6 +101,7 @@ def main():
         rs(out, rows[0], group, dist.ReduceOp.AVG)
         torch.cuda.synchronize(device)
         err = float((out - ref).abs().max().item())
+        ref0 = ref.clone()   # fp32 sum of rows[0]: the timing loops below overwrite `ref`
         ch = symm_impl.channel_for(group, device, "rs") if args.transport == "symm" else None
         w0 = ch.wire_bytes() if ch else 0
         ms_z = _timed(lambda i: rs(out, rows[i & 1], group, dist.ReduceOp.AVG), args.iters, device)
@@ -126,7 +127,7 @@ def main():
         ref16 = torch.empty_like(out16)
         rs(out16, rows16[0], group, dist.ReduceOp.AVG)
         torch.cuda.synchronize(device)
-        err = float((out16.float() - ref).abs().max().item())   # against the fp32 NCCL result above
+        err = float((out16.float() - ref0).abs().max().item())   # against the fp32 NCCL result of the same rows
         ms_z = _timed(lambda i: rs(out16, rows16[i & 1], group, dist.ReduceOp.AVG), args.iters, device)
         scratch = [r.clone() for r in rows16]
         ms_n = _timed(lambda i: dist.reduce_scatter_tensor(ref16, scratch[i & 1], op=dist.ReduceOp.AVG), args.iters, device)
@@ -138,7 +139,7 @@ def main():
                               "zip_bus_gbs": round(payload * (world - 1) / world / ms_z / 1e6, 1),
                               "nccl_bus_gbs": round(payload * (world - 1) / world / ms_n / 1e6, 1),
                               "max_abs_err_vs_fp32_sum": err}), flush=True)
-        del rows16, scratch, out, ref, out16, ref16
+        del rows16, scratch, out, ref, ref0, out16, ref16
         torch.cuda.empty_cache()
     for ch in symm_impl.all_channels():
         ch.check_status()
