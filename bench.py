@@ -104,6 +104,8 @@ def parse_args():
     ap.add_argument("--no-compress", action="store_true", help="ours: stock NCCL collectives")
     ap.add_argument("--act-ckpt", action="store_true")
     ap.add_argument("--gemm", default=None, choices=[None, "auto", "tcgen05", "tcgen05_2sm", "cublas"])
+    ap.add_argument("--reshard-after-forward", default="auto", choices=["auto", "true", "false"],
+                    help="ours (flat): release gathered parameters after forward (ZeRO-3) or keep them until backward")
     ap.add_argument("--comm-stats", action="store_true",
                     help="ours: bracket every collective with CUDA events and report per-step device time, bus "
                          "GB/s and the time compute stood still waiting for communication (a few events per "
@@ -128,8 +130,11 @@ def make_ours(args, device):
     comp = not args.no_compress
     eng = TrainEngine(EngineConfig(model=args.model, quantize=comp, zip_ccl=comp, compress_rs=comp,
                                    transport=args.transport, act_ckpt=args.act_ckpt, sharding=args.sharding,
-                                   time_collectives=args.comm_stats), device)
+                                   time_collectives=args.comm_stats,
+                                   reshard_after_forward={"auto": "auto", "true": True, "false": False}[
+                                       args.reshard_after_forward]), device)
     info = {"gemm_backend": gemm.get_backend(), "native_lib": str(_lib.cuda_lib_path()), "sharding": args.sharding,
+            "reshard_after_forward": eng.flat.reshard_after_forward if eng.flat is not None else True,
             "comm_requested": "zip all-gather + compressed reduce-scatter" if comp else "nccl"}
     make_ours.engine = eng
     return eng.step_on_device, eng.step, info, _lib

@@ -45,6 +45,7 @@ class EngineConfig:
     cpu_offload: bool = False       # fsdp2 only
     error_feedback: bool = True
     time_collectives: bool = False  # flat only: CUDA-event timing of every collective
+    reshard_after_forward: object = "auto"   # flat only: True | False | "auto" (see FlatShardPlan)
 
 
 def build_sharded(cfg: EngineConfig, device: torch.device):
@@ -73,7 +74,7 @@ def build_sharded(cfg: EngineConfig, device: torch.device):
     fplan = FlatShardPlan(ag_hook_factory=ag_factory, rs_hook_factory=rs_factory,
                           forward_prefetch_distance=cfg.forward_prefetch_distance,
                           master_dtype=cfg.master_dtype, act_ckpt=cfg.act_ckpt,
-                          time_collectives=cfg.time_collectives)
+                          time_collectives=cfg.time_collectives, reshard_after_forward=cfg.reshard_after_forward)
     flat = FlatShardEngine(model, shard_groups(model), fplan, device)
     return model, plan, flat
 

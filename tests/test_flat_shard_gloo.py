@@ -22,6 +22,8 @@ def _run(rank, world, kind, steps, out_path, model="tiny"):
         kw.update(quantize=True, zip_ccl=True, compress_rs=True)
     elif kind == "ckpt":
         kw.update(act_ckpt=True)
+    elif kind == "keep":
+        kw.update(reshard_after_forward=False, quantize=True, zip_ccl=True, compress_rs=True)
     elif kind == "fp32":
         kw.update(master_dtype=torch.float32, quantize=True, zip_ccl=True, compress_rs=True)
     eng = TrainEngine(EngineConfig(**kw), torch.device("cpu"))
@@ -35,7 +37,7 @@ def _load(p):
 
 
 def test_flat_engine_lossless_hooks_give_identical_curves(tmp_path):
-    paths = {k: str(tmp_path / f"{k.replace('+', '_')}.pt") for k in ("plain", "zip", "zip+rs", "ckpt")}
+    paths = {k: str(tmp_path / f"{k.replace('+', '_')}.pt") for k in ("plain", "zip", "zip+rs", "ckpt", "keep")}
     for kind, p in paths.items():
         run_ranks(_run, 2, args=(kind, 5, p))
     base = _load(paths["plain"])["losses"]
@@ -43,6 +45,8 @@ def test_flat_engine_lossless_hooks_give_identical_curves(tmp_path):
     assert _load(paths["zip"])["losses"] == base          # lossless all-gather
     assert _load(paths["zip+rs"])["losses"] == base       # bf16 rows, fp32 sum of two ranks
     assert _load(paths["ckpt"])["losses"] == base         # recomputation is exact
+    assert _load(paths["keep"])["losses"] == base         # parameters kept gathered until backward
+    assert _load(paths["keep"])["pool"]["reshard_after_forward"] is False
     pool = _load(paths["plain"])["pool"]
     # steady state: a handful of buffers, not one per layer and step
     assert pool["param_buffers"] <= 9 and pool["grad_buffers"] <= 6, pool

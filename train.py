@@ -91,6 +91,9 @@ def _get_parser() -> argparse.ArgumentParser:
                    help="> 0: ranks publish a heartbeat each step and abort when a peer is silent that long")
     p.add_argument("--loss-log", default=None, help="rank 0 appends 'step loss' lines to this file")
     p.add_argument("--sharding", default="flat", choices=["flat", "fsdp2"])
+    p.add_argument("--reshard-after-forward", default="auto", choices=["auto", "true", "false"],
+                   help="flat sharding: release gathered parameters after forward (the reference's ZeRO-3 setting), keep "
+                        "them until backward, or decide by the memory they take (auto)")
     p.add_argument("--dist-timeout", default=None, type=float,
                    help="seconds after which a collective whose peer never joins fails instead of waiting "
                         "(process-group timeout; the default is the backend's)")
@@ -141,7 +144,8 @@ def main(argv=None):
                         zip_ccl=args.zip_ccl, compress_rs=args.compress_rs, act_ckpt=args.act_ckpt,
                         forward_prefetch_distance=args.forward_prefetch_distance, transport=args.transport,
                         codec_version=args.codec, seed=args.seed, sharding=sharding, cpu_offload=args.cpu_offload,
-                        error_feedback=not args.no_error_feedback, time_collectives=True)
+                        error_feedback=not args.no_error_feedback, time_collectives=True,
+                        reshard_after_forward={"auto": "auto", "true": True, "false": False}[args.reshard_after_forward])
     model, plan, flat = build_sharded(ecfg, device)
     LOGGER.info(f"Training {cfg.num_params()} model parameters ({sharding} sharding)")
     LOGGER.info(f"Initialized model uses {get_mem_stats(device)['curr_alloc_gb']}gb")
