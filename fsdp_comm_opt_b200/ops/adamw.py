@@ -50,7 +50,10 @@ class FusedAdamW(torch.optim.Optimizer):
                     st["exp_avg_sq"] = torch.zeros_like(p, memory_format=torch.preserve_format)
 
     @torch.no_grad()
-    def step(self, closure=None):
+    def step(self, closure=None, split_at: int | None = None, between=None):
+        """``split_at`` / ``between``: update elements ``[0, split_at)`` of every (flat) parameter first, call
+        ``between()``, then update the rest.  The flat-shard engine uses it to start gathering the
+        first groups of the next step while the rest of the shards are still being updated."""
         loss = None
         if closure is not None:
             with torch.enable_grad():
@@ -82,12 +85,20 @@ class FusedAdamW(torch.optim.Optimizer):
                     lib = _lib.cuda()
                     with torch.cuda.device(pl.device):
                         guard = lib.zc_health_word()
-                    _lib.check(lib.zc_adamw_guarded(
-                        pl.data_ptr(), gl.data_ptr(), ml.data_ptr(), vl.data_ptr(), pl.numel(),
-                        _DT[pl.dtype], _DT[gl.dtype], _DT[ml.dtype], float(lr), float(b1), float(b2),
-                        float(eps), float(wd), float(bc1), float(bc2), int(self.zero_grad_in_step),
-                        guard, _lib.stream_ptr(pl.device)), "zc_adamw")
-                    self.kernel_launches += 1
+                    n = pl.numel()
+                    cut = n if split_at is None else max(0, min(n, int(split_at) // 8 * 8))
+                    for lo, hi in ((0, cut), (cut, n)):
+                        if hi > lo:
+                            _lib.check(lib.zc_adamw_guarded(
+                                pl.data_ptr() + lo * pl.element_size(), gl.data_ptr() + lo * gl.element_size(),
+                                ml.data_ptr() + lo * ml.element_size(), vl.data_ptr() + lo * vl.element_size(), hi - lo,
+                                _DT[pl.dtype], _DT[gl.dtype], _DT[ml.dtype], float(lr), float(b1), float(b2),
+                                float(eps), float(wd), float(bc1), float(bc2), int(self.zero_grad_in_step),
+                                guard, _lib.stream_ptr(pl.device)), "zc_adamw")
+                            self.kernel_launches += 1
+                        if hi == cut and between is not None and cut < n:
+                            between()
+                            between = None
                 else:
                     g = gl.float()
                     pf = pl.float()
@@ -99,4 +110,6 @@ class FusedAdamW(torch.optim.Optimizer):
                     pl.copy_(pf), ml.copy_(m), vl.copy_(v)
                     if self.zero_grad_in_step:
                         gl.zero_()
+        if between is not None:
+            between()
         return loss

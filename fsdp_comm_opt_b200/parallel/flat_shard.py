@@ -583,15 +583,37 @@ class FlatShardEngine:
         self._rs_events.clear()
 
     def optimizer_step(self, optimizer, lr_scheduler=None) -> None:
+        """Update all shards, then start the next step's first gathers.  With more than one rank and
+        a ``FusedAdamW`` the update is cut in two: the shards of the first groups (whose gathers the
+        next forward waits for) are updated first, their gathers start, and the rest of the update
+        runs beside them."""
         self.wait_for_gradients()
         self.master_param.grad = self.grad_master
-        optimizer.step()
+        early = self._early_groups() if (self.world > 1 and self.plan.prefetch_next_step and self.cuda
+                                         and self.master_c is self.master) else []
+        if early and hasattr(optimizer, "kernel_launches"):
+            cut = sum(g.shard_numel for g in self.groups[:len(early)])
+
+            def start_first_gathers():
+                self._record_shards_ready()
+                for g in early:
+                    self._issue_unshard(g, urgent=True)
+
+            optimizer.step(split_at=cut, between=start_first_gathers)
+        else:
+            optimizer.step()
         if lr_scheduler is not None:
             lr_scheduler.step()
         self._sync_compute_copy()
         self._record_shards_ready()
         if self.plan.prefetch_next_step:
             self.begin_step()
+
+    def _early_groups(self) -> list:
+        """The leading groups whose gathers ``begin_step`` issues (a prefix of the group list; persistent
+        groups elsewhere in the list are left to ``begin_step``)."""
+        n = 1 + max(0, self.plan.forward_prefetch_distance)
+        return list(self.groups[:n])
 
     # ------------------------------------------------------------------------------------------
     # state

@@ -515,3 +515,24 @@ def test_adamw_is_skipped_while_the_health_word_is_set():
     torch.cuda.synchronize()
     assert not torch.equal(p.detach(), before)
     assert lib.zc_health_read_and_clear() == 0
+
+
+def test_adamw_in_two_launches_equals_one():
+    """``step(split_at=..., between=...)`` updates a prefix first, calls back, then updates the rest:
+    same result as one launch (every element is independent)."""
+    from fsdp_comm_opt_b200.ops.adamw import FusedAdamW
+
+    torch.manual_seed(4)
+    w = torch.randn(100_000, device=DEV).bfloat16()
+    g = torch.randn_like(w)
+    a, b = torch.nn.Parameter(w.clone()), torch.nn.Parameter(w.clone())
+    a.grad, b.grad = g.clone(), g.clone()
+    oa, ob = FusedAdamW([a], lr=1e-2), FusedAdamW([b], lr=1e-2)
+    called = []
+    for _ in range(3):
+        oa.step()
+        ob.step(split_at=33_333, between=lambda: called.append(1))
+    torch.cuda.synchronize()
+    assert len(called) == 3 and ob.kernel_launches == 6 and oa.kernel_launches == 3
+    assert torch.equal(a.detach(), b.detach())
+    assert torch.equal(oa.state[a]["exp_avg_sq"], ob.state[b]["exp_avg_sq"])
