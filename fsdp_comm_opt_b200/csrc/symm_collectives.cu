@@ -260,6 +260,8 @@ __global__ void __launch_bounds__(256) symm_all_gather_kernel(const AgArgs a) {
     uint16_t* dst = a.out + (long long)src * a.n;
     const bool al = (reinterpret_cast<uintptr_t>(dst) & 15) == 0;
     // the item's eight headers in one load, then record k+1 in flight while record k is decoded
+    // (two records ahead was measured and is slower: with eight warps per SM the decoder is bound by
+    // its own instruction stream, and the extra registers cost a resident CTA)
     const uint32_t myhdr = lane < cnt ? __ldcg(reinterpret_cast<const uint32_t*>(slot) + c0 + lane) : 0u;
     RecRegs cur, nxt;
     v2_prefetch(recs, __shfl_sync(FULL, myhdr, 0), lane, cur);
