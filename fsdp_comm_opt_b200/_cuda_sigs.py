@@ -39,6 +39,7 @@ def declare(lib) -> None:
     _sig(lib, "zc_swiglu_fwd", P, P, L, I, P)
     _sig(lib, "zc_swiglu_bwd", P, P, P, L, I, P)
     _sig(lib, "zc_ce_fwd_bwd", P, P, P, P, L, I, I, P)
+    _sig(lib, "zc_ce_fwd_bwd_ld", P, P, P, P, L, I, L, I, P)
     _sig(lib, "zc_quant_int8", P, L, I, P, P)
     _sig(lib, "zc_dequant_int8", P, L, I, L, I, P, P)
     _sig(lib, "zc_adamw", P, P, P, P, L, I, I, I, F, F, F, F, F, F, F, I, P)
@@ -62,6 +63,7 @@ def declare(lib) -> None:
     _sig(lib, "zc_attn_bwd_kt", P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, *([L] * 18), F, P)
     _sig(lib, "zc_gemm_bf16", P, P, P, L, L, L, I, I, I, P)
     _sig(lib, "zc_gemm_bf16_2sm", P, P, P, L, L, L, I, I, I, P)
+    _sig(lib, "zc_gemm_bf16_2sm_ld", P, P, P, L, L, L, L, L, L, I, I, I, P)
     _sig(lib, "zc_gemm_status_read_and_clear")
     # fused collectives
     from ctypes import c_double, c_uint

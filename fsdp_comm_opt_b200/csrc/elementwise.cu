@@ -366,46 +366,45 @@ __global__ void __launch_bounds__(256) swiglu_bwd_kernel(const __nv_bfloat16* __
 // ---------------------------------------------------------------------------------------------
 // Cross-entropy: one CTA per row; pass 1 online max / sum-exp, pass 2 writes the gradient over the
 // logits.  row_loss = lse - logit[label];  grad = (softmax - onehot) * inv_count
+// Rows are `ld` elements apart (ld >= V; ld > V for a vocabulary that is not a multiple of 8, whose
+// logits the GEMM writes into rows padded to an aligned stride); the pad columns come out as zeros.
 // ---------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(1024) ce_kernel(__nv_bfloat16* __restrict__ logits,
                                                   const int64_t* __restrict__ labels,
                                                   float* __restrict__ row_loss, const float* __restrict__ inv_count,
-                                                  int V, int ignore_index) {
+                                                  int V, int64_t ld, int ignore_index) {
   __shared__ float red[32];
   const int64_t row = blockIdx.x;
-  __nv_bfloat16* lr = logits + row * V;
+  __nv_bfloat16* lr = logits + row * ld;
   const int64_t label = labels[row];
-  const bool vec = (V % 8 == 0) && ((reinterpret_cast<uintptr_t>(lr) & 15) == 0);
+  // whole 8-element vectors when the row starts on 16 bytes; the last V % 8 columns one by one
+  const int nvec = ((ld % 8 == 0) && ((reinterpret_cast<uintptr_t>(logits) & 15) == 0)) ? V / 8 : 0;
+  const int tail0 = nvec * 8;
+  const __nv_bfloat16 zero = __float2bfloat16(0.f);
   if (label == ignore_index) {
-    if (vec) {
-      BF8 z;
+    BF8 z;
 #pragma unroll
-      for (int i = 0; i < 4; ++i) z.v[i] = __floats2bfloat162_rn(0.f, 0.f);
-      for (int v = threadIdx.x; v < V / 8; v += blockDim.x) st8(lr + v * 8, z);
-    } else {
-      for (int i = threadIdx.x; i < V; i += blockDim.x) lr[i] = __float2bfloat16(0.f);
-    }
+    for (int i = 0; i < 4; ++i) z.v[i] = __floats2bfloat162_rn(0.f, 0.f);
+    for (int v = threadIdx.x; v < nvec; v += blockDim.x) st8(lr + v * 8, z);
+    for (int64_t i = tail0 + threadIdx.x; i < ld; i += blockDim.x) lr[i] = zero;
     if (threadIdx.x == 0) row_loss[row] = 0.f;
     return;
   }
   float m = -CUDART_INF_F, s = 0.f;
-  if (vec) {
-    for (int v = threadIdx.x; v < V / 8; v += blockDim.x) {
-      float f[8];
-      unpack8(ld8(lr + v * 8), f);
-      float lm = f[0];
+  for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
+    float f[8];
+    unpack8(ld8(lr + v * 8), f);
+    float lm = f[0];
 #pragma unroll
-      for (int j = 1; j < 8; ++j) lm = fmaxf(lm, f[j]);
-      if (lm > m) { s *= __expf(m - lm); m = lm; }
+    for (int j = 1; j < 8; ++j) lm = fmaxf(lm, f[j]);
+    if (lm > m) { s *= __expf(m - lm); m = lm; }
 #pragma unroll
-      for (int j = 0; j < 8; ++j) s += __expf(f[j] - m);
-    }
-  } else {
-    for (int i = threadIdx.x; i < V; i += blockDim.x) {
-      const float f = __bfloat162float(lr[i]);
-      if (f > m) { s *= __expf(m - f); m = f; }
-      s += __expf(f - m);
-    }
+    for (int j = 0; j < 8; ++j) s += __expf(f[j] - m);
+  }
+  for (int i = tail0 + threadIdx.x; i < V; i += blockDim.x) {
+    const float f = __bfloat162float(lr[i]);
+    if (f > m) { s *= __expf(m - f); m = f; }
+    s += __expf(f - m);
   }
   const float gm = block_max(m, red);
   s = (m == -CUDART_INF_F) ? 0.f : s * __expf(m - gm);
@@ -416,23 +415,24 @@ __global__ void __launch_bounds__(1024) ce_kernel(__nv_bfloat16* __restrict__ lo
   __syncthreads();  // everyone has read lr[label] before it is overwritten
   if (threadIdx.x == 0) row_loss[row] = lse - picked;
   const float inv_s = 1.f / gs;
-  if (vec) {
-    for (int v = threadIdx.x; v < V / 8; v += blockDim.x) {
-      float f[8];
-      unpack8(ld8(lr + v * 8), f);
+  for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
+    float f[8];
+    unpack8(ld8(lr + v * 8), f);
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        float p = __expf(f[j] - gm) * inv_s;
-        if (v * 8 + j == label) p -= 1.f;
-        f[j] = p * scale;
-      }
-      st8(lr + v * 8, pack8(f));
+    for (int j = 0; j < 8; ++j) {
+      float p = __expf(f[j] - gm) * inv_s;
+      if (v * 8 + j == label) p -= 1.f;
+      f[j] = p * scale;
     }
-  } else {
-    for (int i = threadIdx.x; i < V; i += blockDim.x) {
+    st8(lr + v * 8, pack8(f));
+  }
+  for (int64_t i = tail0 + threadIdx.x; i < ld; i += blockDim.x) {
+    if (i < V) {
       float p = __expf(__bfloat162float(lr[i]) - gm) * inv_s;
       if (i == label) p -= 1.f;
       lr[i] = __float2bfloat16(p * scale);
+    } else {
+      lr[i] = zero;
     }
   }
 }
@@ -702,11 +702,17 @@ int zc_swiglu_bwd(const void* gu, const void* dy, void* dgu, int64_t T, int F, c
   return zc::launch_status();
 }
 
+int zc_ce_fwd_bwd_ld(void* logits, const int64_t* labels, float* row_loss, const float* inv_count, int64_t T, int V,
+                     int64_t ld, int ignore_index, cudaStream_t st) {
+  if (T == 0) return 0;
+  if (V <= 0 || ld < V) return ERR_BAD_ARG;
+  zc::ce_kernel<<<(unsigned)T, 1024, 0, st>>>((bf16*)logits, labels, row_loss, inv_count, V, ld, ignore_index);
+  return zc::launch_status();
+}
+
 int zc_ce_fwd_bwd(void* logits, const int64_t* labels, float* row_loss, const float* inv_count, int64_t T, int V,
                   int ignore_index, cudaStream_t st) {
-  if (T == 0) return 0;
-  zc::ce_kernel<<<(unsigned)T, 1024, 0, st>>>((bf16*)logits, labels, row_loss, inv_count, V, ignore_index);
-  return zc::launch_status();
+  return zc_ce_fwd_bwd_ld(logits, labels, row_loss, inv_count, T, V, V, ignore_index, st);
 }
 
 int zc_quant_int8(const void* x, int64_t n, int dtype, void* out, cudaStream_t st) {

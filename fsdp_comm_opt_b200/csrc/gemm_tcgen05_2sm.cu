@@ -152,6 +152,7 @@ struct Params {
   __nv_bfloat16* C;
   float* partial;      // [tail tiles][split][256][256] fp32, or null when split == 1
   int64_t M, N, K;
+  int64_t ldc;         // elements between rows of C (>= N rounded up to 8: whole 8-column groups are stored)
   int accumulate;
   int group_m;         // tiles are walked in bands of `group_m` m-tiles, n-major inside a band
   int full_tiles;      // tiles computed whole; the remaining tiles are split along K
@@ -373,7 +374,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
       if (w.slice < 0) {
         const int64_t row = (int64_t)w.mi * BM + row_in_tile;
         const int64_t col0 = (int64_t)w.ni * BN;
-        __nv_bfloat16* crow = p.C + row * p.N + col0;
+        __nv_bfloat16* crow = p.C + row * p.ldc + col0;
         const bool row_ok = row < p.M;
 #pragma unroll 1
         for (int c = 0; c < BN; c += 32) {
@@ -457,7 +458,7 @@ __global__ void __launch_bounds__(256) gemm_2sm_fixup_kernel(const Params p, int
       f[0] += x.x; f[1] += x.y; f[2] += x.z; f[3] += x.w;
       f[4] += y.x; f[5] += y.y; f[6] += y.z; f[7] += y.w;
     }
-    uint4* dst = reinterpret_cast<uint4*>(p.C + ((int64_t)mi * BM + row) * p.N + (int64_t)ni * BN + c8 * 8);
+    uint4* dst = reinterpret_cast<uint4*>(p.C + ((int64_t)mi * BM + row) * p.ldc + (int64_t)ni * BN + c8 * 8);
     if (p.accumulate) {
       const uint4 old = *dst;
       const __nv_bfloat162* ob = reinterpret_cast<const __nv_bfloat162*>(&old);
@@ -493,12 +494,13 @@ static EncodeTiledFn encode_fn() {
   }
   return fn;
 }
-// 2-D bf16 row-major tensor [rows][cols]; box = (box_cols inner, box_rows), 128B swizzle
-static bool make_map(CUtensorMap* m, const void* ptr, int64_t rows, int64_t cols, int box_cols, int box_rows) {
+// 2-D bf16 row-major tensor [rows][cols] with rows `ld` elements apart; box = (box_cols inner, box_rows),
+// 128B swizzle.  Elements past `cols` in a row (padding up to ld) are outside the map and read as zeros.
+static bool make_map(CUtensorMap* m, const void* ptr, int64_t rows, int64_t cols, int64_t ld, int box_cols, int box_rows) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return false;
   cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
   cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
   cuuint32_t el[2] = {1, 1};
   const CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, el,
@@ -553,15 +555,21 @@ extern "C" {
 
 int* zc_gemm_status_word();  // gemm_tcgen05.cu: the current device's GEMM status word
 
-// Same contract as zc_gemm_bf16, for M, N and K multiples of 8 (edge tiles are zero-filled on load and
-// masked on store); shares its status word (zc_gemm_status_read_and_clear; code 8 = a bounded wait of
-// this kernel expired).
-int zc_gemm_bf16_2sm(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K, int trans_a, int trans_b,
-                     int accumulate, cudaStream_t st) {
+// Same contract as zc_gemm_bf16 with explicit leading dimensions: lda / ldb / ldc are the distances in
+// elements between consecutive rows of the STORED A, B and C ([M,K] or [K,M]; [N,K] or [K,N]; [M,N]).
+// M, N and K are free; every leading dimension must be a multiple of 8 (16 bytes) and ldc at least N
+// rounded up to 8, because C is stored in whole 8-column groups (the up to 7 padding columns after
+// column N of a row are written too: with zeros, since the operand columns they multiply are outside the
+// tensor map and load as zeros).  Edge tiles are zero-filled on load and masked on store.  Shares zc_gemm_bf16's status word
+// (zc_gemm_status_read_and_clear; code 8 = a bounded wait of this kernel expired).
+int zc_gemm_bf16_2sm_ld(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K, int64_t lda,
+                        int64_t ldb, int64_t ldc, int trans_a, int trans_b, int accumulate, cudaStream_t st) {
   ZC_NVTX_RANGE("zc_gemm_bf16_2sm");
   using namespace zc;
   using namespace zc::g2;
-  if (M <= 0 || N <= 0 || K <= 0 || M % 8 || N % 8 || K % 8) return ERR_UNSUPPORTED;
+  if (M <= 0 || N <= 0 || K <= 0) return ERR_UNSUPPORTED;
+  if (lda % 8 || ldb % 8 || ldc % 8 || ldc < ((N + 7) / 8) * 8) return ERR_UNSUPPORTED;
+  if (lda < (trans_a ? M : K) || ldb < (trans_b ? K : N)) return ERR_BAD_ARG;
   const int64_t m_tiles = (M + BM - 1) / BM, n_tiles = (N + BN - 1) / BN;
   if (m_tiles * n_tiles > (1 << 28)) return ERR_UNSUPPORTED;
   int* status = zc_gemm_status_word();
@@ -577,10 +585,10 @@ int zc_gemm_bf16_2sm(const void* A, const void* B, void* C, int64_t M, int64_t N
   if (a_major == MAJOR_MN && b_major == MAJOR_K) return ERR_UNSUPPORTED;  // no layer GEMM has this form
   CUtensorMap mapA, mapB;
   bool ok;
-  if (a_major == MAJOR_K) ok = make_map(&mapA, A, M, K, BK, BM_CTA);
-  else ok = make_map(&mapA, A, K, M, 64, BK);
-  if (b_major == MAJOR_K) ok = ok && make_map(&mapB, B, N, K, BK, BN_CTA);
-  else ok = ok && make_map(&mapB, B, K, N, 64, BK);
+  if (a_major == MAJOR_K) ok = make_map(&mapA, A, M, K, lda, BK, BM_CTA);
+  else ok = make_map(&mapA, A, K, M, lda, 64, BK);
+  if (b_major == MAJOR_K) ok = ok && make_map(&mapB, B, N, K, ldb, BK, BN_CTA);
+  else ok = ok && make_map(&mapB, B, K, N, ldb, 64, BK);
   if (!ok) return ERR_BAD_ARG;
   const int smem = STAGES * STAGE + 1024;
   DeviceState& ds = g_state[dev];
@@ -597,7 +605,7 @@ int zc_gemm_bf16_2sm(const void* A, const void* B, void* C, int64_t M, int64_t N
     }
   }
   Params p;
-  p.C = (__nv_bfloat16*)C; p.M = M; p.N = N; p.K = K;
+  p.C = (__nv_bfloat16*)C; p.M = M; p.N = N; p.K = K; p.ldc = ldc;
   p.accumulate = accumulate;
   static const int forced_gm = getenv("ZC_GEMM_GROUP_M") ? atoi(getenv("ZC_GEMM_GROUP_M")) : 0;
   static const int forced_split = getenv("ZC_GEMM_SPLIT") ? atoi(getenv("ZC_GEMM_SPLIT")) : -1;
@@ -649,6 +657,13 @@ int zc_gemm_bf16_2sm(const void* A, const void* B, void* C, int64_t M, int64_t N
     rc = launch_status();
   }
   return rc;
+}
+
+// Contiguous operands: M, N and K multiples of 8.
+int zc_gemm_bf16_2sm(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K, int trans_a, int trans_b,
+                     int accumulate, cudaStream_t st) {
+  if (M % 8 || N % 8 || K % 8) return zc::ERR_UNSUPPORTED;
+  return zc_gemm_bf16_2sm_ld(A, B, C, M, N, K, trans_a ? M : K, trans_b ? K : N, N, trans_a, trans_b, accumulate, st);
 }
 
 }  // extern "C"

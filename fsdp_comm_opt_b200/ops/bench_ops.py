@@ -1,6 +1,6 @@
 """Device-timed micro-benchmarks of the hot kernels against their roofline denominators.
 
-    python -m fsdp_comm_opt_b200.ops.bench_ops [--peaks MEASURED_PEAKS.json] [--only gemm,attn,codec,elt]
+    python -m fsdp_comm_opt_b200.ops.bench_ops [--peaks MEASURED_PEAKS.json] [--only gemm,attn,codec,refcodec,recgemm,elt]
         [--case SUBSTRING] [--gemm-backends tcgen05_2sm,tcgen05,cublas] [--iters N] [--warmup W]
 
 ``--case`` keeps the cases whose name contains the substring; with ``--iters 1 --warmup 1`` and one
@@ -146,6 +146,29 @@ def main():
              frac=round((2 * n + b1 + 2 * cnt) / ms_e1 / 1e6 / hbm, 3), frac_of=tag, bytes_per_elem=round(b1 / n, 4))
         emit(kernel="v1_decode_split", elems=n, gbs=round((2 * n + b1) / ms_d1 / 1e6, 1),
              frac=round((2 * n + b1) / ms_d1 / 1e6 / hbm, 3), frac_of=tag)
+    if "recgemm" in only:
+        # decode fused with the consumer GEMM (weight given as v2 records) against decode, then GEMM
+        from .gemm_records import RecordLinear, linear_t_plain
+        M, N, K = 4096, 28672, 4096
+        w = (torch.randn(N, K, device=dev) * 0.02).bfloat16()
+        x = torch.randn(M, K, device=dev).bfloat16()
+        rec, hdr = codec.v2_encode(w.view(-1))
+        y = torch.empty(N, M, dtype=torch.bfloat16, device=dev)
+        ms_g = _time(lambda: gemm.gemm(w, x, False, True, out=y), args.iters, args.warmup, flush=flush)
+        wbuf = torch.empty_like(w)
+        ms_d = _time(lambda: codec.v2_decode(rec, hdr, N * K, wbuf.view(-1)), args.iters, args.warmup, flush=flush)
+        ms_p = _time(lambda: linear_t_plain(x, rec, hdr, N, K, w_buf=wbuf, out=y), args.iters, args.warmup, flush=flush)
+        ref = y.clone()
+        del w
+        for slab_rows, ring in ((512, 3), (1024, 3), (2048, 3), (4096, 2)):
+            rl = RecordLinear(N, K, dev, slab_rows=slab_rows, ring=ring)
+            ms_f = _time(lambda: rl(x, rec, hdr, out=y), args.iters, args.warmup, flush=flush)
+            emit(kernel="gemm_from_records", M=M, N=N, K=K, slab_rows=slab_rows, ring=ring,
+                 ring_mb=round(ring * slab_rows * K * 2 / 2**20, 1), fused_ms=round(ms_f, 4),
+                 decode_then_gemm_ms=round(ms_p, 4), gemm_alone_ms=round(ms_g, 4), decode_alone_ms=round(ms_d, 4),
+                 fused_over_plain=round(ms_p / ms_f, 3), bit_equal=bool(torch.equal(y, ref)),
+                 l2="flushed between launches")
+            del rl
     if "refcodec" in only:
         # the reference's own kernels (built from its sources under baseline/_ref) on the same input,
         # beside this package's v1 and v2 kernels: encode = its K3 + K4 launches, decode = its K9

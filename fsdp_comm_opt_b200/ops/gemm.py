@@ -4,7 +4,7 @@ Backends (``set_backend``):
   ``"tcgen05_2sm"``  the hand-written sm_100a kernel in ``csrc/gemm_tcgen05_2sm.cu``: clusters of two
                  CTAs, ``tcgen05.mma.cta_group::2`` on 256 x 256 tiles with the B operand split between
                  the pair, TMA loads into 128B-swizzled shared memory, TMEM accumulators, persistent
-                 over tiles with a split-K tail.  Any M, N, K that are multiples of 8.
+                 over tiles with a split-K tail.  Any M, N, K; rows a multiple of 8 elements apart.
   ``"tcgen05"``  the one-SM kernel in ``csrc/gemm_tcgen05.cu`` (128 x 256 tiles; M % 128, N % 128,
                  K % 64).
   ``"cublas"``   ``torch.matmul`` (cuBLASLt), kept as the comparison column of the benchmarks.
@@ -34,21 +34,28 @@ def get_backend() -> str:
     return _BACKEND
 
 
+def _rows_ok(t: torch.Tensor) -> bool:
+    """Row-major 2-D operand the kernels can address: unit column stride, rows a multiple of 16 bytes
+    apart (a slice ``buf[:, :n]`` of a padded buffer qualifies), 16-byte aligned base."""
+    return (t.dim() == 2 and t.stride(1) == 1 and t.stride(0) % 8 == 0 and t.stride(0) >= t.shape[1]
+            and t.data_ptr() % 16 == 0)
+
+
+def _pad8(n: int) -> int:
+    return (n + 7) // 8 * 8
+
+
 def _kernel_for(a: torch.Tensor, b: torch.Tensor, M: int, N: int, K: int, trans_a: bool, trans_b: bool):
-    """The C launcher that will run this GEMM, or None for the library."""
+    """Which hand-written kernel will run this GEMM: "2sm", "1sm", or None for the library."""
     if (not a.is_cuda or a.dtype != torch.bfloat16 or b.dtype != torch.bfloat16 or _BACKEND == "cublas"
-            or min(M, N, K) <= 0 or not (a.is_contiguous() and b.is_contiguous())):
+            or min(M, N, K) <= 0 or not (_rows_ok(a) and _rows_ok(b))):
         return None
-    if (a.data_ptr() | b.data_ptr()) & 15:
-        return None
-    two_sm_ok = (M % 8 == 0 and N % 8 == 0 and K % 8 == 0 and M >= 128 and N >= 128 and K >= 64
-                 and not (trans_a and trans_b))
-    one_sm_ok = M % 128 == 0 and N % 128 == 0 and K % 64 == 0
-    lib = _lib.cuda()
+    two_sm_ok = M >= 128 and N >= 128 and K >= 64 and not (trans_a and trans_b)
+    one_sm_ok = (M % 128 == 0 and N % 128 == 0 and K % 64 == 0 and a.is_contiguous() and b.is_contiguous())
     if _BACKEND in ("auto", "tcgen05_2sm") and two_sm_ok:
-        return lib.zc_gemm_bf16_2sm
+        return "2sm"
     if _BACKEND in ("tcgen05", "tcgen05_2sm") and one_sm_ok:
-        return lib.zc_gemm_bf16
+        return "1sm"
     return None
 
 
@@ -57,18 +64,32 @@ def gemm(a: torch.Tensor, b: torch.Tensor, trans_a: bool, trans_b: bool,
     """C[M,N] (+)= op(A) @ op(B) for row-major 2-D bf16 tensors.
 
     op(A) is A ``[M,K]`` (or A^T of a stored ``[K,M]`` when ``trans_a``); op(B) is B ``[K,N]`` (or
-    B^T of a stored ``[N,K]`` when ``trans_b``).
+    B^T of a stored ``[N,K]`` when ``trans_b``).  Operands and ``out`` may be row slices or column
+    slices of wider buffers as long as rows stay a multiple of 8 elements apart.  When N is not a
+    multiple of 8 (GPT-2's vocabulary of 50257) the result allocated here is a ``[:, :N]`` view of a
+    buffer whose rows are padded to the next multiple of 8, so that the next GEMM and the loss kernel
+    can read it with aligned rows; its padding columns hold zeros.
     """
     M, K = (a.shape[1], a.shape[0]) if trans_a else (a.shape[0], a.shape[1])
     N = b.shape[0] if trans_b else b.shape[1]
-    fn = _kernel_for(a, b, M, N, K, trans_a, trans_b)
-    if fn is not None and (out is None or (out.is_contiguous() and out.data_ptr() % 16 == 0)):
+    kind = _kernel_for(a, b, M, N, K, trans_a, trans_b)
+    if kind is not None and out is not None and not (_rows_ok(out) and out.dtype == torch.bfloat16
+                                                     and (kind == "1sm" and out.is_contiguous()
+                                                          or kind == "2sm" and out.stride(0) >= _pad8(N))):
+        kind = None
+    if kind is not None:
         if out is None:
-            out = torch.empty(M, N, dtype=a.dtype, device=a.device)
+            out = torch.empty(M, _pad8(N), dtype=a.dtype, device=a.device)[:, :N]
             accumulate = False
-        _lib.check(fn(
-            a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, int(trans_a), int(trans_b),
-            int(accumulate), _lib.stream_ptr(a.device)), "zc_gemm_bf16")
+        lib = _lib.cuda()
+        if kind == "2sm":
+            _lib.check(lib.zc_gemm_bf16_2sm_ld(
+                a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, a.stride(0), b.stride(0), out.stride(0),
+                int(trans_a), int(trans_b), int(accumulate), _lib.stream_ptr(a.device)), "zc_gemm_bf16_2sm")
+        else:
+            _lib.check(lib.zc_gemm_bf16(
+                a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, int(trans_a), int(trans_b),
+                int(accumulate), _lib.stream_ptr(a.device)), "zc_gemm_bf16")
         return out
     A = a.t() if trans_a else a
     B = b.t() if trans_b else b
@@ -100,7 +121,7 @@ class _Linear(torch.autograd.Function):
         w = ctx.w
         x2 = x.reshape(-1, x.shape[-1])
         dy2 = dy.reshape(-1, dy.shape[-1])
-        if not dy2.is_contiguous():
+        if not (dy2.is_contiguous() or _rows_ok(dy2)):
             dy2 = dy2.contiguous()
         dx = dw = None
         if ctx.needs_input_grad[0]:

@@ -39,13 +39,15 @@ class _CrossEntropy(torch.autograd.Function):
         valid = (labels != ignore_index)
         count = valid.sum().clamp_min(1).to(torch.float32)
         if logits.is_cuda:
-            if logits.dtype != torch.bfloat16 or not logits.is_contiguous():
-                raise TypeError("CUDA cross_entropy expects contiguous bf16 logits")
+            if logits.dtype != torch.bfloat16 or logits.stride(1) != 1 or logits.stride(0) < V:
+                raise TypeError("CUDA cross_entropy expects bf16 logits with unit column stride")
             inv = (1.0 / count).reshape(1).contiguous()
             row_loss = torch.empty(T, dtype=torch.float32, device=logits.device)
             lab = labels.to(torch.int64).contiguous()
-            _lib.check(_lib.cuda().zc_ce_fwd_bwd(
-                logits.data_ptr(), lab.data_ptr(), row_loss.data_ptr(), inv.data_ptr(), T, V,
+            # rows may be padded (the GEMM's [:, :V] view of aligned rows when V % 8 != 0): the kernel
+            # takes the row stride and zeroes the padding
+            _lib.check(_lib.cuda().zc_ce_fwd_bwd_ld(
+                logits.data_ptr(), lab.data_ptr(), row_loss.data_ptr(), inv.data_ptr(), T, V, logits.stride(0),
                 int(ignore_index), _lib.stream_ptr(logits.device)), "zc_ce_fwd_bwd")
             ctx.grad_logits = logits.detach()  # the buffer now holds d(loss)/d(logits)
             return row_loss.sum() * inv[0]

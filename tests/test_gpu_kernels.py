@@ -434,6 +434,67 @@ def test_tcgen05_gemm_three_forms(backend, M, N, K):
         gemm.set_backend("auto")
 
 
+def test_gemm_with_leading_dimensions_and_odd_sizes():
+    """Operands and results that are slices of wider buffers, and M / N / K that are not multiples of 8
+    (GPT-2's vocabulary): the two-SM kernel takes row strides, zero-fills what lies outside a slice and
+    hands back a [:, :N] view of aligned rows whose padding columns are zero."""
+    from fsdp_comm_opt_b200.ops import gemm
+
+    torch.manual_seed(11)
+    M, N, K = 300, 1001, 520
+    xb = (torch.randn(M, K + 8, device=DEV) * 0.5).bfloat16()
+    x = xb[:, :K - 5]                                # K = 515, rows 528 elements apart
+    Ke = K - 5
+    w = (torch.randn(N, K, device=DEV) * 0.5).bfloat16()[:, :Ke]
+    before = _lib.launch_count()
+    y = gemm.gemm(x, w, False, True)                 # [300, 1001] view of [300, 1008]
+    assert y.shape == (M, N) and y.stride(0) == 1008
+    dx = gemm.gemm(y, w, False, False)               # dgrad form: K = 1001, A strided, B rows = K
+    dw = gemm.gemm(y, x, True, False)                # wgrad form: M = 1001 rows out, both operands strided
+    assert _lib.launch_count() - before == 3, "the hand-written kernel must have been taken"
+    torch.cuda.synchronize()
+    assert _lib.cuda().zc_gemm_status_read_and_clear() == 0
+    yf = y.float()
+    for got, ref in ((y, x.float() @ w.float().t()), (dx, yf @ w.float()), (dw, yf.t() @ x.float())):
+        assert got.shape == ref.shape
+        tol = 2e-2 * ref.abs().max().item()
+        assert (got.float() - ref).abs().max().item() <= tol, (got.float() - ref).abs().max().item()
+    pad = torch.as_strided(y, (M, 1008 - N), (1008, 1), y.storage_offset() + N)
+    assert int(pad.float().abs().max().item()) == 0
+    # a column block of a wider result, accumulated into
+    big = torch.zeros(M, 2048, dtype=torch.bfloat16, device=DEV)
+    gemm.gemm(x, w, False, True, out=big[:, 1024:1024 + N])
+    gemm.gemm(x, w, False, True, out=big[:, 1024:1024 + N], accumulate=True)
+    torch.cuda.synchronize()
+    assert torch.allclose(big[:, 1024:1024 + N].float(), 2 * yf, atol=0.1, rtol=2e-2)
+    assert float(big[:, :1024].float().abs().max()) == 0.0
+
+
+def test_linear_and_loss_over_a_vocabulary_that_is_not_a_multiple_of_8():
+    """lm_head + cross-entropy at an odd vocabulary run on the hand-written GEMM and the strided loss
+    kernel; gradients against fp32 PyTorch."""
+    from fsdp_comm_opt_b200.ops import gemm
+
+    torch.manual_seed(12)
+    T, D, V = 256, 192, 1001
+    x = (torch.randn(T, D, device=DEV) * 0.5).bfloat16().requires_grad_()
+    w = (torch.randn(V, D, device=DEV) * 0.1).bfloat16().requires_grad_()
+    labels = torch.randint(0, V, (T,), device=DEV)
+    labels[7] = -100
+    before = _lib.launch_count()
+    out = loss.cross_entropy(gemm.linear(x, w), labels)
+    out.backward()
+    torch.cuda.synchronize()
+    assert _lib.launch_count() - before >= 4        # three GEMMs and the loss kernel
+    xf, wf = x.detach().float().requires_grad_(), w.detach().float().requires_grad_()
+    ref = F.cross_entropy((xf @ wf.t()).bfloat16().float(), labels, ignore_index=-100)
+    ref2 = F.cross_entropy(xf @ wf.t(), labels, ignore_index=-100)
+    ref2.backward()
+    assert abs(out.item() - ref.item()) < 5e-3
+    assert torch.allclose(x.grad.float(), xf.grad, atol=2e-2 * float(xf.grad.abs().max()), rtol=5e-2)
+    assert torch.allclose(w.grad.float(), wf.grad, atol=2e-2 * float(wf.grad.abs().max()), rtol=5e-2)
+
+
 def test_linear_autograd_on_tcgen05_matches_cublas():
     from fsdp_comm_opt_b200.ops import gemm
 
@@ -536,3 +597,23 @@ def test_adamw_in_two_launches_equals_one():
     assert len(called) == 3 and ob.kernel_launches == 6 and oa.kernel_launches == 3
     assert torch.equal(a.detach(), b.detach())
     assert torch.equal(oa.state[a]["exp_avg_sq"], ob.state[b]["exp_avg_sq"])
+
+
+@pytest.mark.parametrize("N,K,M,slab_rows,ring", [(1024, 512, 256, 256, 3), (2048, 1024, 384, 512, 2), (512, 256, 128, 512, 2)])
+def test_gemm_from_codec_records_matches_fp32_matmul(N, K, M, slab_rows, ring):
+    """Decode fused with the consumer GEMM: the weight is given as v2 records, decoded slab by slab
+    into an L2-resident ring beside the GEMM; same bits as decode-then-GEMM, close to fp32 matmul."""
+    from fsdp_comm_opt_b200.ops.gemm_records import RecordLinear, linear_t_plain
+    g = torch.Generator().manual_seed(N + K)
+    w = (torch.randn(N, K, generator=g) * 0.02).bfloat16().cuda()
+    w[::7, ::5] = 300.0                                   # escapes in most chunks
+    x = torch.randn(M, K, generator=g).bfloat16().cuda()
+    rec, hdr = codec.v2_encode(w.view(-1))
+    rl = RecordLinear(N, K, "cuda", slab_rows=slab_rows, ring=ring)
+    y1 = rl(x, rec, hdr).clone()
+    y2 = rl(x, rec, hdr)                                  # second call runs over the first call's ring
+    plain = linear_t_plain(x, rec, hdr, N, K)
+    torch.cuda.synchronize()
+    ref = w.float() @ x.float().t()
+    assert torch.equal(y1, y2) and torch.equal(y1, plain)
+    assert torch.allclose(y1.float(), ref, rtol=2e-2, atol=2e-2 * float(ref.abs().max()))

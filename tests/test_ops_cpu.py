@@ -180,3 +180,18 @@ def test_gpt2_ops_cpu_paths_match_torch():
     zr.backward(gz)
     for got, want in ((z, zr), (u.grad, u2.grad), (c.grad, c2.grad)):
         assert torch.allclose(got, want, atol=1e-5, rtol=1e-4)
+
+
+def test_gemm_from_codec_records_cpu():
+    from fsdp_comm_opt_b200.ops import codec
+    from fsdp_comm_opt_b200.ops.gemm_records import RecordLinear, linear_t_plain
+    N, K, M = 512, 256, 48
+    g = torch.Generator().manual_seed(5)
+    w = (torch.randn(N, K, generator=g) * 0.02).bfloat16()
+    x = torch.randn(M, K, generator=g).bfloat16()
+    rec, hdr = codec.v2_encode(w.view(-1))
+    y = RecordLinear(N, K, "cpu", slab_rows=128, ring=2)(x, rec, hdr)
+    ref = (w.float() @ x.float().t()).to(torch.bfloat16)
+    assert torch.equal(y, ref) and torch.equal(linear_t_plain(x, rec, hdr, N, K), ref)
+    with pytest.raises(ValueError):
+        RecordLinear(N, K, "cpu", slab_rows=100)
