@@ -68,6 +68,6 @@ def declare(lib) -> None:
     # fused collectives
     from ctypes import c_double, c_uint
 
-    _sig(lib, "zc_symm_all_gather", P, P, P, P, P, L, I, I, L, c_uint, I, I, c_double, P)
+    _sig(lib, "zc_symm_all_gather", P, P, P, P, P, L, I, I, L, c_uint, I, I, c_double, I, P)
     _sig(lib, "zc_symm_all_gather_int8", P, P, P, P, P, L, I, I, L, c_uint, I, I, c_double, P)
-    _sig(lib, "zc_symm_reduce_scatter", P, P, P, P, P, L, I, I, L, c_uint, I, I, F, I, I, c_double, P)
+    _sig(lib, "zc_symm_reduce_scatter", P, P, P, P, P, L, I, I, L, c_uint, I, I, F, I, I, c_double, I, P)

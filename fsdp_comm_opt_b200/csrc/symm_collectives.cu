@@ -134,6 +134,24 @@ __device__ __forceinline__ void warp_copy16_mc(uint8_t* mc_dst, const uint8_t* s
   for (int i = lane; i < nv; i += 32) mc_st128(mc_dst + 16 * i, reinterpret_cast<const uint4*>(src)[i]);
 }
 
+// Verbatim wire: a record is the chunk's 2048 bf16 bytes, lane l's 32 elements at byte l * 64.  Same
+// slots, flags and parity protocol as the compressed records, no header words and no codec work: for
+// links with bandwidth to spare, where the codec's instructions cost the kernels running beside the
+// collective more than the bytes saved.  Chosen per call; every rank must make the same choice.
+__device__ __forceinline__ void store_verbatim(uint8_t* rec, int lane, const LaneIn& li) {
+  uint4* p = reinterpret_cast<uint4*>(rec + lane * 64);
+#pragma unroll
+  for (int k = 0; k < 4; ++k) p[k] = make_uint4(li.w[4 * k], li.w[4 * k + 1], li.w[4 * k + 2], li.w[4 * k + 3]);
+}
+__device__ __forceinline__ void load_verbatim(const uint8_t* rec, int lane, LaneIn& li) {
+  const uint4* p = reinterpret_cast<const uint4*>(rec + lane * 64);
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const uint4 v = __ldcg(p + k);
+    li.w[4 * k] = v.x; li.w[4 * k + 1] = v.y; li.w[4 * k + 2] = v.z; li.w[4 * k + 3] = v.w;
+  }
+}
+
 struct AgArgs {
   const uint16_t* in;     // this rank's shard, n elements
   uint16_t* out;          // world * n elements
@@ -144,6 +162,7 @@ struct AgArgs {
   uint32_t seq;
   int push_ctas;
   int gc;                 // chunks per group in this call: 8, 16, 32 or 64
+  int verbatim;           // 1: records are the chunks' bf16 bytes as they are (no codec work, 2048 B per chunk)
   unsigned long long timeout_ns;
   SymmLayout L;
 };
@@ -158,6 +177,7 @@ __device__ __forceinline__ bool warp_wait_flag(const uint32_t* fl, uint32_t want
   return ok != 0;
 }
 
+template <bool VERBATIM>
 __global__ void __launch_bounds__(256) symm_all_gather_kernel(const AgArgs a) {
   // pushers: the record's tail (planes, escapes, raw exponents), its first 1024 bytes go out straight
   // from registers; decoders: escape staging.  8 KB, so that two collective CTAs fit beside a GEMM CTA.
@@ -197,6 +217,21 @@ __global__ void __launch_bounds__(256) symm_all_gather_kernel(const AgArgs a) {
         LaneIn li;
         load_lane(a.in + e0, a.n - e0, in_al, li);
         if (copy_own) store_lane(own + e0, a.n - e0, own_al, li);
+        if constexpr (VERBATIM) {
+          if (!ZC_SLOT_OK(L, c, V2_SLOT_BYTES, a.local, L.rank)) continue;
+          if (a.mc) {
+            uint8_t* rec = slot_ptr(a.mc, L, parity, L.rank) + L.hdr_bytes + c * V2_SLOT_BYTES + lane * 64;
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+              mc_st128(rec + 16 * k, make_uint4(li.w[4 * k], li.w[4 * k + 1], li.w[4 * k + 2], li.w[4 * k + 3]));
+          } else {
+            for (int q = 0; q < L.world; ++q)
+              if (q != L.rank)
+                store_verbatim(slot_ptr(a.peers[q], L, parity, L.rank) + L.hdr_bytes + c * V2_SLOT_BYTES, lane, li);
+          }
+          if (lane == 0) pushed += (unsigned long long)V2_SLOT_BYTES * (L.world - 1);
+          continue;
+        }
         LaneSplit s;
         split_lane(li, s);
         const uint32_t hdr = v2_encode_chunk_hint<false>(s, srec[warp] - 1024, lane, hint, hint_esc);
@@ -259,6 +294,22 @@ __global__ void __launch_bounds__(256) symm_all_gather_kernel(const AgArgs a) {
     const uint8_t* recs = slot + L.hdr_bytes + c0 * V2_SLOT_BYTES;
     uint16_t* dst = a.out + (long long)src * a.n;
     const bool al = (reinterpret_cast<uintptr_t>(dst) & 15) == 0;
+    if constexpr (VERBATIM) {
+      // a copy: all loads of the slice first, then the stores
+      for (int k0 = 0; k0 < cnt; k0 += 4) {
+        LaneIn v[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          if (k0 + k < cnt) load_verbatim(recs + (long long)(k0 + k) * V2_SLOT_BYTES, lane, v[k]);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          if (k0 + k >= cnt) continue;
+          const long long e0 = (c0 + k0 + k) * V2_CHUNK_ELEMS + lane * 32;
+          store_lane(dst + e0, a.n - e0, al, v[k]);
+        }
+      }
+      continue;
+    }
     // the item's eight headers in one load, then record k+1 in flight while record k is decoded
     // (two records ahead was measured and is slower: with eight warps per SM the decoder is bound by
     // its own instruction stream, and the extra registers cost a resident CTA)
@@ -305,6 +356,7 @@ struct RsArgs {
   uint32_t seq;
   int push_ctas, in_fp32, out_fp32;
   int gc;                 // chunks per group in this call: 8, 16, 32 or 64
+  int verbatim;           // 1: records are the chunks' bf16 bytes as they are
   float scale;
   unsigned long long timeout_ns;
   SymmLayout L;
@@ -341,6 +393,32 @@ __device__ __forceinline__ void load_lane_f32(const void* base, bool fp32, long 
   }
 }
 
+// the 32 sums of one lane, times `scale`, to the fp32 or bf16 output
+__device__ __forceinline__ void store_lane_scaled(void* out, int out_fp32, long long e0, long long valid, float scale,
+                                                  const float (&acc)[32]) {
+  if (out_fp32) {
+    float* dst = reinterpret_cast<float*>(out) + e0;
+    if (valid >= 32 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        reinterpret_cast<float4*>(dst)[j] = make_float4(acc[4 * j] * scale, acc[4 * j + 1] * scale,
+                                                        acc[4 * j + 2] * scale, acc[4 * j + 3] * scale);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (j < valid) dst[j] = acc[j] * scale;
+    }
+  } else {
+    LaneIn o;
+#pragma unroll
+    for (int j = 0; j < 16; ++j)
+      o.w[j] = f_to_bf16_bits(acc[2 * j] * scale) | (f_to_bf16_bits(acc[2 * j + 1] * scale) << 16);
+    uint16_t* dst = reinterpret_cast<uint16_t*>(out) + e0;
+    store_lane(dst, valid, (reinterpret_cast<uintptr_t>(dst) & 15) == 0, o);
+  }
+}
+
+template <bool VERBATIM>
 __global__ void __launch_bounds__(256, 2) symm_reduce_scatter_kernel(const RsArgs a) {
   // pushers: the record's tail (planes, escapes, raw exponents), its first 1024 bytes go out straight
   // from registers; decoders: escape staging.  8 KB, so that two collective CTAs fit beside a GEMM CTA.
@@ -400,6 +478,12 @@ __global__ void __launch_bounds__(256, 2) symm_reduce_scatter_kernel(const RsArg
 #pragma unroll
           for (int k = 0; k < 16; ++k) li.w[k] = f_to_bf16_bits(v[2 * k]) | (f_to_bf16_bits(v[2 * k + 1]) << 16);
         }
+        if constexpr (VERBATIM) {
+          if (!ZC_SLOT_OK(L, c, V2_SLOT_BYTES, a.local, q)) continue;
+          store_verbatim(slot + L.hdr_bytes + c * V2_SLOT_BYTES, lane, li);
+          if (lane == 0) pushed += (unsigned long long)V2_SLOT_BYTES;
+          continue;
+        }
         LaneSplit s;
         split_lane(li, s);
         const uint32_t hdr = v2_encode_chunk_hint<false>(s, srec[warp] - 1024, lane, hint, hint_esc);
@@ -450,6 +534,28 @@ __global__ void __launch_bounds__(256, 2) symm_reduce_scatter_kernel(const RsArg
       if (lane == 0) *okp = 0;
       break;
     }
+    if constexpr (VERBATIM) {
+      for (int k = 0; k < cnt; ++k) {
+        const long long c = c0 + k;
+        const long long e0 = c * V2_CHUNK_ELEMS + lane * 32;
+        const long long valid = a.shard - e0;
+        // fixed order (this rank's own row, then the sources by rank): a deterministic sum
+        float acc[32];
+        load_lane_f32(a.in, a.in_fp32, (long long)L.rank * a.shard + e0, valid, acc);
+        for (int p = 0; p < L.world; ++p) {
+          if (p == L.rank) continue;
+          LaneIn o;
+          load_verbatim(slot_ptr(a.local, L, parity, p) + L.hdr_bytes + c * V2_SLOT_BYTES, lane, o);
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            acc[2 * j] += bf16_bits_to_f(o.w[j] & 0xFFFFu);
+            acc[2 * j + 1] += bf16_bits_to_f(o.w[j] >> 16);
+          }
+        }
+        if (valid > 0) store_lane_scaled(a.out, a.out_fp32, e0, valid, a.scale, acc);
+      }
+      continue;
+    }
     const uint8_t* myslot = slot_ptr(a.local, L, parity, is_src ? lane : p0);
     uint32_t myhdr = is_src ? __ldcg(reinterpret_cast<const uint32_t*>(myslot) + c0) : 0u;
     RecRegs cur, nxt;
@@ -488,26 +594,7 @@ __global__ void __launch_bounds__(256, 2) symm_reduce_scatter_kernel(const RsArg
       }
       myhdr = nexthdr;
       if (valid <= 0) continue;
-      if (a.out_fp32) {
-        float* dst = reinterpret_cast<float*>(a.out) + e0;
-        if (valid >= 32 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
-#pragma unroll
-          for (int j = 0; j < 8; ++j)
-            reinterpret_cast<float4*>(dst)[j] = make_float4(acc[4 * j] * a.scale, acc[4 * j + 1] * a.scale,
-                                                            acc[4 * j + 2] * a.scale, acc[4 * j + 3] * a.scale);
-        } else {
-#pragma unroll
-          for (int j = 0; j < 32; ++j)
-            if (j < valid) dst[j] = acc[j] * a.scale;
-        }
-      } else {
-        LaneIn o;
-#pragma unroll
-        for (int j = 0; j < 16; ++j)
-          o.w[j] = f_to_bf16_bits(acc[2 * j] * a.scale) | (f_to_bf16_bits(acc[2 * j + 1] * a.scale) << 16);
-        uint16_t* dst = reinterpret_cast<uint16_t*>(a.out) + e0;
-        store_lane(dst, valid, (reinterpret_cast<uintptr_t>(dst) & 15) == 0, o);
-      }
+      store_lane_scaled(a.out, a.out_fp32, e0, valid, a.scale, acc);
     }
   }
   __syncthreads();
@@ -713,9 +800,10 @@ long long zc_symm_buffer_bytes(int world, long long nc_max) {
 
 // in: n bf16 elements; out: world*n; peers: device array of `world` buffer pointers
 // mc: multicast mapping of the symmetric buffer (NVSwitch), or null to push with per-peer stores
+// verbatim: 0 = v2 records (compressed), 1 = the bf16 bytes as they are
 int zc_symm_all_gather(const void* in, void* out, void* const* peers, void* local, void* mc, long long n, int rank,
                        int world, long long nc_max, unsigned seq, int push_ctas, int dec_ctas, double timeout_s,
-                       cudaStream_t st) {
+                       int verbatim, cudaStream_t st) {
   ZC_NVTX_RANGE("zc_symm_all_gather");
   using namespace zc;
   const long long nc = (n + V2_CHUNK_ELEMS - 1) / V2_CHUNK_ELEMS;
@@ -726,7 +814,7 @@ int zc_symm_all_gather(const void* in, void* out, void* const* peers, void* loca
     return ERR_BAD_ARG;
   AgArgs a;
   a.in = (const uint16_t*)in; a.out = (uint16_t*)out; a.peers = (uint8_t* const*)peers; a.local = (uint8_t*)local;
-  a.mc = (uint8_t*)mc; a.n = n; a.seq = seq;
+  a.mc = (uint8_t*)mc; a.n = n; a.seq = seq; a.verbatim = verbatim ? 1 : 0;
   a.timeout_ns = (unsigned long long)(timeout_s * 1e9);
   a.L = make_layout(world, rank, nc_max);
   a.gc = pick_group_chunks(nc, sm_count(), a.L.max_groups);
@@ -735,14 +823,15 @@ int zc_symm_all_gather(const void* in, void* out, void* const* peers, void* loca
   a.push_ctas = (int)std::min<long long>(push_ctas, ngroups);
   const long long dec_items = ngroups * (world - 1) * (a.gc / 8);
   const int dec = (int)std::min<long long>(dec_ctas, (dec_items + 7) / 8);
-  symm_all_gather_kernel<<<a.push_ctas + dec, 256, 0, st>>>(a);
+  if (a.verbatim) symm_all_gather_kernel<true><<<a.push_ctas + dec, 256, 0, st>>>(a);
+  else symm_all_gather_kernel<false><<<a.push_ctas + dec, 256, 0, st>>>(a);
   return launch_status();
 }
 
 int zc_symm_reduce_scatter(const void* in, void* out, void* residual, void* const* peers, void* local,
                            long long shard, int rank, int world, long long nc_max, unsigned seq, int in_fp32,
                            int out_fp32, float scale, int push_ctas, int dec_ctas, double timeout_s,
-                           cudaStream_t st) {
+                           int verbatim, cudaStream_t st) {
   ZC_NVTX_RANGE("zc_symm_reduce_scatter");
   using namespace zc;
   const long long nc = (shard + V2_CHUNK_ELEMS - 1) / V2_CHUNK_ELEMS;
@@ -751,7 +840,7 @@ int zc_symm_reduce_scatter(const void* in, void* out, void* residual, void* cons
   RsArgs a;
   a.in = in; a.out = out; a.residual = (uint16_t*)residual; a.peers = (uint8_t* const*)peers;
   a.local = (uint8_t*)local; a.shard = shard; a.seq = seq; a.in_fp32 = in_fp32;
-  a.out_fp32 = out_fp32; a.scale = scale;
+  a.out_fp32 = out_fp32; a.scale = scale; a.verbatim = verbatim ? 1 : 0;
   a.timeout_ns = (unsigned long long)(timeout_s * 1e9);
   a.L = make_layout(world, rank, nc_max);
   // a pusher item is (destination, group): world - 1 times as many items as groups
@@ -761,7 +850,8 @@ int zc_symm_reduce_scatter(const void* in, void* out, void* residual, void* cons
   a.push_ctas = (int)std::min<long long>(push_ctas, ngroups * (world - 1));
   const long long dec_items = ngroups * (a.gc / 8);
   const int dec = (int)std::min<long long>(dec_ctas, (dec_items + 7) / 8);
-  symm_reduce_scatter_kernel<<<a.push_ctas + dec, 256, 0, st>>>(a);
+  if (a.verbatim) symm_reduce_scatter_kernel<true><<<a.push_ctas + dec, 256, 0, st>>>(a);
+  else symm_reduce_scatter_kernel<false><<<a.push_ctas + dec, 256, 0, st>>>(a);
   return launch_status();
 }
 
@@ -776,7 +866,7 @@ int zc_symm_all_gather_int8(const void* in, void* out, void* const* peers, void*
   if (world < 2 || world > 64 || nc > nc_max || nc == 0 || push_ctas < 1 || dec_ctas < 1) return ERR_BAD_ARG;
   AgArgs a;
   a.in = (const uint16_t*)in; a.out = (uint16_t*)out; a.peers = (uint8_t* const*)peers; a.local = (uint8_t*)local;
-  a.mc = (uint8_t*)mc; a.n = n; a.seq = seq; a.push_ctas = push_ctas; a.gc = GROUP_CHUNKS;
+  a.mc = (uint8_t*)mc; a.n = n; a.seq = seq; a.push_ctas = push_ctas; a.gc = GROUP_CHUNKS; a.verbatim = 0;
   a.timeout_ns = (unsigned long long)(timeout_s * 1e9);
   a.L = make_layout(world, rank, nc_max);
   uint32_t* word = reinterpret_cast<uint32_t*>(local) + CW_ABSMAX;

@@ -40,6 +40,7 @@ class EngineConfig:
     forward_prefetch_distance: int = 1
     transport: str = "auto"
     codec_version: str = "auto"
+    wire: str = "compressed"        # "compressed" | "verbatim": what the fused collectives put on the wire
     seed: int = 0
     sharding: str = "flat"          # "flat" | "fsdp2"
     cpu_offload: bool = False       # fsdp2 only
@@ -56,7 +57,7 @@ def build_sharded(cfg: EngineConfig, device: torch.device):
     plan = FSDPPlan(quantize=cfg.quantize, zip_ccl=cfg.zip_ccl, compress_rs=cfg.compress_rs,
                     cpu_offload=cfg.cpu_offload, forward_prefetch_distance=cfg.forward_prefetch_distance,
                     transport=cfg.transport, codec_version=cfg.codec_version, act_ckpt=cfg.act_ckpt,
-                    error_feedback=cfg.error_feedback)
+                    error_feedback=cfg.error_feedback, wire=cfg.wire)
     if cfg.sharding == "fsdp2":
         with torch.device("meta"):
             model = build_model(mcfg).to(cfg.master_dtype)

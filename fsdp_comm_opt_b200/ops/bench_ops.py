@@ -1,6 +1,6 @@
 """Device-timed micro-benchmarks of the hot kernels against their roofline denominators.
 
-    python -m fsdp_comm_opt_b200.ops.bench_ops [--peaks MEASURED_PEAKS.json] [--only gemm,attn,codec,refcodec,recgemm,elt]
+    python -m fsdp_comm_opt_b200.ops.bench_ops [--peaks MEASURED_PEAKS.json] [--only gemm,attn,codec,refcodec,recgemm,beside,elt]
         [--case SUBSTRING] [--gemm-backends tcgen05_2sm,tcgen05,cublas] [--iters N] [--warmup W]
 
 ``--case`` keeps the cases whose name contains the substring; with ``--iters 1 --warmup 1`` and one
@@ -166,9 +166,76 @@ def main():
             emit(kernel="gemm_from_records", M=M, N=N, K=K, slab_rows=slab_rows, ring=ring,
                  ring_mb=round(ring * slab_rows * K * 2 / 2**20, 1), fused_ms=round(ms_f, 4),
                  decode_then_gemm_ms=round(ms_p, 4), gemm_alone_ms=round(ms_g, 4), decode_alone_ms=round(ms_d, 4),
-                 fused_over_plain=round(ms_p / ms_f, 3), bit_equal=bool(torch.equal(y, ref)),
+                 fused_over_plain=round(ms_p / ms_f, 3),
+                 max_abs_diff_vs_plain=float((y.float() - ref.float()).abs().max().item()),
                  l2="flushed between launches")
             del rl
+    if "beside" in only:
+        # What a GEMM loop pays for work that runs beside it on a high-priority side stream (the
+        # position of the collectives during training): decode, encode, or a plain device copy of the
+        # same kind of buffer.  hidden = (t_gemm + t_side - t_both) / min(t_gemm, t_side): 1 if the
+        # side work is free, 0 if the two simply add up.
+        M, N, K = 4096, 14336, 4096
+        x = (torch.randn(M, K, device=dev) * 0.05).bfloat16()
+        w = (torch.randn(N, K, device=dev) * 0.02).bfloat16()
+        y = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
+        n = 1 << 27
+        src = (torch.randn(n, device=dev) * 0.02).bfloat16()
+        rec, hdr = codec.v2_encode(src)
+        out, out2 = torch.empty_like(src), torch.empty_like(src)
+        lib = _lib.cuda()
+        side = torch.cuda.Stream(priority=-1)
+        main_s = torch.cuda.current_stream()
+        nsm = torch.cuda.get_device_properties(dev).multi_processor_count
+
+        def gemms():
+            for _ in range(24):
+                gemm.gemm(x, w, False, True, out=y)
+
+        def both(main_fn, side_fn):
+            t = None
+            for _ in range(max(3, args.warmup)):
+                torch.cuda.synchronize()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                es = torch.cuda.Event()
+                e0.record(main_s)
+                side.wait_event(e0)
+                if side_fn is not None:
+                    with torch.cuda.stream(side):
+                        side_fn()
+                es.record(side)
+                if main_fn is not None:
+                    main_fn()
+                main_s.wait_event(es)
+                e1.record(main_s)
+                torch.cuda.synchronize()
+                t = e0.elapsed_time(e1)
+            return t
+
+        def rep(fn, r):
+            def f():
+                for _ in range(r):
+                    fn()
+            return f
+
+        kinds = {
+            "v2_decode, one CTA per SM": (lambda: lib.zc_v2_decode_ctas(rec.data_ptr(), hdr.data_ptr(), n, out.data_ptr(), nsm,
+                                                                        _lib.stream_ptr()), n),
+            "v2_decode, 64 CTAs": (lambda: lib.zc_v2_decode_ctas(rec.data_ptr(), hdr.data_ptr(), n, out.data_ptr(), 64,
+                                                                 _lib.stream_ptr()), n),
+            "v2_encode": (lambda: codec.v2_encode(src, rec, hdr), n),
+            "device copy (bf16)": (lambda: out2.copy_(src), n),
+        }
+        t_g = both(gemms, None)
+        for name, (fn, elems) in kinds.items():
+            t1 = both(None, fn)
+            r = max(1, int(round(0.8 * t_g / t1)))
+            t_s = both(None, rep(fn, r))
+            t_b = both(gemms, rep(fn, r))
+            emit(kernel="gemm_beside", side=name, gemm_loop_ms=round(t_g, 3), side_alone_ms=round(t_s, 3),
+                 together_ms=round(t_b, 3), hidden=round((t_g + t_s - t_b) / min(t_g, t_s), 3),
+                 gemm_ms_paid_per_g_elem=round((t_b - t_g) / (r * elems / 1e9), 3) if t_b > t_g else 0.0,
+                 side_g_elems=round(r * elems / 1e9, 2))
     if "refcodec" in only:
         # the reference's own kernels (built from its sources under baseline/_ref) on the same input,
         # beside this package's v1 and v2 kernels: encode = its K3 + K4 launches, decode = its K9

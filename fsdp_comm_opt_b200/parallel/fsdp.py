@@ -30,6 +30,7 @@ class FSDPPlan:
     reduce_dtype: torch.dtype = torch.float32
     transport: str = "auto"
     codec_version: str = "auto"
+    wire: str = "compressed"         # "compressed" | "verbatim" (fused transport: raw bf16 bytes, no codec work)
     error_feedback: bool = True
     act_ckpt: bool = False
     mesh: Optional[object] = None
@@ -40,14 +41,14 @@ class FSDPPlan:
 def _install_hooks(m: FSDPModule, plan: FSDPPlan) -> None:
     if plan.quantize:
         if plan.zip_ccl:
-            hook = ZipCCLAllGather(codec_version=plan.codec_version, transport=plan.transport)
+            hook = ZipCCLAllGather(codec_version=plan.codec_version, transport=plan.transport, wire=plan.wire)
         else:
             hook = QuantizedAllGather(transport=plan.transport)
         m.set_custom_all_gather(hook)
         plan.ag_hooks.append(hook)
     if plan.compress_rs:
         rs = ZipCCLReduceScatter(error_feedback=plan.error_feedback, reduce_dtype=plan.reduce_dtype,
-                                 transport=plan.transport)
+                                 transport=plan.transport, wire=plan.wire)
         m.set_custom_reduce_scatter(rs)
         plan.rs_hooks.append(rs)
 
@@ -59,14 +60,14 @@ def make_hook_factories(plan: FSDPPlan, reduce_out_dtype: torch.dtype = torch.bf
     ag = rs = None
     if plan.quantize:
         def ag():
-            hook = (ZipCCLAllGather(codec_version=plan.codec_version, transport=plan.transport) if plan.zip_ccl
+            hook = (ZipCCLAllGather(codec_version=plan.codec_version, transport=plan.transport, wire=plan.wire) if plan.zip_ccl
                     else QuantizedAllGather(transport=plan.transport))
             plan.ag_hooks.append(hook)
             return hook
     if plan.compress_rs:
         def rs():
             hook = ZipCCLReduceScatter(error_feedback=plan.error_feedback, reduce_dtype=reduce_out_dtype,
-                                       transport=plan.transport)
+                                       transport=plan.transport, wire=plan.wire)
             plan.rs_hooks.append(hook)
             return hook
     return ag, rs

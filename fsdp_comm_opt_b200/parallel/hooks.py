@@ -137,6 +137,11 @@ class ZipCCLAllGather(_CommBase):
     are gathered with two collectives and no host sync; on ``"symm"`` only the used bytes of each
     record cross NVLink.
 
+    ``wire="verbatim"`` (fused ``"symm"`` transport only) runs the same one-kernel push / flag /
+    gather protocol on the raw bf16 bytes, with no codec work: for links with bandwidth to spare,
+    where the codec's instructions cost the kernels running beside the collective more than the
+    bytes saved.  On the ``"lib"`` transport it is a plain library all-gather.
+
     Non-bf16 inputs are gathered uncompressed (the reference value-casts them to bf16, which is
     lossy for fp32 and wrong for FSDP's mixed-dtype uint8 buffers).
     """
@@ -144,7 +149,10 @@ class ZipCCLAllGather(_CommBase):
     ELEMS_PER_BLOCK = codec.ELEMS_PER_BLOCK
 
     def __init__(self, base_exponent: int = 122, base_update_interval: int = 16, *,
-                 codec_version: str = "auto", transport: str = "auto"):
+                 codec_version: str = "auto", transport: str = "auto", wire: str = "compressed"):
+        if wire not in ("compressed", "verbatim"):
+            raise ValueError(f"unknown wire format {wire!r}")
+        self.wire = wire
         self.base_exponent = base_exponent
         self.base_update_interval = max(1, base_update_interval)
         self.codec_version = codec_version
@@ -199,7 +207,9 @@ class ZipCCLAllGather(_CommBase):
             from . import symm_impl as symm
 
             return symm.channel_for(group, x.device, "ag").all_gather(
-                output_tensor, x, mode="zip", async_op=async_op, urgent=self.urgent)
+                output_tensor, x, mode="zip", async_op=async_op, urgent=self.urgent, verbatim=self.wire == "verbatim")
+        if self.wire == "verbatim":
+            return dist.all_gather_into_tensor(output_tensor, x, group=group, async_op=async_op)
         if version == "v2":
             return self._lib_v2(output_tensor, x, group, world, async_op)
         return self._lib_v1(output_tensor, x, group, world, async_op)
@@ -298,12 +308,19 @@ class ZipCCLReduceScatter(_CommBase):
     The sum is scaled according to ``op`` (SUM, AVG or NCCL's PreMulSum) and written to
     ``output_tensor``.  Wire volume is about 1.4 B/element instead of 4 (fp32 NCCL).
 
+    ``wire="verbatim"`` (fused ``"symm"`` transport only): the same kernel and the same arithmetic
+    (bf16 rounding with error feedback, fp32 sum in rank order) with the bf16 rows pushed as they
+    are, 2 B/element and no codec work.
+
     The residual is training state: ``state_dict()`` / ``load_state_dict()`` expose it so a
     checkpoint can carry it per rank.
     """
 
     def __init__(self, error_feedback: bool = True, reduce_dtype: Optional[torch.dtype] = None, *,
-                 residual_dtype: torch.dtype = torch.bfloat16, transport: str = "auto"):
+                 residual_dtype: torch.dtype = torch.bfloat16, transport: str = "auto", wire: str = "compressed"):
+        if wire not in ("compressed", "verbatim"):
+            raise ValueError(f"unknown wire format {wire!r}")
+        self.wire = wire
         self.error_feedback = error_feedback
         self.reduce_dtype = reduce_dtype
         self.residual_dtype = residual_dtype
@@ -349,7 +366,8 @@ class ZipCCLReduceScatter(_CommBase):
             from . import symm_impl as symm
 
             return symm.channel_for(group, x.device, "rs").reduce_scatter(
-                output_tensor, x, scale=scale, residual=self._residual_for(x), async_op=async_op, urgent=self.urgent)
+                output_tensor, x, scale=scale, residual=self._residual_for(x), async_op=async_op, urgent=self.urgent,
+                verbatim=self.wire == "verbatim")
         return self._lib(output_tensor, x, group, world, scale, async_op)
 
     def _lib(self, output_tensor, x, group, world, scale, async_op):

@@ -232,9 +232,10 @@ class Channel:
                                                                 min(self.dec_ctas, self.bg_dec_ctas))
 
     def all_gather(self, output_tensor: torch.Tensor, x: torch.Tensor, mode: str = "zip", async_op: bool = False,
-                   urgent: bool = True):
-        """``mode="zip"``: lossless v2 codec.  ``mode="int8"``: per-shard absmax int8 (every rank,
-        the source included, ends up with the dequantised values)."""
+                   urgent: bool = True, verbatim: bool = False):
+        """``mode="zip"``: lossless v2 codec, or with ``verbatim`` the raw bf16 bytes on the same
+        protocol.  ``mode="int8"``: per-shard absmax int8 (every rank, the source included, ends
+        up with the dequantised values)."""
         if mode not in ("zip", "int8"):
             raise ValueError(f"unknown all-gather mode {mode!r}")
         if x.dtype != torch.bfloat16 or output_tensor.dtype != torch.bfloat16:
@@ -244,10 +245,11 @@ class Channel:
         seq = self._next_seq()
         fn = self._lib.zc_symm_all_gather if mode == "zip" else self._lib.zc_symm_all_gather_int8
         push, dec = self._budget(urgent)
-        _lib.check(fn(
-            x.data_ptr(), output_tensor.data_ptr(), self.peers_dev, self.local_ptr, self.mc_ptr or None, n, self.rank,
-            self.world, self.nc_max, seq, push, dec, self.timeout_s,
-            _lib.stream_ptr(self.device)), "zc_symm_all_gather")
+        args = (x.data_ptr(), output_tensor.data_ptr(), self.peers_dev, self.local_ptr, self.mc_ptr or None, n, self.rank,
+                self.world, self.nc_max, seq, push, dec, self.timeout_s)
+        if mode == "zip":
+            args += (int(verbatim),)
+        _lib.check(fn(*args, _lib.stream_ptr(self.device)), "zc_symm_all_gather")
         self.calls += 1
         self.elements += n * (self.world - 1)
         return self._work() if async_op else None
@@ -258,7 +260,7 @@ class Channel:
         return AggregatedWork([], ready_event=ev)
 
     def reduce_scatter(self, output_tensor: torch.Tensor, x: torch.Tensor, scale: float, residual, async_op=False,
-                       urgent: bool = True):
+                       urgent: bool = True, verbatim: bool = False):
         shard = x.numel() // self.world
         if output_tensor.numel() != shard or output_tensor.dtype not in (torch.float32, torch.bfloat16):
             raise ValueError("output must hold numel/world fp32 or bf16 elements")
@@ -271,7 +273,7 @@ class Channel:
             x.data_ptr(), output_tensor.data_ptr(), _lib.ptr(residual), self.peers_dev, self.local_ptr, shard,
             self.rank, self.world, self.nc_max, seq, int(x.dtype == torch.float32),
             int(output_tensor.dtype == torch.float32), float(scale), push, dec,
-            self.timeout_s, _lib.stream_ptr(self.device)), "zc_symm_reduce_scatter")
+            self.timeout_s, int(verbatim), _lib.stream_ptr(self.device)), "zc_symm_reduce_scatter")
         self.calls += 1
         self.elements += shard * (self.world - 1)
         return self._work() if async_op else None

@@ -161,6 +161,55 @@ def test_compressed_reduce_scatter_nccl_ranks(transport):
     run_ranks(_rs_case, WORLD, (transport,), backend="nccl")
 
 
+def _verbatim_case(rank, world):
+    """The verbatim wire (raw bf16 bytes on the fused protocol): the all-gather is bit exact, with
+    multicast stores and with per-peer stores, and the reduce-scatter gives the bits of the compressed
+    one (same rounding, same order of the fp32 sum); 2 bytes per element cross the links."""
+    import torch.distributed as dist
+    from fsdp_comm_opt_b200.parallel import symm_impl
+    from fsdp_comm_opt_b200.parallel.hooks import ZipCCLAllGather, ZipCCLReduceScatter
+
+    dev = torch.device("cuda", rank)
+    grp = dist.group.WORLD
+    assert symm_impl.available(grp)
+    sizes = [1 << 20, 777, 65536 * 3 + 5, 4096]
+    symm_impl.channel_for(grp, dev, "ag").reserve(max(sizes))
+    ag = ZipCCLAllGather(transport="symm", wire="verbatim")
+    for it, n in enumerate(sizes):
+        g = torch.Generator().manual_seed(7 * it + rank)
+        x = (torch.randn(n, generator=g) * 0.02).to(torch.bfloat16).to(dev)
+        ref = torch.zeros(world * n, dtype=torch.bfloat16, device=dev)
+        dist.all_gather_into_tensor(ref, x)
+        out = torch.zeros(world * n, dtype=torch.bfloat16, device=dev)
+        w = ag(out, x, grp, async_op=(it % 2 == 0))
+        if w is not None:
+            w.wait()
+        torch.cuda.synchronize()
+        assert torch.equal(_bits(out), _bits(ref)), (it, n)
+    ch = symm_impl.channel_for(grp, dev, "ag")
+    nchunks = sum((n + 1023) // 1024 for n in sizes)
+    assert ch.wire_bytes() == 2048 * nchunks * (world - 1)
+    for dtype in (torch.float32, torch.bfloat16):
+        shard = 50_000
+        g = torch.Generator().manual_seed(99 + rank)
+        x = (torch.randn(world * shard, generator=g) * 1e-3).to(dtype).to(dev)
+        outs = []
+        for wire in ("compressed", "verbatim"):
+            hook = ZipCCLReduceScatter(transport="symm", wire=wire)
+            o = torch.zeros(shard, dtype=dtype, device=dev)
+            hook(o, x.clone(), grp, dist.ReduceOp.AVG)
+            torch.cuda.synchronize()
+            outs.append(o)
+        assert torch.equal(outs[0], outs[1]), dtype
+    for c in symm_impl.all_channels():
+        c.check_status()
+        c.check_canaries()
+
+
+def test_verbatim_wire_on_the_fused_transport():
+    run_ranks(_verbatim_case, WORLD, (), backend="nccl")
+
+
 def _timeout_case(rank, world):
     """Rank 1 never joins one collective; rank 0's bounded wait must expire into a status word,
     surface as SymmTimeout on the host, and leave the context usable."""

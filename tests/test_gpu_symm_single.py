@@ -41,17 +41,17 @@ class _World:
     def status(self, r):
         return self.bufs[r][:4096].view(torch.int32)[65:68].tolist()
 
-    def all_gather(self, rank, x, out, push, dec, seq=1):
+    def all_gather(self, rank, x, out, push, dec, seq=1, verbatim=False):
         _lib.check(self.lib.zc_symm_all_gather(
             x.data_ptr(), out.data_ptr(), self.ptrs.data_ptr(), self.bufs[rank].data_ptr(), None, x.numel(), rank,
-            self.world, self.nc_max, seq, push, dec, 1.0, _lib.stream_ptr(DEV)), "zc_symm_all_gather")
+            self.world, self.nc_max, seq, push, dec, 1.0, int(verbatim), _lib.stream_ptr(DEV)), "zc_symm_all_gather")
 
-    def reduce_scatter(self, rank, x, out, push, dec, seq=1, scale=1.0):
+    def reduce_scatter(self, rank, x, out, push, dec, seq=1, scale=1.0, verbatim=False):
         shard = x.numel() // self.world
         _lib.check(self.lib.zc_symm_reduce_scatter(
             x.data_ptr(), out.data_ptr(), None, self.ptrs.data_ptr(), self.bufs[rank].data_ptr(), shard, rank,
             self.world, self.nc_max, seq, int(x.dtype == torch.float32), int(out.dtype == torch.float32), scale,
-            push, dec, 1.0, _lib.stream_ptr(DEV)), "zc_symm_reduce_scatter")
+            push, dec, 1.0, int(verbatim), _lib.stream_ptr(DEV)), "zc_symm_reduce_scatter")
 
 
 def _params(n, seed, outliers=False):
@@ -63,15 +63,16 @@ def _params(n, seed, outliers=False):
     return x.bfloat16()
 
 
+@pytest.mark.parametrize("verbatim", [False, True], ids=["compressed", "verbatim"])
 @pytest.mark.parametrize("world,n", [(2, 1 << 20), (4, 300_001), (8, 1 << 18), (8, 5000)])
-def test_fused_all_gather_ranks_in_sequence(world, n):
+def test_fused_all_gather_ranks_in_sequence(world, n, verbatim):
     w = _World(world, n)
     shards = [_params(n, 10 + r, outliers=(r % 2 == 1)) for r in range(world)]
     scratch = torch.empty(world * n, dtype=torch.bfloat16, device=DEV)
     for r in range(1, world):                      # the other ranks: encode and push only
-        w.all_gather(r, shards[r], scratch, push=32, dec=0)
+        w.all_gather(r, shards[r], scratch, push=32, dec=0, verbatim=verbatim)
     out = torch.zeros(world * n, dtype=torch.bfloat16, device=DEV)
-    w.all_gather(0, shards[0], out, push=32, dec=64)   # rank 0: push, then decode what has arrived
+    w.all_gather(0, shards[0], out, push=32, dec=64, verbatim=verbatim)   # rank 0: push, then decode what has arrived
     torch.cuda.synchronize()
     assert w.status(0) == [0, 0, 0] and w.canaries_intact()
     assert torch.equal(out.view(torch.int16), torch.cat(shards).view(torch.int16))
@@ -79,14 +80,15 @@ def test_fused_all_gather_ranks_in_sequence(world, n):
 
 @pytest.mark.parametrize("world,shard,dtype", [(2, 1 << 19, torch.bfloat16), (4, 70_000, torch.float32),
                                                (8, 1 << 16, torch.bfloat16), (8, 3000, torch.bfloat16)])
-def test_fused_reduce_scatter_ranks_in_sequence(world, shard, dtype):
+@pytest.mark.parametrize("verbatim", [False, True], ids=["compressed", "verbatim"])
+def test_fused_reduce_scatter_ranks_in_sequence(world, shard, dtype, verbatim):
     w = _World(world, shard)
     rows = [(_params(world * shard, 40 + r, outliers=True).float() * 0.05).bfloat16().to(dtype) for r in range(world)]
     dummy = torch.empty(shard, dtype=torch.float32, device=DEV)
     for r in range(1, world):
-        w.reduce_scatter(r, rows[r], dummy, push=48, dec=0)
+        w.reduce_scatter(r, rows[r], dummy, push=48, dec=0, verbatim=verbatim)
     out = torch.zeros(shard, dtype=torch.float32, device=DEV)
-    w.reduce_scatter(0, rows[0], out, push=48, dec=64, scale=1.0 / world)
+    w.reduce_scatter(0, rows[0], out, push=48, dec=64, scale=1.0 / world, verbatim=verbatim)
     torch.cuda.synchronize()
     assert w.status(0) == [0, 0, 0] and w.canaries_intact()
     # the kernel adds its own row first, then the sources by rank, in fp32

@@ -11,6 +11,7 @@ optimizer / LR step -> zero_grad -> profiler step -> logging -> checkpoint), and
   --act-ckpt                    activation checkpointing per decoder block
   --steps N                     stop after N optimizer steps
   --transport / --codec         symm | lib | auto,  v1 | v2 | auto
+  --wire                        compressed | verbatim (fused transport: raw bf16 bytes, no codec work)
   --master-dtype fp32           keep fp32 master weights (communication stays bf16)
   --sharding {flat,fsdp2}       the package's flat-shard ZeRO-3 engine (default) or PyTorch FSDP2
                                 (the reference's wrapping; chosen automatically for --cpu-offload)
@@ -85,6 +86,9 @@ def _get_parser() -> argparse.ArgumentParser:
     p.add_argument("--steps", default=None, type=int)
     p.add_argument("--transport", default="auto", choices=["auto", "symm", "lib"])
     p.add_argument("--codec", default="auto", choices=["auto", "v1", "v2"])
+    p.add_argument("--wire", default="compressed", choices=["compressed", "verbatim"],
+                   help="what the fused collectives move: v2 records, or the raw bf16 bytes on the same one-kernel "
+                        "protocol (no codec work; for links with bandwidth to spare)")
     p.add_argument("--master-dtype", default="bf16", choices=["bf16", "fp32"])
     p.add_argument("--num-samples", default=1 << 14, type=int, help="synthetic dataset length")
     p.add_argument("--heartbeat-timeout", default=0.0, type=float,
@@ -143,7 +147,7 @@ def main(argv=None):
     ecfg = EngineConfig(model=cfg, lr=args.lr, master_dtype=master_dtype, quantize=args.quantize,
                         zip_ccl=args.zip_ccl, compress_rs=args.compress_rs, act_ckpt=args.act_ckpt,
                         forward_prefetch_distance=args.forward_prefetch_distance, transport=args.transport,
-                        codec_version=args.codec, seed=args.seed, sharding=sharding, cpu_offload=args.cpu_offload,
+                        codec_version=args.codec, wire=args.wire, seed=args.seed, sharding=sharding, cpu_offload=args.cpu_offload,
                         error_feedback=not args.no_error_feedback, time_collectives=True,
                         reshard_after_forward={"auto": "auto", "true": True, "false": False}[args.reshard_after_forward])
     model, plan, flat = build_sharded(ecfg, device)
