@@ -30,9 +30,11 @@ def declare(lib) -> None:
     _sig(lib, "zc_rmsnorm_fwd", P, P, P, P, P, P, L, I, F, P)
     _sig(lib, "zc_rmsnorm_bwd", P, P, P, P, P, P, P, P, L, I, P)
     _sig(lib, "zc_rmsnorm_bwd_ctas", L)
-    _sig(lib, "zc_layernorm_fwd", P, P, P, P, P, P, L, I, F, P)
+    _sig(lib, "zc_layernorm_fwd", P, P, P, P, P, P, P, P, L, I, F, P)
     _sig(lib, "zc_layernorm_bwd_ctas", L)
-    _sig(lib, "zc_layernorm_bwd", P, P, P, P, P, P, P, P, L, I, P)
+    _sig(lib, "zc_layernorm_bwd", P, P, P, P, P, P, P, P, P, I, I, I, P, L, I, P)
+    _sig(lib, "zc_bf16_column_sum_blocks", L)
+    _sig(lib, "zc_bf16_column_sum", P, L, I, L, P, I, I, P, P)
     _sig(lib, "zc_bias_gelu_fwd", P, P, P, L, I, P)
     _sig(lib, "zc_bias_gelu_bwd", P, P, P, P, L, I, P)
     _sig(lib, "zc_rope_inplace", P, P, P, L, I, I, I, I, F, P)
@@ -64,6 +66,7 @@ def declare(lib) -> None:
     _sig(lib, "zc_gemm_bf16", P, P, P, L, L, L, I, I, I, P)
     _sig(lib, "zc_gemm_bf16_2sm", P, P, P, L, L, L, I, I, I, P)
     _sig(lib, "zc_gemm_bf16_2sm_ld", P, P, P, L, L, L, L, L, L, I, I, I, P)
+    _sig(lib, "zc_gemm_bf16_2sm_bias", P, P, P, P, L, L, L, L, L, L, I, I, I, P)
     _sig(lib, "zc_gemm_status_read_and_clear")
     # fused collectives
     from ctypes import c_double, c_uint

@@ -153,6 +153,7 @@ struct Params {
   float* partial;      // [tail tiles][split][256][256] fp32, or null when split == 1
   int64_t M, N, K;
   int64_t ldc;         // elements between rows of C (>= N rounded up to 8: whole 8-column groups are stored)
+  const __nv_bfloat16* bias;  // [N] added to every row before rounding, or null
   int accumulate;
   int group_m;         // tiles are walked in bands of `group_m` m-tiles, n-major inside a band
   int full_tiles;      // tiles computed whole; the remaining tiles are split along K
@@ -197,6 +198,24 @@ __device__ __forceinline__ Unit unit_of(int u, const Params& p, int m_tiles, int
   }
   tile_coords(t, m_tiles, n_tiles, p.group_m, w.mi, w.ni);
   return w;
+}
+
+// f[j] += bias[col + j], j = 0..7 (col is a multiple of 8; the last group of a ragged N is read element-wise)
+__device__ __forceinline__ void add_bias8(const __nv_bfloat16* bias, int64_t col, int64_t N, float (&f)[8]) {
+  if (col + 8 <= N) {
+    const uint4 b = __ldg(reinterpret_cast<const uint4*>(bias + col));
+    const __nv_bfloat162* bb = reinterpret_cast<const __nv_bfloat162*>(&b);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 t = __bfloat1622float2(bb[j]);
+      f[2 * j] += t.x;
+      f[2 * j + 1] += t.y;
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      if (col + j < N) f[j] += __bfloat162float(bias[col + j]);
+  }
 }
 
 template <int A_MAJOR, int B_MAJOR>
@@ -387,6 +406,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
             float f[8];
 #pragma unroll
             for (int j = 0; j < 8; ++j) f[j] = __uint_as_float(r[q * 8 + j]);
+            if (p.bias) add_bias8(p.bias, col0 + c + q * 8, p.N, f);
             uint4* dst = reinterpret_cast<uint4*>(crow + c + q * 8);
             if (p.accumulate) {
               const uint4 old = *dst;
@@ -458,6 +478,7 @@ __global__ void __launch_bounds__(256) gemm_2sm_fixup_kernel(const Params p, int
       f[0] += x.x; f[1] += x.y; f[2] += x.z; f[3] += x.w;
       f[4] += y.x; f[5] += y.y; f[6] += y.z; f[7] += y.w;
     }
+    if (p.bias) add_bias8(p.bias, (int64_t)ni * BN + c8 * 8, p.N, f);
     uint4* dst = reinterpret_cast<uint4*>(p.C + ((int64_t)mi * BM + row) * p.ldc + (int64_t)ni * BN + c8 * 8);
     if (p.accumulate) {
       const uint4 old = *dst;
@@ -562,9 +583,13 @@ int* zc_gemm_status_word();  // gemm_tcgen05.cu: the current device's GEMM statu
 // column N of a row are written too: with zeros, since the operand columns they multiply are outside the
 // tensor map and load as zeros).  Edge tiles are zero-filled on load and masked on store.  Shares zc_gemm_bf16's status word
 // (zc_gemm_status_read_and_clear; code 8 = a bounded wait of this kernel expired).
-int zc_gemm_bf16_2sm_ld(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K, int64_t lda,
-                        int64_t ldb, int64_t ldc, int trans_a, int trans_b, int accumulate, cudaStream_t st) {
+// `bias`: null, or N bf16 values (16-byte aligned) added to every row of the product before it is rounded
+// (and before the old C is added when `accumulate` is set).
+int zc_gemm_bf16_2sm_bias(const void* A, const void* B, void* C, const void* bias, int64_t M, int64_t N, int64_t K,
+                          int64_t lda, int64_t ldb, int64_t ldc, int trans_a, int trans_b, int accumulate,
+                          cudaStream_t st) {
   ZC_NVTX_RANGE("zc_gemm_bf16_2sm");
+  if (reinterpret_cast<uintptr_t>(bias) & 15) return zc::ERR_UNSUPPORTED;
   using namespace zc;
   using namespace zc::g2;
   if (M <= 0 || N <= 0 || K <= 0) return ERR_UNSUPPORTED;
@@ -606,6 +631,7 @@ int zc_gemm_bf16_2sm_ld(const void* A, const void* B, void* C, int64_t M, int64_
   }
   Params p;
   p.C = (__nv_bfloat16*)C; p.M = M; p.N = N; p.K = K; p.ldc = ldc;
+  p.bias = (const __nv_bfloat16*)bias;
   p.accumulate = accumulate;
   static const int forced_gm = getenv("ZC_GEMM_GROUP_M") ? atoi(getenv("ZC_GEMM_GROUP_M")) : 0;
   static const int forced_split = getenv("ZC_GEMM_SPLIT") ? atoi(getenv("ZC_GEMM_SPLIT")) : -1;
@@ -657,6 +683,11 @@ int zc_gemm_bf16_2sm_ld(const void* A, const void* B, void* C, int64_t M, int64_
     rc = launch_status();
   }
   return rc;
+}
+
+int zc_gemm_bf16_2sm_ld(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K, int64_t lda,
+                        int64_t ldb, int64_t ldc, int trans_a, int trans_b, int accumulate, cudaStream_t st) {
+  return zc_gemm_bf16_2sm_bias(A, B, C, nullptr, M, N, K, lda, ldb, ldc, trans_a, trans_b, accumulate, st);
 }
 
 // Contiguous operands: M, N and K multiples of 8.

@@ -57,12 +57,15 @@ __device__ __forceinline__ float2 block_sum2(float a, float b, float2* red) {
 
 // ---------------------------------------------------------------------------------------------
 // LayerNorm.  One CTA per row, row cached in registers (cols <= 8192, cols % 8 == 0).
-//   mean = E[x], rstd = rsqrt(E[(x - mean)^2] + eps), y = (x - mean) * rstd * w + b
+//   mean = E[h], rstd = rsqrt(E[(h - mean)^2] + eps), y = (h - mean) * rstd * w + b
+// h = x, or with `res` the residual sum x + res rounded to bf16, which is also written to `h_out`
+// (the residual add of the block before, done here instead of in a kernel of its own).
 // ---------------------------------------------------------------------------------------------
 template <int MAXV>
 __global__ void __launch_bounds__(LN_THREADS) layernorm_fwd_kernel(
-    const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w, const __nv_bfloat16* __restrict__ b,
-    __nv_bfloat16* __restrict__ y, float* __restrict__ mean_out, float* __restrict__ rstd_out, int cols, float eps) {
+    const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ res, const __nv_bfloat16* __restrict__ w,
+    const __nv_bfloat16* __restrict__ b, __nv_bfloat16* __restrict__ y, __nv_bfloat16* __restrict__ h_out,
+    float* __restrict__ mean_out, float* __restrict__ rstd_out, int cols, float eps) {
   __shared__ float2 red[32];
   const int64_t row = blockIdx.x;
   const int nvec = cols / 8;
@@ -73,6 +76,15 @@ __global__ void __launch_bounds__(LN_THREADS) layernorm_fwd_kernel(
     const int v = threadIdx.x + i * LN_THREADS;
     if (v < nvec) {
       unpack8(ld8(x + row * cols + v * 8), h[i]);
+      if (res) {
+        float r[8];
+        unpack8(ld8(res + row * cols + v * 8), r);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) h[i][j] += r[j];
+        const BF8 hb = pack8(h[i]);
+        st8(h_out + row * cols + v * 8, hb);
+        unpack8(hb, h[i]);  // normalise what was stored: the backward pass reads it back
+      }
 #pragma unroll
       for (int j = 0; j < 8; ++j) s += h[i][j];
     }
@@ -109,14 +121,14 @@ __global__ void __launch_bounds__(LN_THREADS) layernorm_fwd_kernel(
   }
 }
 
-// dx = rstd * (g - mean(g) - xhat * mean(g * xhat)),  g = dy * w,  xhat = (x - mean) * rstd
+// dx = rstd * (g - mean(g) - xhat * mean(g * xhat)) (+ dh),  g = dy * w,  xhat = (x - mean) * rstd
 // dw = sum_rows dy * xhat, db = sum_rows dy: per-CTA partial sums in registers, written to
-// partials[cta][0 | 1][cols] and summed by column_sum_kernel (no atomics)
+// partials[cta][0 | 1][cols] and summed by column_sum_deliver_kernel (no atomics)
 template <int MAXV>
 __global__ void __launch_bounds__(LN_THREADS) layernorm_bwd_kernel(
     const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
-    const float* __restrict__ mean_in, const float* __restrict__ rstd_in, __nv_bfloat16* __restrict__ dx,
-    float* __restrict__ partials, int64_t rows, int cols) {
+    const float* __restrict__ mean_in, const float* __restrict__ rstd_in, const __nv_bfloat16* __restrict__ dh,
+    __nv_bfloat16* __restrict__ dx, float* __restrict__ partials, int64_t rows, int cols) {
   __shared__ float2 red[32];
   const int nvec = cols / 8;
   float wv[MAXV][8], dwacc[MAXV][8], dbacc[MAXV][8];
@@ -158,6 +170,12 @@ __global__ void __launch_bounds__(LN_THREADS) layernorm_bwd_kernel(
         float o[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j) o[j] = rstd * (g[i][j] - m1 - xh[i][j] * m2);
+        if (dh) {  // gradient arriving through the residual path of the same tensor
+          float e[8];
+          unpack8(ld8(dh + row * cols + v * 8), e);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) o[j] += e[j];
+        }
         st8(dx + row * cols + v * 8, pack8(o));
       }
     }
@@ -177,10 +195,15 @@ __global__ void __launch_bounds__(LN_THREADS) layernorm_bwd_kernel(
   }
 }
 
-// out[c] = sum_r in[r][c] for an [nrows, ncols] fp32 matrix (ncols % 4 == 0);
-// block (32, 32): 32 float4 columns x 32 row groups
-__global__ void __launch_bounds__(1024) column_sum_kernel(const float* __restrict__ in, int nrows, int ncols,
-                                                          float* __restrict__ out) {
+// out[c] = sum_r in[r][c] for an [nrows, ncols] fp32 matrix (ncols % 4 == 0); block (32, 32): 32 float4
+// columns x 32 row groups.  The result is delivered where the optimizer reads it: columns [0, seg) go to outA,
+// [seg, 2 seg) to outB (null: a single segment), as fp32 or bf16, overwriting or adding to what is
+// there.  Used for LayerNorm's weight / bias gradients and the linear layers' bias gradients, which
+// can then be written straight into the flat gradient buffer of a sharded engine.
+__global__ void __launch_bounds__(1024) column_sum_deliver_kernel(const float* __restrict__ in, int nrows, int ncols,
+                                                                  int seg, void* __restrict__ outA,
+                                                                  void* __restrict__ outB, int out_bf16, int accA,
+                                                                  int accB) {
   __shared__ float4 acc[32][32];
   const int c4 = blockIdx.x * 32 + threadIdx.x;
   float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -198,7 +221,50 @@ __global__ void __launch_bounds__(1024) column_sum_kernel(const float* __restric
       const float4 v = acc[k][threadIdx.x];
       s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
     }
-    reinterpret_cast<float4*>(out)[c4] = s;
+    const float f[4] = {s.x, s.y, s.z, s.w};
+    const int col = c4 * 4;                       // seg % 4 == 0: a float4 never straddles the segments
+    const bool second = outB != nullptr && col >= seg;
+    void* out = second ? outB : outA;
+    const int oc = second ? col - seg : col;
+    const int accumulate = second ? accB : accA;
+    if (out_bf16) {
+      __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(out) + oc;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) o[j] = __float2bfloat16_rn(f[j] + (accumulate ? __bfloat162float(o[j]) : 0.f));
+    } else {
+      float* o = reinterpret_cast<float*>(out) + oc;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) o[j] = f[j] + (accumulate ? o[j] : 0.f);
+    }
+  }
+}
+
+// partial column sums of a bf16 matrix [rows, cols] (rows `ld` elements apart): block (32, 8) covers
+// 256 columns; blockIdx.y strides over the rows; partials[blockIdx.y][cols] fp32
+__global__ void __launch_bounds__(256) bf16_column_partials_kernel(const __nv_bfloat16* __restrict__ in, int64_t rows,
+                                                                   int cols, int64_t ld, float* __restrict__ partials) {
+  __shared__ float red[8][32][8];
+  const int v = blockIdx.x * 32 + threadIdx.x;  // 8-column vector
+  float a[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  if (v * 8 < cols) {
+    for (int64_t r = (int64_t)blockIdx.y * 8 + threadIdx.y; r < rows; r += (int64_t)gridDim.y * 8) {
+      float f[8];
+      unpack8(ld8(in + r * ld + v * 8), f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) a[j] += f[j];
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < 8; ++j) red[threadIdx.y][threadIdx.x][j] = a[j];
+  __syncthreads();
+  if (threadIdx.y == 0 && v * 8 < cols) {
+#pragma unroll
+    for (int k = 1; k < 8; ++k)
+#pragma unroll
+      for (int j = 0; j < 8; ++j) a[j] += red[k][threadIdx.x][j];
+    float4* dst = reinterpret_cast<float4*>(partials + (int64_t)blockIdx.y * cols + v * 8);
+    dst[0] = make_float4(a[0], a[1], a[2], a[3]);
+    dst[1] = make_float4(a[4], a[5], a[6], a[7]);
   }
 }
 
@@ -260,15 +326,17 @@ extern "C" {
 using zc::ERR_UNSUPPORTED;
 typedef __nv_bfloat16 bf16;
 
-int zc_layernorm_fwd(const void* x, const void* w, const void* b, void* y, float* mean, float* rstd, int64_t rows,
-                     int cols, float eps, cudaStream_t st) {
+// res / h_out: both null, or the residual to add to x first and where to write the sum
+int zc_layernorm_fwd(const void* x, const void* res, const void* w, const void* b, void* y, void* h_out, float* mean,
+                     float* rstd, int64_t rows, int cols, float eps, cudaStream_t st) {
   using namespace zc::gpt2;
-  if (cols % 8 || cols > LN_MAX_COLS) return ERR_UNSUPPORTED;
+  if (cols % 8 || cols > LN_MAX_COLS || ((res == nullptr) != (h_out == nullptr))) return ERR_UNSUPPORTED;
   if (rows == 0) return 0;
   const int nvec = cols / 8;
-#define ZC_LN_FWD(V)                                                                                           \
-  layernorm_fwd_kernel<V><<<(unsigned)rows, LN_THREADS, 0, st>>>((const bf16*)x, (const bf16*)w, (const bf16*)b, \
-                                                                 (bf16*)y, mean, rstd, cols, eps)
+#define ZC_LN_FWD(V)                                                                                              \
+  layernorm_fwd_kernel<V><<<(unsigned)rows, LN_THREADS, 0, st>>>((const bf16*)x, (const bf16*)res, (const bf16*)w,  \
+                                                                 (const bf16*)b, (bf16*)y, (bf16*)h_out, mean, rstd, \
+                                                                 cols, eps)
   if (nvec <= LN_THREADS) ZC_LN_FWD(1);
   else if (nvec <= 2 * LN_THREADS) ZC_LN_FWD(2);
   else ZC_LN_FWD(4);
@@ -279,9 +347,11 @@ int zc_layernorm_fwd(const void* x, const void* w, const void* b, void* y, float
 // CTAs the backward launches for `rows` rows: `partials` must hold [that many, 2, cols] fp32
 int zc_layernorm_bwd_ctas(int64_t rows) { return (int)std::min<int64_t>(rows, (int64_t)zc::sm_count() * 4); }
 
-// dwdb: [2, cols] fp32 (weight gradient, then bias gradient), overwritten
-int zc_layernorm_bwd(const void* dy, const void* x, const void* w, const float* mean, const float* rstd, void* dx,
-                     float* dwdb, float* partials, int64_t rows, int cols, cudaStream_t st) {
+// dh: null, or a gradient of the same shape added to dx.  dw / db: [cols] each, fp32 or (out_bf16) bf16,
+// overwritten or (acc_w / acc_b) added to.
+int zc_layernorm_bwd(const void* dy, const void* x, const void* w, const float* mean, const float* rstd,
+                     const void* dh, void* dx, void* dw, void* db, int out_bf16, int acc_w, int acc_b,
+                     float* partials, int64_t rows, int cols, cudaStream_t st) {
   using namespace zc::gpt2;
   if (cols % 8 || cols > LN_MAX_COLS) return ERR_UNSUPPORTED;
   if (rows == 0) return 0;
@@ -289,12 +359,31 @@ int zc_layernorm_bwd(const void* dy, const void* x, const void* w, const float* 
   const int nvec = cols / 8;
 #define ZC_LN_BWD(V)                                                                                          \
   layernorm_bwd_kernel<V><<<grid, LN_THREADS, 0, st>>>((const bf16*)dy, (const bf16*)x, (const bf16*)w, mean, rstd, \
-                                                       (bf16*)dx, partials, rows, cols)
+                                                       (const bf16*)dh, (bf16*)dx, partials, rows, cols)
   if (nvec <= LN_THREADS) ZC_LN_BWD(1);
   else if (nvec <= 2 * LN_THREADS) ZC_LN_BWD(2);
   else ZC_LN_BWD(4);
 #undef ZC_LN_BWD
-  column_sum_kernel<<<(2 * cols / 4 + 31) / 32, dim3(32, 32), 0, st>>>(partials, grid, 2 * cols, dwdb);
+  column_sum_deliver_kernel<<<(2 * cols / 4 + 31) / 32, dim3(32, 32), 0, st>>>(partials, grid, 2 * cols, cols, dw, db,
+                                                                                out_bf16, acc_w, acc_b);
+  return zc::launch_status();
+}
+
+// Row blocks of zc_bf16_column_sum for `rows` rows: `partials` must hold [that many, cols] fp32
+int zc_bf16_column_sum_blocks(int64_t rows) { return (int)std::max<int64_t>(1, std::min<int64_t>(rows / 64, 32)); }
+
+// out[c] (+)= sum over rows of in[r][c] for a bf16 matrix whose rows are `ld` elements apart
+// (cols % 8 == 0, ld % 8 == 0): the bias gradient of a linear layer from its output gradient.
+int zc_bf16_column_sum(const void* in, int64_t rows, int cols, int64_t ld, void* out, int out_bf16, int accumulate,
+                       float* partials, cudaStream_t st) {
+  using namespace zc::gpt2;
+  if (cols % 8 || ld % 8 || (reinterpret_cast<uintptr_t>(in) & 15)) return ERR_UNSUPPORTED;
+  if (rows == 0 || cols == 0) return 0;
+  const int rb = zc_bf16_column_sum_blocks(rows);
+  bf16_column_partials_kernel<<<dim3((cols / 8 + 31) / 32, rb), dim3(32, 8), 0, st>>>((const bf16*)in, rows, cols, ld,
+                                                                                       partials);
+  column_sum_deliver_kernel<<<(cols / 4 + 31) / 32, dim3(32, 32), 0, st>>>(partials, rb, cols, cols, out, nullptr,
+                                                                            out_bf16, accumulate, 0);
   return zc::launch_status();
 }
 

@@ -1,8 +1,9 @@
 """GPT-2-shape decoder (LayerNorm, learned positions, biased projections, tanh-GELU MLP, tied
 output embedding): the family of the reference's shipped run (run.sh:1, GPT-2-XL), discovered by
 the reference at ``model.transformer.h`` (train.py:99-100).  Attention, GEMMs, LayerNorm, the fused
-bias + GELU of the MLP, the loss and the optimizer are the package's own ops; the remaining bias
-adds and residual adds are PyTorch elementwise ops.
+bias + GELU of the MLP, the loss and the optimizer are the package's own ops.  Bias adds run in the
+GEMM epilogue, residual adds inside the LayerNorm that follows them, and the gradients of biases and
+norm parameters are written by their kernels straight into a sharded engine's gradient buffer.
 """
 from __future__ import annotations
 
@@ -31,7 +32,7 @@ class BiasLinear(nn.Module):
         nn.init.zeros_(self.bias)
 
     def forward(self, x):
-        return gemm.linear(x, self.weight) + self.bias.to(x.dtype)
+        return gemm.linear(x, self.weight, self.bias)
 
 
 class GPT2Block(nn.Module):
@@ -46,21 +47,26 @@ class GPT2Block(nn.Module):
         self.ln_1 = nn.LayerNorm(d, eps=cfg.norm_eps)
         self.ln_2 = nn.LayerNorm(d, eps=cfg.norm_eps)
 
-    def forward(self, x):
+    def forward(self, x, delta=None):
+        """``x`` is the residual stream before the previous block's MLP output ``delta`` was added: the
+        sum is formed inside ``ln_1``.  Returns the residual stream after attention and this block's MLP
+        output, to be added by the next norm."""
         cfg = self.cfg
         B, S, d = x.shape
         H, hd = cfg.n_heads, cfg.head_dim
-        ln1 = gpt2_ops.layer_norm(x, self.ln_1.weight, self.ln_1.bias, self.ln_1.eps)
+        if delta is None:
+            ln1 = gpt2_ops.layer_norm(x, self.ln_1.weight, self.ln_1.bias, self.ln_1.eps)
+        else:
+            ln1, x = gpt2_ops.add_layer_norm(x, delta, self.ln_1.weight, self.ln_1.bias, self.ln_1.eps)
         qkv = self.c_attn(ln1).view(B, S, 3 * H, hd)
         if x.is_cuda and hd not in (64, 128):
             q, k, v = (t.transpose(1, 2) for t in qkv.split(H, dim=2))
             o = F.scaled_dot_product_attention(q, k, v, is_causal=True).transpose(1, 2).reshape(B, S, d)
         else:
             o = attn_ops.causal_attention(qkv, H, H).view(B, S, d)
-        x = x + self.c_proj(o)
-        ln2 = gpt2_ops.layer_norm(x, self.ln_2.weight, self.ln_2.bias, self.ln_2.eps)
+        ln2, x = gpt2_ops.add_layer_norm(x, self.c_proj(o), self.ln_2.weight, self.ln_2.bias, self.ln_2.eps)
         h = gpt2_ops.bias_gelu(gemm.linear(ln2, self.c_fc.weight), self.c_fc.bias)
-        return x + self.c_mlp_proj(h)
+        return x, self.c_mlp_proj(h)
 
 
 class GPT2Backbone(nn.Module):
@@ -87,13 +93,13 @@ class GPT2ForCausalLM(nn.Module):
         B, S = input_ids.shape
         t = self.transformer
         pos = torch.arange(S, device=input_ids.device)
-        x = t.wte(input_ids) + t.wpe(pos)[None]
+        x, m = t.wte(input_ids), t.wpe(pos)[None].expand(B, S, -1)   # the position add runs in the first norm
         for blk in t.h:
             if self.activation_checkpointing and torch.is_grad_enabled():
-                x = checkpoint(blk, x, use_reentrant=False)
+                x, m = checkpoint(blk, x, m, use_reentrant=False)
             else:
-                x = blk(x)
-        x = gpt2_ops.layer_norm(x, t.ln_f.weight, t.ln_f.bias, t.ln_f.eps)
+                x, m = blk(x, m)
+        x, _ = gpt2_ops.add_layer_norm(x, m, t.ln_f.weight, t.ln_f.bias, t.ln_f.eps)
         logits = gemm.linear(x, t.wte.weight)  # tied output embedding
         loss = None
         if labels is not None:

@@ -60,7 +60,7 @@ def _kernel_for(a: torch.Tensor, b: torch.Tensor, M: int, N: int, K: int, trans_
 
 
 def gemm(a: torch.Tensor, b: torch.Tensor, trans_a: bool, trans_b: bool,
-         out: torch.Tensor | None = None, accumulate: bool = False) -> torch.Tensor:
+         out: torch.Tensor | None = None, accumulate: bool = False, bias: torch.Tensor | None = None) -> torch.Tensor:
     """C[M,N] (+)= op(A) @ op(B) for row-major 2-D bf16 tensors.
 
     op(A) is A ``[M,K]`` (or A^T of a stored ``[K,M]`` when ``trans_a``); op(B) is B ``[K,N]`` (or
@@ -68,7 +68,8 @@ def gemm(a: torch.Tensor, b: torch.Tensor, trans_a: bool, trans_b: bool,
     slices of wider buffers as long as rows stay a multiple of 8 elements apart.  When N is not a
     multiple of 8 (GPT-2's vocabulary of 50257) the result allocated here is a ``[:, :N]`` view of a
     buffer whose rows are padded to the next multiple of 8, so that the next GEMM and the loss kernel
-    can read it with aligned rows; its padding columns hold zeros.
+    can read it with aligned rows; its padding columns hold zeros.  ``bias`` ([N]) is added to every
+    row in the kernel's epilogue (the two-SM kernel), else by a separate add.
     """
     M, K = (a.shape[1], a.shape[0]) if trans_a else (a.shape[0], a.shape[1])
     N = b.shape[0] if trans_b else b.shape[1]
@@ -83,21 +84,32 @@ def gemm(a: torch.Tensor, b: torch.Tensor, trans_a: bool, trans_b: bool,
             accumulate = False
         lib = _lib.cuda()
         if kind == "2sm":
-            _lib.check(lib.zc_gemm_bf16_2sm_ld(
-                a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, a.stride(0), b.stride(0), out.stride(0),
-                int(trans_a), int(trans_b), int(accumulate), _lib.stream_ptr(a.device)), "zc_gemm_bf16_2sm")
+            fused_bias = (bias is not None and bias.dtype == torch.bfloat16 and bias.is_contiguous()
+                          and bias.numel() == N and bias.data_ptr() % 16 == 0)
+            _lib.check(lib.zc_gemm_bf16_2sm_bias(
+                a.data_ptr(), b.data_ptr(), out.data_ptr(), bias.data_ptr() if fused_bias else None, M, N, K,
+                a.stride(0), b.stride(0), out.stride(0), int(trans_a), int(trans_b), int(accumulate),
+                _lib.stream_ptr(a.device)), "zc_gemm_bf16_2sm")
+            if bias is not None and not fused_bias:
+                out.add_(bias.to(out.dtype))
         else:
             _lib.check(lib.zc_gemm_bf16(
                 a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, int(trans_a), int(trans_b),
                 int(accumulate), _lib.stream_ptr(a.device)), "zc_gemm_bf16")
+            if bias is not None:
+                out.add_(bias.to(out.dtype))
         return out
     A = a.t() if trans_a else a
     B = b.t() if trans_b else b
     if out is None:
-        return torch.matmul(A, B)
-    if accumulate:
-        return out.addmm_(A, B)
-    return torch.matmul(A, B, out=out)
+        res = torch.matmul(A, B)
+    elif accumulate:
+        res = out.addmm_(A, B)
+    else:
+        res = torch.matmul(A, B, out=out)
+    if bias is not None:
+        res.add_(bias.to(res.dtype))
+    return res
 
 
 class _Linear(torch.autograd.Function):
@@ -108,11 +120,13 @@ class _Linear(torch.autograd.Function):
     ``.grad`` tensor is produced."""
 
     @staticmethod
-    def forward(ctx, x, w):
+    def forward(ctx, x, w, bias=None):
         ctx.save_for_backward(x)
         ctx.w = w
+        ctx.bias = bias
         x2 = x.reshape(-1, x.shape[-1])
-        y = gemm(x2, w, False, True)           # [T,K] @ [N,K]^T
+        b = None if bias is None else (bias if bias.dtype == x.dtype else bias.to(x.dtype))
+        y = gemm(x2, w, False, True, bias=b)   # [T,K] @ [N,K]^T (+ bias in the epilogue)
         return y.view(*x.shape[:-1], w.shape[0])
 
     @staticmethod
@@ -133,11 +147,16 @@ class _Linear(torch.autograd.Function):
                 w.main_grad_written = True
             else:
                 dw = gemm(dy2, x2, True, False)                # [T,N]^T @ [T,K]
-        return dx, dw
+        db = None
+        if ctx.bias is not None and ctx.needs_input_grad[2]:
+            from .gpt2_ops import bias_grad
+
+            db = bias_grad(dy2, ctx.bias)                      # column sums, into bias.main_grad when it has one
+        return dx, dw, db
 
 
-def linear(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
-    """``x [..., K] @ w[N, K]^T`` without bias."""
+def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None) -> torch.Tensor:
+    """``x [..., K] @ w[N, K]^T (+ bias)``."""
     if x.dtype != w.dtype:
         w = w.to(x.dtype)
-    return _Linear.apply(x, w)
+    return _Linear.apply(x, w, bias)

@@ -399,6 +399,66 @@ def test_bias_gelu_fwd_bwd(rows, cols):
     assert torch.allclose(b.grad.float(), bf.grad, atol=0.02 * rows ** 0.5 + 0.05, rtol=3e-2)
 
 
+@pytest.mark.parametrize("rows,cols,main_grad", [(64, 1600, None), (300, 256, torch.bfloat16), (2048, 1600, torch.float32)])
+def test_add_layernorm_and_direct_gradient_delivery(rows, cols, main_grad):
+    """LayerNorm fused with the residual add in front of it, the gradient arriving through the sum added
+    inside the backward kernel, and dw / db written (or accumulated) straight into ``main_grad``."""
+    torch.manual_seed(23)
+    x = (torch.randn(rows, cols, device=DEV) * 2).bfloat16().requires_grad_()
+    r = (torch.randn(rows, cols, device=DEV)).bfloat16().requires_grad_()
+    w = (1 + 0.1 * torch.randn(cols, device=DEV)).bfloat16().requires_grad_()
+    b = (0.1 * torch.randn(cols, device=DEV)).bfloat16().requires_grad_()
+    if main_grad is not None:
+        for p_ in (w, b):
+            p_.main_grad = torch.full((cols,), 0.5, dtype=main_grad, device=DEV)
+            p_.main_grad_written = True            # accumulate on top of the 0.5
+    y, h = gpt2_ops.add_layer_norm(x, r, w, b, 1e-5)
+    g, gh = torch.randn_like(y), torch.randn_like(h)
+    torch.autograd.backward([y, h], [g, gh])
+    xf, rf, wf, bf = (t.detach().float().requires_grad_() for t in (x, r, w, b))
+    hf = (xf + rf)
+    hq = hf.bfloat16().float()                     # the kernel normalises the stored (rounded) sum
+    ref = F.layer_norm(hf + (hq - hf).detach(), (cols,), wf, bf, 1e-5)
+    torch.autograd.backward([ref, hf], [g.float(), gh.float()])
+    assert torch.equal(h.float(), hq)
+    assert torch.allclose(y.float(), ref, atol=3e-2, rtol=2e-2)
+    assert torch.allclose(x.grad.float(), xf.grad, atol=4e-2, rtol=3e-2)
+    assert torch.equal(x.grad, r.grad)
+    tol = dict(atol=0.02 * rows ** 0.5 + 0.05, rtol=3e-2)
+    if main_grad is None:
+        assert torch.allclose(w.grad.float(), wf.grad, **tol) and torch.allclose(b.grad.float(), bf.grad, **tol)
+    else:
+        assert w.grad is None and b.grad is None
+        assert torch.allclose(w.main_grad.float() - 0.5, wf.grad, **tol)
+        assert torch.allclose(b.main_grad.float() - 0.5, bf.grad, **tol)
+
+
+@pytest.mark.parametrize("T,K,N", [(2048, 1600, 4800), (300, 256, 1000)])
+def test_linear_with_bias_in_the_gemm_epilogue(T, K, N):
+    from fsdp_comm_opt_b200.ops import gemm
+
+    torch.manual_seed(24)
+    x = (torch.randn(T, K, device=DEV) * 0.5).bfloat16().requires_grad_()
+    w = (torch.randn(N, K, device=DEV) * 0.05).bfloat16().requires_grad_()
+    b = torch.randn(N, device=DEV).bfloat16().requires_grad_()
+    b.main_grad = torch.zeros(N, dtype=torch.bfloat16, device=DEV)
+    b.main_grad_written = False
+    g = torch.randn(T, N, device=DEV).bfloat16()
+    before = _lib.launch_count()
+    y = gemm.linear(x, w, b)
+    y.backward(g)
+    torch.cuda.synchronize()
+    assert _lib.launch_count() - before >= 4          # three GEMMs and the column-sum kernel pair
+    xf, wf, bf = (t.detach().float().requires_grad_() for t in (x, w, b))
+    ref = xf @ wf.t() + bf
+    ref.backward(g.float())
+    assert torch.allclose(y.float(), ref, atol=2e-2 * float(ref.abs().max()), rtol=2e-2)
+    assert b.grad is None and b.main_grad_written
+    assert torch.allclose(b.main_grad.float(), bf.grad, atol=0.02 * T ** 0.5 + 0.1, rtol=3e-2)
+    assert torch.allclose(x.grad.float(), xf.grad, atol=2e-2 * float(xf.grad.abs().max()), rtol=3e-2)
+    assert torch.allclose(w.grad.float(), wf.grad, atol=2e-2 * float(wf.grad.abs().max()), rtol=3e-2)
+
+
 # ------------------------------------------------------------------ GEMM
 @pytest.mark.parametrize("backend,M,N,K", [
     ("tcgen05", 128, 128, 128), ("tcgen05", 256, 512, 384), ("tcgen05", 4096, 1536, 1024), ("tcgen05", 384, 256, 4096),
