@@ -322,6 +322,32 @@ def main():
     try:
         dev_ms, dev_loss, launches, (d0, d1) = run("device")
         e2e_ms, e2e_loss, _, (x0, x1) = run("e2e")
+        if args.impl == "ours":
+            # A step that produced a non-finite loss did not train (and runs fast: NaN operands draw
+            # little power): such a number must not be reported.  Build the engine again and measure
+            # once more; a second failure ends the run with an error.
+            import gc
+            import math
+
+            def any_rank_bad(*vals):
+                bad = torch.tensor([float(any(v is None or not math.isfinite(v) for v in vals))], device=device)
+                dist.all_reduce(bad, op=dist.ReduceOp.MAX)
+                return bool(bad.item())
+
+            if any_rank_bad(dev_loss, e2e_loss):
+                if rank == 0:
+                    print("[bench] non-finite loss in the timed steps: rebuilding the engine and measuring again",
+                          file=sys.stderr, flush=True)
+                make_ours.engine = None
+                step_dev = step_host = None
+                gc.collect()
+                torch.cuda.empty_cache()
+                step_dev, step_host, info, lib = make_ours(args, device)
+                dev_ms, dev_loss, launches, (d0, d1) = run("device")
+                e2e_ms, e2e_loss, _, (x0, x1) = run("e2e")
+                info["remeasured"] = "first attempt gave a non-finite loss"
+                if any_rank_bad(dev_loss, e2e_loss):
+                    raise RuntimeError(f"non-finite loss twice (device run {dev_loss}, end-to-end run {e2e_loss})")
     except torch.OutOfMemoryError as e:
         if args.impl != "reference":
             raise

@@ -203,11 +203,22 @@ struct RecRegs {
   uint4 e0, e1;     // bytes [16 lane, 16 lane + 16) and [512 + 16 lane, ...) of the escape area
 };
 
+// SM_SPLIT: the sign+mantissa section is stored as two 512-byte halves (lane l's bytes 0..15 at 16 l,
+// bytes 16..31 at 512 + 16 l) instead of 32 consecutive bytes per lane.  The fused collectives stage
+// their records that way: each of a warp's two stores then covers 512 contiguous bytes of the peer's
+// memory instead of 32 half-used 32-byte sectors.  Records in the documented format use SM_SPLIT = false.
+template <bool SM_SPLIT = false>
 __device__ __forceinline__ void v2_prefetch(const uint8_t* rec, uint32_t hdr, int lane, RecRegs& r) {
   r.hdr = hdr;
-  const uint4* smp = reinterpret_cast<const uint4*>(rec + lane * 32);
-  r.sm0 = __ldcg(smp);
-  r.sm1 = __ldcg(smp + 1);
+  if (SM_SPLIT) {
+    const uint4* smp = reinterpret_cast<const uint4*>(rec) + lane;
+    r.sm0 = __ldcg(smp);
+    r.sm1 = __ldcg(smp + 32);
+  } else {
+    const uint4* smp = reinterpret_cast<const uint4*>(rec + lane * 32);
+    r.sm0 = __ldcg(smp);
+    r.sm1 = __ldcg(smp + 1);
+  }
   const int w = v2_hdr_width(hdr);
   if (w == V2_RAW_WIDTH) {
     const uint4* ep = reinterpret_cast<const uint4*>(rec + 1024 + lane * 32);

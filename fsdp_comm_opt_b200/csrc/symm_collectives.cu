@@ -111,11 +111,13 @@ __device__ __forceinline__ void warp_copy16(uint8_t* dst, const uint8_t* src, in
     reinterpret_cast<uint4*>(dst)[i] = reinterpret_cast<const uint4*>(src)[i];
 }
 
-// the 32 sign+mantissa bytes of one lane, straight from registers to (peer) memory
+// the 32 sign+mantissa bytes of one lane, straight from registers to (peer) memory, as two halves 512
+// bytes apart (v2_prefetch<true> reads them back): each store instruction of the warp covers 512
+// contiguous bytes, so the data crosses NVLink in full lines
 __device__ __forceinline__ void store_sm32(uint8_t* rec, int lane, const LaneSplit& s) {
-  uint4* p = reinterpret_cast<uint4*>(rec + lane * 32);
+  uint4* p = reinterpret_cast<uint4*>(rec) + lane;
   p[0] = make_uint4(s.sm[0], s.sm[1], s.sm[2], s.sm[3]);
-  p[1] = make_uint4(s.sm[4], s.sm[5], s.sm[6], s.sm[7]);
+  p[32] = make_uint4(s.sm[4], s.sm[5], s.sm[6], s.sm[7]);
 }
 
 // NVSwitch multicast stores: one store to the multicast mapping of the symmetric buffer lands at the
@@ -134,20 +136,23 @@ __device__ __forceinline__ void warp_copy16_mc(uint8_t* mc_dst, const uint8_t* s
   for (int i = lane; i < nv; i += 32) mc_st128(mc_dst + 16 * i, reinterpret_cast<const uint4*>(src)[i]);
 }
 
-// Verbatim wire: a record is the chunk's 2048 bf16 bytes, lane l's 32 elements at byte l * 64.  Same
-// slots, flags and parity protocol as the compressed records, no header words and no codec work: for
-// links with bandwidth to spare, where the codec's instructions cost the kernels running beside the
-// collective more than the bytes saved.  Chosen per call; every rank must make the same choice.
+// Verbatim wire: a record is the chunk's 2048 bf16 bytes with no codec work, interleaved so that every
+// store and load instruction of a warp covers 512 contiguous bytes (lane l's k-th 16 bytes sit at
+// byte (k * 32 + l) * 16): remote stores leave the GPU as full lines.  Same slots, flags and parity
+// protocol as the compressed records, no header words.  For links with bandwidth to spare, where the
+// codec's instructions cost the kernels running beside the collective more than the bytes saved.
+// Chosen per call; every rank must make the same choice.
 __device__ __forceinline__ void store_verbatim(uint8_t* rec, int lane, const LaneIn& li) {
-  uint4* p = reinterpret_cast<uint4*>(rec + lane * 64);
+  uint4* p = reinterpret_cast<uint4*>(rec);
 #pragma unroll
-  for (int k = 0; k < 4; ++k) p[k] = make_uint4(li.w[4 * k], li.w[4 * k + 1], li.w[4 * k + 2], li.w[4 * k + 3]);
+  for (int k = 0; k < 4; ++k)
+    p[k * 32 + lane] = make_uint4(li.w[4 * k], li.w[4 * k + 1], li.w[4 * k + 2], li.w[4 * k + 3]);
 }
 __device__ __forceinline__ void load_verbatim(const uint8_t* rec, int lane, LaneIn& li) {
-  const uint4* p = reinterpret_cast<const uint4*>(rec + lane * 64);
+  const uint4* p = reinterpret_cast<const uint4*>(rec);
 #pragma unroll
   for (int k = 0; k < 4; ++k) {
-    const uint4 v = __ldcg(p + k);
+    const uint4 v = __ldcg(p + k * 32 + lane);
     li.w[4 * k] = v.x; li.w[4 * k + 1] = v.y; li.w[4 * k + 2] = v.z; li.w[4 * k + 3] = v.w;
   }
 }
@@ -220,10 +225,11 @@ __global__ void __launch_bounds__(256) symm_all_gather_kernel(const AgArgs a) {
         if constexpr (VERBATIM) {
           if (!ZC_SLOT_OK(L, c, V2_SLOT_BYTES, a.local, L.rank)) continue;
           if (a.mc) {
-            uint8_t* rec = slot_ptr(a.mc, L, parity, L.rank) + L.hdr_bytes + c * V2_SLOT_BYTES + lane * 64;
+            uint8_t* rec = slot_ptr(a.mc, L, parity, L.rank) + L.hdr_bytes + c * V2_SLOT_BYTES;
 #pragma unroll
             for (int k = 0; k < 4; ++k)
-              mc_st128(rec + 16 * k, make_uint4(li.w[4 * k], li.w[4 * k + 1], li.w[4 * k + 2], li.w[4 * k + 3]));
+              mc_st128(rec + 16 * (k * 32 + lane),
+                       make_uint4(li.w[4 * k], li.w[4 * k + 1], li.w[4 * k + 2], li.w[4 * k + 3]));
           } else {
             for (int q = 0; q < L.world; ++q)
               if (q != L.rank)
@@ -243,8 +249,8 @@ __global__ void __launch_bounds__(256) symm_all_gather_kernel(const AgArgs a) {
         }
         if (a.mc) {
           uint8_t* rec = slot_ptr(a.mc, L, parity, L.rank) + L.hdr_bytes + c * V2_SLOT_BYTES;
-          mc_st128(rec + lane * 32, make_uint4(s.sm[0], s.sm[1], s.sm[2], s.sm[3]));
-          mc_st128(rec + lane * 32 + 16, make_uint4(s.sm[4], s.sm[5], s.sm[6], s.sm[7]));
+          mc_st128(rec + lane * 16, make_uint4(s.sm[0], s.sm[1], s.sm[2], s.sm[3]));
+          mc_st128(rec + 512 + lane * 16, make_uint4(s.sm[4], s.sm[5], s.sm[6], s.sm[7]));
           warp_copy16_mc(rec + 1024, srec[warp], used - 1024, lane);
           if (lane == 0) mc_st32(reinterpret_cast<uint32_t*>(slot_ptr(a.mc, L, parity, L.rank)) + c, hdr);
         } else {
@@ -315,10 +321,10 @@ __global__ void __launch_bounds__(256) symm_all_gather_kernel(const AgArgs a) {
     // its own instruction stream, and the extra registers cost a resident CTA)
     const uint32_t myhdr = lane < cnt ? __ldcg(reinterpret_cast<const uint32_t*>(slot) + c0 + lane) : 0u;
     RecRegs cur, nxt;
-    v2_prefetch(recs, __shfl_sync(FULL, myhdr, 0), lane, cur);
+    v2_prefetch<true>(recs, __shfl_sync(FULL, myhdr, 0), lane, cur);
     for (int k = 0; k < cnt; ++k) {
       const uint32_t hn = __shfl_sync(FULL, myhdr, (k + 1) & 7);
-      if (k + 1 < cnt) v2_prefetch(recs + (long long)(k + 1) * V2_SLOT_BYTES, hn, lane, nxt);
+      if (k + 1 < cnt) v2_prefetch<true>(recs + (long long)(k + 1) * V2_SLOT_BYTES, hn, lane, nxt);
       LaneSplit s;
       v2_decode_regs(cur, esc, lane, s);
       LaneIn o;
@@ -559,7 +565,7 @@ __global__ void __launch_bounds__(256, 2) symm_reduce_scatter_kernel(const RsArg
     const uint8_t* myslot = slot_ptr(a.local, L, parity, is_src ? lane : p0);
     uint32_t myhdr = is_src ? __ldcg(reinterpret_cast<const uint32_t*>(myslot) + c0) : 0u;
     RecRegs cur, nxt;
-    v2_prefetch(slot_ptr(a.local, L, parity, p0) + L.hdr_bytes + c0 * V2_SLOT_BYTES, __shfl_sync(FULL, myhdr, p0), lane,
+    v2_prefetch<true>(slot_ptr(a.local, L, parity, p0) + L.hdr_bytes + c0 * V2_SLOT_BYTES, __shfl_sync(FULL, myhdr, p0), lane,
                 cur);
     for (int k = 0; k < cnt; ++k) {
       const long long c = c0 + k;
@@ -575,10 +581,10 @@ __global__ void __launch_bounds__(256, 2) symm_reduce_scatter_kernel(const RsArg
         int pn = p + 1;
         if (pn == L.rank) ++pn;
         if (pn < L.world) {
-          v2_prefetch(slot_ptr(a.local, L, parity, pn) + L.hdr_bytes + c * V2_SLOT_BYTES, __shfl_sync(FULL, myhdr, pn),
+          v2_prefetch<true>(slot_ptr(a.local, L, parity, pn) + L.hdr_bytes + c * V2_SLOT_BYTES, __shfl_sync(FULL, myhdr, pn),
                       lane, nxt);
         } else if (k + 1 < cnt) {
-          v2_prefetch(slot_ptr(a.local, L, parity, p0) + L.hdr_bytes + (c + 1) * V2_SLOT_BYTES,
+          v2_prefetch<true>(slot_ptr(a.local, L, parity, p0) + L.hdr_bytes + (c + 1) * V2_SLOT_BYTES,
                       __shfl_sync(FULL, nexthdr, p0), lane, nxt);
         }
         LaneSplit s;

@@ -210,6 +210,58 @@ def test_verbatim_wire_on_the_fused_transport():
     run_ranks(_verbatim_case, WORLD, (), backend="nccl")
 
 
+def _back_to_back_case(rank, world, wire):
+    """Many collectives of changing sizes queued on one stream with no host synchronisation in between
+    (the way a training step issues them), results checked only at the end: exercises the reuse of the
+    two parity buffers and of the flags while ranks run ahead of one another."""
+    import torch.distributed as dist
+    from fsdp_comm_opt_b200.parallel import symm_impl
+    from fsdp_comm_opt_b200.parallel.hooks import ZipCCLAllGather, ZipCCLReduceScatter
+
+    dev = torch.device("cuda", rank)
+    grp = dist.group.WORLD
+    sizes = [1 << 23, 300_000, 1 << 25, 4096, (1 << 22) + 1024, 70_000, 1 << 24, 1 << 20]
+    symm_impl.channel_for(grp, dev, "ag").reserve(max(sizes))
+    symm_impl.channel_for(grp, dev, "rs").reserve(max(sizes))
+    ag = ZipCCLAllGather(transport="symm", wire=wire)
+    rs = ZipCCLReduceScatter(transport="symm", wire=wire, error_feedback=False)
+    g = torch.Generator(device=dev).manual_seed(1234 + rank)
+    side = torch.cuda.Stream(dev)
+    xs, outs, refs, rxs, routs, rrefs = [], [], [], [], [], []
+    for rep in range(3):
+        for n in sizes:
+            x = (torch.randn(n, generator=g, device=dev) * 0.02).bfloat16()
+            ref = torch.empty(world * n, dtype=torch.bfloat16, device=dev)
+            dist.all_gather_into_tensor(ref, x)
+            xs.append(x), refs.append(ref), outs.append(torch.zeros(world * n, dtype=torch.bfloat16, device=dev))
+            shard = n // world // 8 * 8
+            rx = (torch.randn(world * shard, generator=g, device=dev) * 1e-3).bfloat16()
+            rref = torch.empty(shard, dtype=torch.float32, device=dev)
+            dist.reduce_scatter_tensor(rref, rx.float(), op=dist.ReduceOp.SUM)
+            rxs.append(rx), rrefs.append(rref), routs.append(torch.zeros(shard, dtype=torch.float32, device=dev))
+    torch.cuda.synchronize()
+    dist.barrier()
+    side.wait_stream(torch.cuda.current_stream(dev))
+    for i in range(len(xs)):                      # all-gathers on this stream, reduce-scatters on another
+        ag(outs[i], xs[i], grp, async_op=True)
+        with torch.cuda.stream(side):
+            rs(routs[i], rxs[i], grp, dist.ReduceOp.SUM, async_op=True)
+        if i % 5 == rank:                         # ranks drift apart
+            torch.cuda._sleep(3_000_000)
+    torch.cuda.synchronize()
+    for i in range(len(xs)):
+        assert torch.equal(_bits(outs[i]), _bits(refs[i])), ("all_gather", wire, i, xs[i].numel())
+        assert torch.allclose(routs[i], rrefs[i], rtol=1e-5, atol=1e-7), ("reduce_scatter", wire, i)
+    for c in symm_impl.all_channels():
+        c.check_status()
+        c.check_canaries()
+
+
+@pytest.mark.parametrize("wire", ["compressed", "verbatim"])
+def test_back_to_back_collectives_without_host_sync(wire):
+    run_ranks(_back_to_back_case, WORLD, (wire,), backend="nccl")
+
+
 def _timeout_case(rank, world):
     """Rank 1 never joins one collective; rank 0's bounded wait must expire into a status word,
     surface as SymmTimeout on the host, and leave the context usable."""
