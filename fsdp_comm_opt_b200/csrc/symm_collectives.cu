@@ -620,8 +620,8 @@ __global__ void __launch_bounds__(256, 2) symm_reduce_scatter_kernel(const RsArg
 // ---------------------------------------------------------------------------------------------
 // int8 all-gather: the arithmetic of the int8 hook (per-shard absmax scale = max(absmax/127, 1e-8),
 // q = clamp(round(x / scale), -127, 127)) on the same staging protocol.  A chunk's record is its
-// 1024 int8 values at the start of its slot; the header word carries the source's scale, so the
-// wire cost is 1028 bytes per 1024 elements.  Every rank, the source included, ends up with the
+// 1024 int8 values at the start of its slot (lane l's bytes 0..15 at 16 l, 16..31 at 512 + 16 l);
+// the header word carries the source's scale, so the wire cost is 1028 bytes per 1024 elements.  Every rank, the source included, ends up with the
 // dequantised values, so all ranks see identical parameters.
 // ---------------------------------------------------------------------------------------------
 constexpr int CW_ABSMAX = 70;  // bits of max|x| over the shard being gathered (set by absmax_bf16_kernel)
@@ -698,17 +698,17 @@ __global__ void __launch_bounds__(256) symm_all_gather_int8_kernel(const AgArgs 
         const uint4 q0 = make_uint4(qw[0], qw[1], qw[2], qw[3]), q1 = make_uint4(qw[4], qw[5], qw[6], qw[7]);
         if (a.mc) {
           uint8_t* slot = slot_ptr(a.mc, L, parity, L.rank);
-          uint8_t* dst = slot + L.hdr_bytes + c * V2_SLOT_BYTES + lane * 32;
+          uint8_t* dst = slot + L.hdr_bytes + c * V2_SLOT_BYTES + lane * 16;  // two 512-byte halves, as store_sm32
           mc_st128(dst, q0);
-          mc_st128(dst + 16, q1);
+          mc_st128(dst + 512, q1);
           if (lane == 0) mc_st32(reinterpret_cast<uint32_t*>(slot) + c, __float_as_uint(scale));
         } else {
           for (int q = 0; q < L.world; ++q) {
             if (q == L.rank) continue;
             uint8_t* slot = slot_ptr(a.peers[q], L, parity, L.rank);
-            uint4* dst = reinterpret_cast<uint4*>(slot + L.hdr_bytes + c * V2_SLOT_BYTES + lane * 32);
+            uint4* dst = reinterpret_cast<uint4*>(slot + L.hdr_bytes + c * V2_SLOT_BYTES) + lane;
             dst[0] = q0;
-            dst[1] = q1;
+            dst[32] = q1;
             if (lane == 0) reinterpret_cast<uint32_t*>(slot)[c] = __float_as_uint(scale);
           }
         }
@@ -742,8 +742,8 @@ __global__ void __launch_bounds__(256) symm_all_gather_int8_kernel(const AgArgs 
       const long long c = g * GROUP_CHUNKS + it * 8 + warp;
       if (c >= nc) break;
       const float scale = __uint_as_float(__ldcg(reinterpret_cast<const uint32_t*>(slot) + c));
-      const uint4* rec = reinterpret_cast<const uint4*>(slot + L.hdr_bytes + c * V2_SLOT_BYTES + lane * 32);
-      const uint4 q0 = __ldcg(rec), q1 = __ldcg(rec + 1);
+      const uint4* rec = reinterpret_cast<const uint4*>(slot + L.hdr_bytes + c * V2_SLOT_BYTES) + lane;
+      const uint4 q0 = __ldcg(rec), q1 = __ldcg(rec + 32);
       const uint32_t qw[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
       LaneIn o;
 #pragma unroll
