@@ -160,3 +160,32 @@ def _work_case(rank, world):
 
 def test_aggregated_work_semantics():
     run_ranks(_work_case, 2)
+
+
+def _verbatim_case(rank, world):
+    """``wire="verbatim"`` away from the fused transport: the all-gather is the plain library
+    collective, the reduce-scatter keeps its arithmetic (same result as the compressed wire)."""
+    import torch.distributed as dist
+    from fsdp_comm_opt_b200.parallel.hooks import ZipCCLAllGather, ZipCCLReduceScatter
+
+    g = torch.Generator().manual_seed(50 + rank)
+    x = (torch.randn(5000, generator=g) * 0.02).to(torch.bfloat16)
+    out = torch.zeros(world * 5000, dtype=torch.bfloat16)
+    ref = torch.zeros_like(out)
+    dist.all_gather_into_tensor(ref, x)
+    hook = ZipCCLAllGather(wire="verbatim")
+    w = hook(out, x, dist.group.WORLD, async_op=True)
+    if w is not None:
+        w.wait()
+    assert torch.equal(_bits(out), _bits(ref)) and hook.last_transport == "lib"
+    rows = torch.randn(world * 3000, generator=g) * 1e-3
+    o1, o2 = torch.zeros(3000), torch.zeros(3000)
+    ZipCCLReduceScatter(wire="verbatim")(o1, rows.clone(), dist.group.WORLD, dist.ReduceOp.AVG)
+    ZipCCLReduceScatter()(o2, rows.clone(), dist.group.WORLD, dist.ReduceOp.AVG)
+    assert torch.equal(o1, o2)
+    with pytest.raises(ValueError):
+        ZipCCLAllGather(wire="zstd")
+
+
+def test_verbatim_wire_on_the_library_transport():
+    run_ranks(_verbatim_case, 2)
