@@ -62,7 +62,8 @@ def test_flag_surface_matches_reference():
            "-s", "--seq-length", "--cpu-offload", "-p", "--profiler", "--profiler-wait", "--profiler-warmup",
            "--profiler-active", "--forward-prefetch-distance", "-q", "--quantize", "--zip-ccl"}
     assert ref <= opts
-    assert {"--synthetic", "--model-shape", "--device", "--compress-rs", "--act-ckpt", "--steps"} <= opts
+    assert {"--synthetic", "--model-shape", "--device", "--compress-rs", "--act-ckpt", "--steps", "--wire",
+            "--transport", "--codec", "--sharding"} <= opts
 
 
 def _gpt2_quant_actckpt(rank, world, loss_log):
@@ -75,6 +76,15 @@ def test_gpt2_family_int8_hook_and_activation_checkpointing(tmp_path):
     run_ranks(_gpt2_quant_actckpt, 2, init_pg=False, args=(log,))
     ls = _losses(log)
     assert len(ls) == 3 and all(8.0 < l < 10.0 for l in ls)
+
+
+def test_verbatim_wire_trains_like_the_compressed_one(tmp_path):
+    """``--wire verbatim`` changes what crosses the links, not the arithmetic: same loss curve."""
+    a, b = str(tmp_path / "a.log"), str(tmp_path / "b.log")
+    common = ["--steps", "4", "-q", "--zip-ccl", "--compress-rs", "--model-shape", "gpt2-tiny"]
+    run_ranks(_train, 2, init_pg=False, args=(common, a))
+    run_ranks(_train, 2, init_pg=False, args=(common + ["--wire", "verbatim"], b))
+    assert _losses(a) == _losses(b) and len(_losses(a)) == 4
 
 
 def _heartbeat_case(rank, world):
