@@ -210,6 +210,7 @@ __global__ void __launch_bounds__(RN_THREADS) rmsnorm_bwd_kernel(
   for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
     const float rstd = rstd_in[row];
     float g[MAXV][8], xh[MAXV][8];
+    BF8 eh[MAXV];  // the residual-path gradient, fetched with the other operands: one memory round trip per row
     float dot = 0.f;
 #pragma unroll
     for (int i = 0; i < MAXV; ++i) {
@@ -218,6 +219,7 @@ __global__ void __launch_bounds__(RN_THREADS) rmsnorm_bwd_kernel(
         float d[8];
         unpack8(ld8(dy + row * cols + v * 8), d);
         unpack8(ld8(h + row * cols + v * 8), xh[i]);
+        if (dh) eh[i] = ld8(dh + row * cols + v * 8);
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
           xh[i][j] *= rstd;
@@ -237,7 +239,7 @@ __global__ void __launch_bounds__(RN_THREADS) rmsnorm_bwd_kernel(
         for (int j = 0; j < 8; ++j) o[j] = rstd * (g[i][j] - xh[i][j] * dot);
         if (dh) {
           float e[8];
-          unpack8(ld8(dh + row * cols + v * 8), e);
+          unpack8(eh[i], e);
 #pragma unroll
           for (int j = 0; j < 8; ++j) o[j] += e[j];
         }
