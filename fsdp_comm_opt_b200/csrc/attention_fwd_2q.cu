@@ -5,7 +5,7 @@
 // every K/V block it loads.  Key blocks hold 64 keys, so a softmax thread owns a whole score row
 // of a block (64 fp32 registers): no partner thread, no exchange through shared memory, and the
 // row maximum, the exponentials and the row sum come from one read of TMEM.
-//   warp 0      TMA producer: both Q tiles once, then K/V blocks into a three-stage ring
+//   warp 0      TMA producer: both Q tiles once, then K/V blocks into a four-stage ring
 //   warps 1,10  MMA issuers, one per tile: S_t = Q_t K_j^T (128 x 64, fp32 in TMEM) and
 //               O_t += P_t V_j with the output accumulating in TMEM for the whole row of blocks
 //   warps 2-5   softmax of tile 0, warps 6-9 softmax of tile 1, one thread per query row.  A
@@ -15,8 +15,12 @@
 // The running maximum is only raised when the new block's maximum exceeds it by more than 2^8
 // (exponentials stay below 256, exact enough in bf16 and fp32); raising it rescales the row of O in
 // TMEM (tcgen05.ld, multiply, tcgen05.st), which after the first few blocks almost never happens.
-// TMEM (512 columns allocated): S_0 64 | S_1 64 | O_0 128 | O_1 128.
-// Shared memory: Q 2 x 32 KB, K/V ring 3 x (16 + 16) KB, P 2 tiles x 2 block parities x 16 KB.
+// The probabilities never touch shared memory: a softmax thread writes its row of P_t as bf16 pairs
+// into tensor memory (tcgen05.st) and O_t += P_t V_j takes its A operand from there, so that MMA
+// fetches only V from shared memory.
+// TMEM (512 columns allocated): S_0 64 | S_1 64 | O_0 128 | O_1 128 | P: tile t, block parity u at
+// 384 + (2 t + u) * 32 (64 keys as 32 columns).
+// Shared memory: Q 2 x 32 KB, K/V ring 4 x (16 + 16) KB.
 // CTAs are numbered heaviest first (the last 256 queries see the most keys).  Every wait is
 // bounded; a timed-out role raises a CTA-wide abort flag, the CTA frees its TMEM and returns, and the
 // launcher's status word reports it.
@@ -37,7 +41,7 @@ using namespace attn;
 
 constexpr int THREADS = 352;
 constexpr int KB = 64;          // keys per block
-constexpr int STAGES = 3;       // K/V ring
+constexpr int STAGES = 4;       // K/V ring
 constexpr float RAISE = 8.f;    // log2 of the factor by which a row maximum may lag behind
 
 struct Params {
@@ -70,7 +74,6 @@ __global__ void __launch_bounds__(THREADS, 1) attn_fwd_2q_kernel(const __grid_co
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sQ = smem;              // tile t at t * 32 KB: two 64-column slabs of [128 x 128 B]
   uint8_t* sKV = smem + 65536;     // stage s at s * 32 KB: K (two slabs of [64 x 128 B]), then V
-  uint8_t* sP = smem + 65536 + STAGES * 32768;  // tile t, block parity u at (2 t + u) * 16 KB: [128 rows x 64 keys] bf16
   __shared__ uint64_t q_full, kv_full[STAGES], kv_empty[STAGES], s_full[2], s_empty[2], p_full[2], o_full[4];  // o_full[2 t + (j & 1)]
   __shared__ uint32_t tmem_base;
   __shared__ volatile int s_abort;
@@ -140,15 +143,14 @@ __global__ void __launch_bounds__(THREADS, 1) attn_fwd_2q_kernel(const __grid_co
       const int t = warp == 1 ? 0 : 1;
       const uint32_t id_s = idesc_bf16(128, KB, MAJOR_K, MAJOR_K);
       const uint32_t id_o = idesc_bf16(128, D, MAJOR_K, MAJOR_MN);
-      const uint32_t aQ = smem_u32(sQ) + t * 32768, aKV = smem_u32(sKV), aP = smem_u32(sP) + t * 32768;
-      const uint32_t tm_s = tm + t * 64, tm_o = tm + 128 + t * 128;
+      const uint32_t aQ = smem_u32(sQ) + t * 32768, aKV = smem_u32(sKV);
+      const uint32_t tm_s = tm + t * 64, tm_o = tm + 128 + t * 128, tm_p = tm + 384 + t * 64;
       const int nbt = nb[t];
       // descriptors at offset 0 of each operand; byte offsets are added to the start-address field as
       // offset >> 4 (shared memory is below 256 KB, the 14-bit field never carries)
       const uint64_t dQ0 = smem_desc(aQ, 16, 1024);               // Q tile, K-major, 16 KB slabs
       const uint64_t dK0 = smem_desc(aKV, 16, 1024);              // K block of stage 0, K-major, 8 KB slabs
       const uint64_t dV0 = smem_desc(aKV + 16384, 8192, 1024);    // V block of stage 0, MN-major
-      const uint64_t dP0 = smem_desc(aP, 16, 1024);               // P tile of parity 0, K-major
       bool ok = role_wait(&q_full, 0, &s_abort);
       // S_t(j) = Q_t K_j^T: A = Q tile (K-major, 16 KB slabs), B = K block (K-major, 8 KB slabs)
       auto issue_s = [&](int j) -> bool {
@@ -179,12 +181,12 @@ __global__ void __launch_bounds__(THREADS, 1) attn_fwd_2q_kernel(const __grid_co
         if (!(ok = role_wait(&p_full[t], j & 1, &s_abort))) break;
         tc_fence_after_sync();
         if (t == 0) ZC_TRACE(1, j, 2);
-        // O_t += P_t V_j: A = P tile [128 x 64 keys] K-major, B = V block [64 keys x 128] MN-major
+        // O_t += P_t V_j: A = P tile [128 x 64 keys] in tensor memory, B = V block [64 keys x 128] MN-major
         const uint64_t dV = dV0 + (uint64_t)((j % STAGES) * (32768 >> 4));
-        const uint64_t dP = dP0 + (uint64_t)((j & 1) * (16384 >> 4));
+        const uint32_t tP = tm_p + (uint32_t)((j & 1) * 32);
 #pragma unroll
         for (int k = 0; k < KB / 16; ++k)
-          mma_bf16(tm_o, dP + (uint64_t)((k * 32) >> 4), dV + (uint64_t)((k * 2048) >> 4), id_o, (j | k) != 0);
+          mma_bf16_tmem_a(tm_o, tP + (uint32_t)(k * 8), dV + (uint64_t)((k * 2048) >> 4), id_o, (j | k) != 0);
         mma_commit(&o_full[2 * t + (j & 1)]);
         mma_commit(&kv_empty[j % STAGES]);  // this tile's readers of the stage have been issued
         if (t == 0) ZC_TRACE(1, j, 3);
@@ -199,7 +201,7 @@ __global__ void __launch_bounds__(THREADS, 1) attn_fwd_2q_kernel(const __grid_co
     const int row = qt0 + r;
     const int nbt = nb[t];
     const uint32_t lane_base = (uint32_t)(quarter * 32);
-    const uint32_t tm_s = tm + t * 64, tm_o = tm + 128 + t * 128;
+    const uint32_t tm_s = tm + t * 64, tm_o = tm + 128 + t * 128, tm_p = tm + 384 + t * 64;
     const float sl2 = p.scale * LOG2E;
     float m_ref = -CUDART_INF_F, l = 0.f;
     bool fail = false;
@@ -247,7 +249,6 @@ __global__ void __launch_bounds__(THREADS, 1) attn_fwd_2q_kernel(const __grid_co
       if (tr) ZC_TRACE(0, j, 3);
       // P_t is double-buffered by block parity: block j's buffer was last read by P_t V of block
       // j-2, which has long completed (the wait returns at once for j < 2)
-      uint8_t* tp = sP + (2 * t + (j & 1)) * 16384;
       fail = !mbar_wait_parked(&o_full[2 * t + (j & 1)], ((j >> 1) & 1) ^ 1, &s_abort);
       if (__any_sync(0xffffffffu, fail || s_abort)) { fail = true; break; }
       if (j > 0 && __any_sync(0xffffffffu, raise)) {
@@ -270,6 +271,7 @@ __global__ void __launch_bounds__(THREADS, 1) attn_fwd_2q_kernel(const __grid_co
       }
       if (tr) ZC_TRACE(0, j, 4);
       float rs4[4] = {0.f, 0.f, 0.f, 0.f};
+      uint32_t pk[32];  // the row of P as bf16 pairs: column c holds keys 2 c (low half) and 2 c + 1
 #pragma unroll
       for (int q = 0; q < 8; ++q) {
         const uint32_t* src = q < 4 ? &sa[q * 8] : &sb[(q - 4) * 8];
@@ -279,12 +281,13 @@ __global__ void __launch_bounds__(THREADS, 1) attn_fwd_2q_kernel(const __grid_co
           e[i] = exp2f(__uint_as_float(src[i]) * sl2 - m_use);
           rs4[i & 3] += e[i];
         }
-        *reinterpret_cast<uint4*>(tp + sw128_off(r, q)) =
-            make_uint4(pack_bf16(e[0], e[1]), pack_bf16(e[2], e[3]), pack_bf16(e[4], e[5]), pack_bf16(e[6], e[7]));
+#pragma unroll
+        for (int i = 0; i < 4; ++i) pk[q * 4 + i] = pack_bf16(e[2 * i], e[2 * i + 1]);
       }
+      tmem_st32(tmem_addr(tm_p + (uint32_t)((j & 1) * 32), lane_base, 0), pk);
       l += (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
+      tmem_st_wait();
       if (tr) ZC_TRACE(0, j, 5);
-      fence_proxy_async_smem();
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&p_full[t]);
@@ -387,7 +390,7 @@ int zc_attn_fwd_2q(const void* q, const void* k, const void* v, void* o, float* 
   p.ncb = (S + 255) / 256;
   p.trace = g_trace;
   if (!p.status) return ERR_BAD_ARG;
-  const int smem = 65536 + STAGES * 32768 + 4 * 16384 + 1024;
+  const int smem = 65536 + STAGES * 32768 + 1024;
   static bool attr = false;
   if (!attr) { cudaFuncSetAttribute(attn_fwd_2q_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); attr = true; }
   attn_fwd_2q_kernel<<<p.ncb * Hq * B, THREADS, smem, st>>>(mq, mk, mv, p);
