@@ -29,6 +29,7 @@ from __future__ import annotations
 
 import argparse
 import contextlib
+import math
 import os
 from pathlib import Path
 
@@ -265,6 +266,10 @@ def main(argv=None):
                 loss_value = outputs.loss.item()  # the one host synchronisation of a step
                 if device.type == "cuda":
                     check_device_status()  # an expired device-side wait becomes an exception here
+                if not math.isfinite(loss_value):
+                    # stop before the next checkpoint can save the state: the last good one is on disk
+                    raise FloatingPointError(f"non-finite loss {loss_value} at step {state['global_step']} "
+                                             f"on rank {rank}; resume from the last checkpoint")
                 state["running_loss"] += loss_value
                 if args.loss_log and rank == 0:
                     with open(args.loss_log, "a") as fp:
