@@ -2,6 +2,7 @@
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
         -m fsdp_comm_opt_b200.parallel.bench_collectives [--min-log2 20 --max-log2 30 --iters 4]
+        [--budget exclusive|in-step]
 
 For total tensor sizes 2^20 .. 2^30 elements (powers of 4) it times
   * all-gather of bf16 shards   (parameter-like N(0, 0.02) data): fused symm kernel vs NCCL
@@ -13,6 +14,9 @@ measured wire bytes per element, the max abs error against NCCL, and the achieve
 NVLink roofline (compressed bytes that must leave a GPU / 770 GB/s measured peer bandwidth).
 Timing: CUDA events on the launching stream, 2 warm-up calls, max over ranks; inputs alternate
 between two buffers so consecutive calls do not hit the same L2 lines for sizes under the L2.
+``--budget exclusive`` (default): the collective is alone on the GPU, as in this sweep, and gets the
+CTA budget of the whole machine (``hook.exclusive = True``); ``--budget in-step``: the budget it has
+inside a training step, which leaves room for the GEMMs and for a second collective in flight.
 """
 from __future__ import annotations
 
@@ -52,6 +56,7 @@ def main():
     ap.add_argument("--max-log2", type=int, default=30)
     ap.add_argument("--iters", type=int, default=4)
     ap.add_argument("--transport", default="symm", choices=["symm", "lib"])
+    ap.add_argument("--budget", default="exclusive", choices=["exclusive", "in-step"])
     args = ap.parse_args()
     rank, world, device = init_distributed("cuda")
     from . import symm_impl
@@ -59,6 +64,7 @@ def main():
     group = dist.group.WORLD
     ag = ZipCCLAllGather(transport=args.transport)
     rs = ZipCCLReduceScatter(transport=args.transport)
+    ag.exclusive = rs.exclusive = args.budget == "exclusive"
     for lg in range(args.min_log2, args.max_log2 + 1, 2):
         total = 1 << lg
         shard = total // world
@@ -80,7 +86,7 @@ def main():
         wire_pe = (w1 - w0) / ((args.iters + 2) * shard * (world - 1)) if ch else None
         roof_ms = (wire_pe * shard * (world - 1) / (PEER_GBS * 1e6)) if wire_pe else None
         if rank == 0:
-            print(json.dumps({"op": "all_gather", "elements": total, "world": world, "data": "params N(0,0.02)",
+            print(json.dumps({"op": "all_gather", "elements": total, "world": world, "budget": args.budget, "data": "params N(0,0.02)",
                               "zip_ms": round(ms_z, 4), "nccl_ms": round(ms_n, 4),
                               "zip_bus_gbs": round(payload * (world - 1) / world / ms_z / 1e6, 1),
                               "nccl_bus_gbs": round(payload * (world - 1) / world / ms_n / 1e6, 1),
@@ -112,7 +118,7 @@ def main():
         wire_pe = (w1 - w0) / ((args.iters + 2) * shard * (world - 1)) if ch else None
         roof_ms = (wire_pe * shard * (world - 1) / (PEER_GBS * 1e6)) if wire_pe else None
         if rank == 0:
-            print(json.dumps({"op": "reduce_scatter", "elements": total, "world": world,
+            print(json.dumps({"op": "reduce_scatter", "elements": total, "world": world, "budget": args.budget,
                               "data": "grads N(0,1e-3) + 1% x100 outliers, fp32 input",
                               "zip_ms": round(ms_z, 4), "nccl_ms": round(ms_n, 4),
                               "zip_bus_gbs": round(payload * (world - 1) / world / ms_z / 1e6, 1),
@@ -133,7 +139,7 @@ def main():
         ms_n = _timed(lambda i: dist.reduce_scatter_tensor(ref16, scratch[i & 1], op=dist.ReduceOp.AVG), args.iters, device)
         payload = 2.0 * shard * world
         if rank == 0:
-            print(json.dumps({"op": "reduce_scatter_bf16", "elements": total, "world": world,
+            print(json.dumps({"op": "reduce_scatter_bf16", "elements": total, "world": world, "budget": args.budget,
                               "data": "same gradients as bf16 rows; NCCL column = bf16 reduce-scatter (bf16 accumulation)",
                               "zip_ms": round(ms_z, 4), "nccl_ms": round(ms_n, 4),
                               "zip_bus_gbs": round(payload * (world - 1) / world / ms_z / 1e6, 1),

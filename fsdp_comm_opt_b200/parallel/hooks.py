@@ -57,9 +57,14 @@ class _CommBase:
 
     ``urgent`` (read at call time; the sharding engine sets it per call): False when the collective
     runs in the shadow of compute and may take a small share of the SMs, True when the step waits
-    for it.  Only the fused symmetric-memory transport looks at it."""
+    for it.  ``exclusive``: set it when nothing else of this process runs on the GPU beside the
+    collective (a stand-alone gather or reduce, as in the collective sweep); the kernel then gets
+    the CTA budget of the whole machine instead of the share that leaves room for a training
+    step's GEMMs and for a second collective in flight.  Only the fused symmetric-memory transport
+    looks at either."""
 
     urgent = True
+    exclusive = False
 
     def allocate(self, size, *, dtype, device):
         return torch.empty(size, dtype=dtype, device=device)
@@ -207,7 +212,8 @@ class ZipCCLAllGather(_CommBase):
             from . import symm_impl as symm
 
             return symm.channel_for(group, x.device, "ag").all_gather(
-                output_tensor, x, mode="zip", async_op=async_op, urgent=self.urgent, verbatim=self.wire == "verbatim")
+                output_tensor, x, mode="zip", async_op=async_op, urgent=self.urgent, verbatim=self.wire == "verbatim",
+                exclusive=self.exclusive)
         if self.wire == "verbatim":
             return dist.all_gather_into_tensor(output_tensor, x, group=group, async_op=async_op)
         if version == "v2":
@@ -367,7 +373,7 @@ class ZipCCLReduceScatter(_CommBase):
 
             return symm.channel_for(group, x.device, "rs").reduce_scatter(
                 output_tensor, x, scale=scale, residual=self._residual_for(x), async_op=async_op, urgent=self.urgent,
-                verbatim=self.wire == "verbatim")
+                verbatim=self.wire == "verbatim", exclusive=self.exclusive)
         return self._lib(output_tensor, x, group, world, scale, async_op)
 
     def _lib(self, output_tensor, x, group, world, scale, async_op):

@@ -123,7 +123,7 @@ class Channel:
         self.elements = 0
         sm = torch.cuda.get_device_properties(device).multi_processor_count
         # The codec is integer-ALU work, the GEMMs it overlaps with are tensor-pipe work, and a
-        # collective CTA needs only 16 KB of shared memory, so two of them fit beside a GEMM CTA on
+        # collective CTA needs only 8 KB of shared memory, so two of them fit beside a GEMM CTA on
         # every SM.  One pusher and one decoder CTA per SM keeps the wall time of a collective
         # short; fewer CTAs make it encode-bound (measured: 24+37 CTAs -> 89 GB/s bus at 2 GPUs).
         # Progress argument for two collectives in flight at once (FSDP overlaps the next all-gather
@@ -141,6 +141,16 @@ class Channel:
         # step).  So background collectives default to the full budget too; ZC_SYMM_BG_* lowers it.
         self.bg_push_ctas = int(os.environ.get("ZC_SYMM_BG_PUSH_CTAS", str(self.push_ctas)))
         self.bg_dec_ctas = int(os.environ.get("ZC_SYMM_BG_DEC_CTAS", str(self.dec_ctas)))
+        # Budget of a collective that has the GPU to itself (``exclusive=True``: no GEMM resident, no
+        # second collective whose pushers need slots, so the progress argument above does not bind).
+        # Measured at four ranks, 2^28 elements: the all-gather is bound by its decoders (148 + 276 CTAs:
+        # 0.56 ms against 0.68 ms with the in-step budget, NCCL 0.76 ms), the reduce-scatter by both halves
+        # (296 + 296: 0.87 ms against 1.02 ms, NCCL fp32 1.36 ms); more all-gather pushers than one per SM
+        # only take issue slots from its decoders (296 + 296: 0.66 ms).
+        if kind == "rs":
+            self.excl_push_ctas, self.excl_dec_ctas = 2 * sm, 2 * sm
+        else:
+            self.excl_push_ctas, self.excl_dec_ctas = sm, max(8, 2 * sm - 20)
         self._lib = _lib.cuda()
         self._lib._lib.zc_symm_buffer_bytes.restype = ctypes.c_int64
         self._lib._lib.zc_symm_buffer_bytes.argtypes = [ctypes.c_int, ctypes.c_int64]
@@ -227,12 +237,14 @@ class Channel:
         return int(self._ctrl()[CW_WIRE_LO:CW_WIRE_LO + 2].view(torch.int64).item())
 
     # -- collectives -----------------------------------------------------------------------------
-    def _budget(self, urgent: bool):
+    def _budget(self, urgent: bool, exclusive: bool = False):
+        if exclusive:
+            return self.excl_push_ctas, self.excl_dec_ctas
         return (self.push_ctas, self.dec_ctas) if urgent else (min(self.push_ctas, self.bg_push_ctas),
                                                                 min(self.dec_ctas, self.bg_dec_ctas))
 
     def all_gather(self, output_tensor: torch.Tensor, x: torch.Tensor, mode: str = "zip", async_op: bool = False,
-                   urgent: bool = True, verbatim: bool = False):
+                   urgent: bool = True, verbatim: bool = False, exclusive: bool = False):
         """``mode="zip"``: lossless v2 codec, or with ``verbatim`` the raw bf16 bytes on the same
         protocol.  ``mode="int8"``: per-shard absmax int8 (every rank, the source included, ends
         up with the dequantised values)."""
@@ -244,7 +256,7 @@ class Channel:
         self.reserve(n)
         seq = self._next_seq()
         fn = self._lib.zc_symm_all_gather if mode == "zip" else self._lib.zc_symm_all_gather_int8
-        push, dec = self._budget(urgent)
+        push, dec = self._budget(urgent, exclusive)
         args = (x.data_ptr(), output_tensor.data_ptr(), self.peers_dev, self.local_ptr, self.mc_ptr or None, n, self.rank,
                 self.world, self.nc_max, seq, push, dec, self.timeout_s)
         if mode == "zip":
@@ -260,7 +272,7 @@ class Channel:
         return AggregatedWork([], ready_event=ev)
 
     def reduce_scatter(self, output_tensor: torch.Tensor, x: torch.Tensor, scale: float, residual, async_op=False,
-                       urgent: bool = True, verbatim: bool = False):
+                       urgent: bool = True, verbatim: bool = False, exclusive: bool = False):
         shard = x.numel() // self.world
         if output_tensor.numel() != shard or output_tensor.dtype not in (torch.float32, torch.bfloat16):
             raise ValueError("output must hold numel/world fp32 or bf16 elements")
@@ -268,7 +280,7 @@ class Channel:
             raise TypeError("the fused reduce-scatter keeps its residual in bf16")
         self.reserve(shard)
         seq = self._next_seq()
-        push, dec = self._budget(urgent)
+        push, dec = self._budget(urgent, exclusive)
         _lib.check(self._lib.zc_symm_reduce_scatter(
             x.data_ptr(), output_tensor.data_ptr(), _lib.ptr(residual), self.peers_dev, self.local_ptr, shard,
             self.rank, self.world, self.nc_max, seq, int(x.dtype == torch.float32),
