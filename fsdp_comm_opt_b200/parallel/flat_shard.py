@@ -149,6 +149,7 @@ class ShardGroup:
         self.ag_hook = None
         self.rs_hook = None
         self.grads_ready = False  # gradient buffer handed out for this backward
+        self.view_cache = {}      # (buffer address, dtype) -> (buffer, per-parameter views)
 
 
 @dataclass
@@ -289,9 +290,24 @@ class FlatShardEngine:
                     repl[id(p)] = q
                 mod._parameters[name] = q
 
+    @staticmethod
+    def _slot_views(g: ShardGroup, flat: torch.Tensor):
+        """Per-parameter views of a flat buffer of this group's layout.  The buffers come from small
+        pools and return every step, so the views are made once per buffer and kept (with a reference
+        to the buffer, which makes its address a safe key): a step then costs one attribute store per
+        parameter instead of a slice, a view and their dispatch."""
+        key = (flat.data_ptr(), flat.dtype)
+        hit = g.view_cache.get(key)
+        if hit is None:
+            if len(g.view_cache) >= 8:
+                g.view_cache.pop(next(iter(g.view_cache)))
+            hit = (flat, [flat[s.offset:s.offset + s.numel].view(s.shape) for s in g.slots])
+            g.view_cache[key] = hit
+        return hit[1]
+
     def _replace_param_storage(self, g: ShardGroup, flat: torch.Tensor) -> None:
-        for s in g.slots:
-            s.param.data = flat[s.offset:s.offset + s.numel].view(s.shape)
+        for s, v in zip(g.slots, self._slot_views(g, flat)):
+            s.param.data = v
 
     def _materialize(self) -> None:
         """Initialise every group's parameters (the same values on every rank: every rank draws the
@@ -420,8 +436,8 @@ class FlatShardEngine:
     # gradients
     # ------------------------------------------------------------------------------------------
     def _set_main_grads(self, g: ShardGroup) -> None:
-        for s in g.slots:
-            s.param.main_grad = g.full_grad[s.offset:s.offset + s.numel].view(s.shape)
+        for s, v in zip(g.slots, self._slot_views(g, g.full_grad)):
+            s.param.main_grad = v
             s.param.main_grad_written = False
 
     def _prepare_grads(self, g: ShardGroup) -> None:
