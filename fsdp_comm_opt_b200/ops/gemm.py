@@ -80,7 +80,8 @@ def gemm(a: torch.Tensor, b: torch.Tensor, trans_a: bool, trans_b: bool,
         kind = None
     if kind is not None:
         if out is None:
-            out = torch.empty(M, _pad8(N), dtype=a.dtype, device=a.device)[:, :N]
+            out = torch.empty(M, N, dtype=a.dtype, device=a.device) if N % 8 == 0 else \
+                torch.empty(M, _pad8(N), dtype=a.dtype, device=a.device)[:, :N]
             accumulate = False
         lib = _lib.cuda()
         if kind == "2sm":
