@@ -102,7 +102,7 @@ def parse_args():
                     help="reference arm: its shipped run uses -q --zip-ccl (zip)")
     ap.add_argument("--transport", default="auto", choices=["auto", "symm", "lib"])
     ap.add_argument("--no-compress", action="store_true", help="ours: stock NCCL collectives")
-    ap.add_argument("--wire", default="compressed", choices=["compressed", "verbatim"],
+    ap.add_argument("--wire", default="compressed", choices=["compressed", "nibble", "verbatim"],
                     help="ours: what the fused collectives move (verbatim = raw bf16 bytes, no codec work; a "
                          "comparison arm, the headline configuration is compressed)")
     ap.add_argument("--act-ckpt", action="store_true")
@@ -139,7 +139,9 @@ def make_ours(args, device):
     info = {"gemm_backend": gemm.get_backend(), "native_lib": str(_lib.cuda_lib_path()), "sharding": args.sharding,
             "reshard_after_forward": eng.flat.reshard_after_forward if eng.flat is not None else True,
             "comm_requested": ("nccl" if not comp else "zip all-gather + compressed reduce-scatter"
-                               if args.wire == "compressed" else "fused all-gather + reduce-scatter, verbatim bf16 wire")}
+                               if args.wire == "compressed" else
+                               "zip all-gather + compressed reduce-scatter, nibble-mode records" if args.wire == "nibble"
+                               else "fused all-gather + reduce-scatter, verbatim bf16 wire")}
     make_ours.engine = eng
     return eng.step_on_device, eng.step, info, _lib
 

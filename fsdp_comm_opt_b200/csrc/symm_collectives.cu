@@ -182,8 +182,11 @@ __device__ __forceinline__ bool warp_wait_flag(const uint32_t* fl, uint32_t want
   return ok != 0;
 }
 
-template <bool VERBATIM>
-__global__ void __launch_bounds__(256) symm_all_gather_kernel(const AgArgs a) {
+// WIRE: 0 = v2 records (bit planes), 1 = verbatim bf16, 2 = v2 records in nibble mode
+// (three CTAs per SM by registers: two of them still fit beside a resident GEMM CTA and a
+// reduce-scatter CTA, which is what the CTA budgets assume)
+template <int WIRE>
+__global__ void __launch_bounds__(256, 3) symm_all_gather_kernel(const AgArgs a) {
   // pushers: the record's tail (planes, escapes, raw exponents), its first 1024 bytes go out straight
   // from registers; decoders: escape staging.  8 KB, so that two collective CTAs fit beside a GEMM CTA.
   __shared__ __align__(16) uint8_t srec[8][V2_SLOT_BYTES / 2];
@@ -222,7 +225,7 @@ __global__ void __launch_bounds__(256) symm_all_gather_kernel(const AgArgs a) {
         LaneIn li;
         load_lane(a.in + e0, a.n - e0, in_al, li);
         if (copy_own) store_lane(own + e0, a.n - e0, own_al, li);
-        if constexpr (VERBATIM) {
+        if constexpr (WIRE == 1) {
           if (!ZC_SLOT_OK(L, c, V2_SLOT_BYTES, a.local, L.rank)) continue;
           if (a.mc) {
             uint8_t* rec = slot_ptr(a.mc, L, parity, L.rank) + L.hdr_bytes + c * V2_SLOT_BYTES;
@@ -240,7 +243,8 @@ __global__ void __launch_bounds__(256) symm_all_gather_kernel(const AgArgs a) {
         }
         LaneSplit s;
         split_lane(li, s);
-        const uint32_t hdr = v2_encode_chunk_hint<false>(s, srec[warp] - 1024, lane, hint, hint_esc);
+        const uint32_t hdr = WIRE == 2 ? v2_encode_chunk_nibble(s, srec[warp] - 1024, lane)
+                                       : v2_encode_chunk_hint<false>(s, srec[warp] - 1024, lane, hint, hint_esc);
         __syncwarp();
         const int used = v2_record_bytes(hdr);
         if (!ZC_SLOT_OK(L, c, used, a.local, L.rank)) {
@@ -300,15 +304,15 @@ __global__ void __launch_bounds__(256) symm_all_gather_kernel(const AgArgs a) {
     const uint8_t* recs = slot + L.hdr_bytes + c0 * V2_SLOT_BYTES;
     uint16_t* dst = a.out + (long long)src * a.n;
     const bool al = (reinterpret_cast<uintptr_t>(dst) & 15) == 0;
-    if constexpr (VERBATIM) {
+    if constexpr (WIRE == 1) {
       // a copy: all loads of the slice first, then the stores
-      for (int k0 = 0; k0 < cnt; k0 += 4) {
-        LaneIn v[4];
+      for (int k0 = 0; k0 < cnt; k0 += 2) {
+        LaneIn v[2];
 #pragma unroll
-        for (int k = 0; k < 4; ++k)
+        for (int k = 0; k < 2; ++k)
           if (k0 + k < cnt) load_verbatim(recs + (long long)(k0 + k) * V2_SLOT_BYTES, lane, v[k]);
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {
+        for (int k = 0; k < 2; ++k) {
           if (k0 + k >= cnt) continue;
           const long long e0 = (c0 + k0 + k) * V2_CHUNK_ELEMS + lane * 32;
           store_lane(dst + e0, a.n - e0, al, v[k]);
@@ -321,12 +325,12 @@ __global__ void __launch_bounds__(256) symm_all_gather_kernel(const AgArgs a) {
     // its own instruction stream, and the extra registers cost a resident CTA)
     const uint32_t myhdr = lane < cnt ? __ldcg(reinterpret_cast<const uint32_t*>(slot) + c0 + lane) : 0u;
     RecRegs cur, nxt;
-    v2_prefetch<true>(recs, __shfl_sync(FULL, myhdr, 0), lane, cur);
+    v2_prefetch<true, WIRE == 2>(recs, __shfl_sync(FULL, myhdr, 0), lane, cur);
     for (int k = 0; k < cnt; ++k) {
       const uint32_t hn = __shfl_sync(FULL, myhdr, (k + 1) & 7);
-      if (k + 1 < cnt) v2_prefetch<true>(recs + (long long)(k + 1) * V2_SLOT_BYTES, hn, lane, nxt);
+      if (k + 1 < cnt) v2_prefetch<true, WIRE == 2>(recs + (long long)(k + 1) * V2_SLOT_BYTES, hn, lane, nxt);
       LaneSplit s;
-      v2_decode_regs(cur, esc, lane, s);
+      v2_decode_regs<WIRE == 2>(cur, esc, lane, s);
       LaneIn o;
       join_lane(s, o);
       const long long e0 = (c0 + k) * V2_CHUNK_ELEMS + lane * 32;
@@ -424,7 +428,8 @@ __device__ __forceinline__ void store_lane_scaled(void* out, int out_fp32, long 
   }
 }
 
-template <bool VERBATIM>
+// WIRE: 0 = v2 records (bit planes), 1 = verbatim bf16, 2 = v2 records in nibble mode
+template <int WIRE>
 __global__ void __launch_bounds__(256, 2) symm_reduce_scatter_kernel(const RsArgs a) {
   // pushers: the record's tail (planes, escapes, raw exponents), its first 1024 bytes go out straight
   // from registers; decoders: escape staging.  8 KB, so that two collective CTAs fit beside a GEMM CTA.
@@ -484,7 +489,7 @@ __global__ void __launch_bounds__(256, 2) symm_reduce_scatter_kernel(const RsArg
 #pragma unroll
           for (int k = 0; k < 16; ++k) li.w[k] = f_to_bf16_bits(v[2 * k]) | (f_to_bf16_bits(v[2 * k + 1]) << 16);
         }
-        if constexpr (VERBATIM) {
+        if constexpr (WIRE == 1) {
           if (!ZC_SLOT_OK(L, c, V2_SLOT_BYTES, a.local, q)) continue;
           store_verbatim(slot + L.hdr_bytes + c * V2_SLOT_BYTES, lane, li);
           if (lane == 0) pushed += (unsigned long long)V2_SLOT_BYTES;
@@ -492,7 +497,8 @@ __global__ void __launch_bounds__(256, 2) symm_reduce_scatter_kernel(const RsArg
         }
         LaneSplit s;
         split_lane(li, s);
-        const uint32_t hdr = v2_encode_chunk_hint<false>(s, srec[warp] - 1024, lane, hint, hint_esc);
+        const uint32_t hdr = WIRE == 2 ? v2_encode_chunk_nibble(s, srec[warp] - 1024, lane)
+                                       : v2_encode_chunk_hint<false>(s, srec[warp] - 1024, lane, hint, hint_esc);
         __syncwarp();
         const int used = v2_record_bytes(hdr);
         if (!ZC_SLOT_OK(L, c, used, a.local, q)) {
@@ -540,7 +546,7 @@ __global__ void __launch_bounds__(256, 2) symm_reduce_scatter_kernel(const RsArg
       if (lane == 0) *okp = 0;
       break;
     }
-    if constexpr (VERBATIM) {
+    if constexpr (WIRE == 1) {
       for (int k = 0; k < cnt; ++k) {
         const long long c = c0 + k;
         const long long e0 = c * V2_CHUNK_ELEMS + lane * 32;
@@ -565,7 +571,7 @@ __global__ void __launch_bounds__(256, 2) symm_reduce_scatter_kernel(const RsArg
     const uint8_t* myslot = slot_ptr(a.local, L, parity, is_src ? lane : p0);
     uint32_t myhdr = is_src ? __ldcg(reinterpret_cast<const uint32_t*>(myslot) + c0) : 0u;
     RecRegs cur, nxt;
-    v2_prefetch<true>(slot_ptr(a.local, L, parity, p0) + L.hdr_bytes + c0 * V2_SLOT_BYTES, __shfl_sync(FULL, myhdr, p0), lane,
+    v2_prefetch<true, WIRE == 2>(slot_ptr(a.local, L, parity, p0) + L.hdr_bytes + c0 * V2_SLOT_BYTES, __shfl_sync(FULL, myhdr, p0), lane,
                 cur);
     for (int k = 0; k < cnt; ++k) {
       const long long c = c0 + k;
@@ -581,14 +587,14 @@ __global__ void __launch_bounds__(256, 2) symm_reduce_scatter_kernel(const RsArg
         int pn = p + 1;
         if (pn == L.rank) ++pn;
         if (pn < L.world) {
-          v2_prefetch<true>(slot_ptr(a.local, L, parity, pn) + L.hdr_bytes + c * V2_SLOT_BYTES, __shfl_sync(FULL, myhdr, pn),
+          v2_prefetch<true, WIRE == 2>(slot_ptr(a.local, L, parity, pn) + L.hdr_bytes + c * V2_SLOT_BYTES, __shfl_sync(FULL, myhdr, pn),
                       lane, nxt);
         } else if (k + 1 < cnt) {
-          v2_prefetch<true>(slot_ptr(a.local, L, parity, p0) + L.hdr_bytes + (c + 1) * V2_SLOT_BYTES,
+          v2_prefetch<true, WIRE == 2>(slot_ptr(a.local, L, parity, p0) + L.hdr_bytes + (c + 1) * V2_SLOT_BYTES,
                       __shfl_sync(FULL, nexthdr, p0), lane, nxt);
         }
         LaneSplit s;
-        v2_decode_regs(cur, esc, lane, s);
+        v2_decode_regs<WIRE == 2>(cur, esc, lane, s);
         LaneIn o;
         join_lane(s, o);
 #pragma unroll
@@ -806,10 +812,11 @@ long long zc_symm_buffer_bytes(int world, long long nc_max) {
 
 // in: n bf16 elements; out: world*n; peers: device array of `world` buffer pointers
 // mc: multicast mapping of the symmetric buffer (NVSwitch), or null to push with per-peer stores
-// verbatim: 0 = v2 records (compressed), 1 = the bf16 bytes as they are
+// wire: 0 = v2 records (bit planes, about 1.40 bytes per element), 1 = the bf16 bytes as they are,
+// 2 = v2 records in nibble mode (about 1.50 bytes per element, roughly half the codec instructions)
 int zc_symm_all_gather(const void* in, void* out, void* const* peers, void* local, void* mc, long long n, int rank,
                        int world, long long nc_max, unsigned seq, int push_ctas, int dec_ctas, double timeout_s,
-                       int verbatim, cudaStream_t st) {
+                       int wire, cudaStream_t st) {
   ZC_NVTX_RANGE("zc_symm_all_gather");
   using namespace zc;
   const long long nc = (n + V2_CHUNK_ELEMS - 1) / V2_CHUNK_ELEMS;
@@ -820,7 +827,7 @@ int zc_symm_all_gather(const void* in, void* out, void* const* peers, void* loca
     return ERR_BAD_ARG;
   AgArgs a;
   a.in = (const uint16_t*)in; a.out = (uint16_t*)out; a.peers = (uint8_t* const*)peers; a.local = (uint8_t*)local;
-  a.mc = (uint8_t*)mc; a.n = n; a.seq = seq; a.verbatim = verbatim ? 1 : 0;
+  a.mc = (uint8_t*)mc; a.n = n; a.seq = seq; a.verbatim = wire == 1;
   a.timeout_ns = (unsigned long long)(timeout_s * 1e9);
   a.L = make_layout(world, rank, nc_max);
   a.gc = pick_group_chunks(nc, sm_count(), a.L.max_groups);
@@ -829,15 +836,16 @@ int zc_symm_all_gather(const void* in, void* out, void* const* peers, void* loca
   a.push_ctas = (int)std::min<long long>(push_ctas, ngroups);
   const long long dec_items = ngroups * (world - 1) * (a.gc / 8);
   const int dec = (int)std::min<long long>(dec_ctas, (dec_items + 7) / 8);
-  if (a.verbatim) symm_all_gather_kernel<true><<<a.push_ctas + dec, 256, 0, st>>>(a);
-  else symm_all_gather_kernel<false><<<a.push_ctas + dec, 256, 0, st>>>(a);
+  if (wire == 1) symm_all_gather_kernel<1><<<a.push_ctas + dec, 256, 0, st>>>(a);
+  else if (wire == 2) symm_all_gather_kernel<2><<<a.push_ctas + dec, 256, 0, st>>>(a);
+  else symm_all_gather_kernel<0><<<a.push_ctas + dec, 256, 0, st>>>(a);
   return launch_status();
 }
 
 int zc_symm_reduce_scatter(const void* in, void* out, void* residual, void* const* peers, void* local,
                            long long shard, int rank, int world, long long nc_max, unsigned seq, int in_fp32,
                            int out_fp32, float scale, int push_ctas, int dec_ctas, double timeout_s,
-                           int verbatim, cudaStream_t st) {
+                           int wire, cudaStream_t st) {
   ZC_NVTX_RANGE("zc_symm_reduce_scatter");
   using namespace zc;
   const long long nc = (shard + V2_CHUNK_ELEMS - 1) / V2_CHUNK_ELEMS;
@@ -846,7 +854,7 @@ int zc_symm_reduce_scatter(const void* in, void* out, void* residual, void* cons
   RsArgs a;
   a.in = in; a.out = out; a.residual = (uint16_t*)residual; a.peers = (uint8_t* const*)peers;
   a.local = (uint8_t*)local; a.shard = shard; a.seq = seq; a.in_fp32 = in_fp32;
-  a.out_fp32 = out_fp32; a.scale = scale; a.verbatim = verbatim ? 1 : 0;
+  a.out_fp32 = out_fp32; a.scale = scale; a.verbatim = wire == 1;
   a.timeout_ns = (unsigned long long)(timeout_s * 1e9);
   a.L = make_layout(world, rank, nc_max);
   // a pusher item is (destination, group): world - 1 times as many items as groups
@@ -856,8 +864,9 @@ int zc_symm_reduce_scatter(const void* in, void* out, void* residual, void* cons
   a.push_ctas = (int)std::min<long long>(push_ctas, ngroups * (world - 1));
   const long long dec_items = ngroups * (a.gc / 8);
   const int dec = (int)std::min<long long>(dec_ctas, (dec_items + 7) / 8);
-  if (a.verbatim) symm_reduce_scatter_kernel<true><<<a.push_ctas + dec, 256, 0, st>>>(a);
-  else symm_reduce_scatter_kernel<false><<<a.push_ctas + dec, 256, 0, st>>>(a);
+  if (wire == 1) symm_reduce_scatter_kernel<1><<<a.push_ctas + dec, 256, 0, st>>>(a);
+  else if (wire == 2) symm_reduce_scatter_kernel<2><<<a.push_ctas + dec, 256, 0, st>>>(a);
+  else symm_reduce_scatter_kernel<0><<<a.push_ctas + dec, 256, 0, st>>>(a);
   return launch_status();
 }
 

@@ -52,6 +52,11 @@ def _resolve_transport(transport: str, device: torch.device, group) -> str:
     return "symm" if symm.available(group) else "lib"
 
 
+# what the fused transport moves: v2 records with bit planes (smallest), v2 records in nibble mode
+# (about 7 % larger, roughly half the codec instructions), or the raw bf16 bytes
+WIRES = ("compressed", "nibble", "verbatim")
+
+
 class _CommBase:
     """Shared ``allocate`` (plain caching-allocator buffers, like the reference hooks).
 
@@ -142,10 +147,14 @@ class ZipCCLAllGather(_CommBase):
     are gathered with two collectives and no host sync; on ``"symm"`` only the used bytes of each
     record cross NVLink.
 
-    ``wire="verbatim"`` (fused ``"symm"`` transport only) runs the same one-kernel push / flag /
-    gather protocol on the raw bf16 bytes, with no codec work: for links with bandwidth to spare,
-    where the codec's instructions cost the kernels running beside the collective more than the
-    bytes saved.  On the ``"lib"`` transport it is a plain library all-gather.
+    ``wire`` (fused ``"symm"`` transport only): ``"compressed"`` moves v2 records with bit planes
+    (about 1.40 bytes per element); ``"nibble"`` the same records with the 4-bit codes packed two per
+    byte and the window anchored at the chunk's largest exponent (about 1.50 bytes per element for
+    roughly half the codec instructions; still lossless); ``"verbatim"`` runs the same one-kernel
+    push / flag / gather protocol on the raw bf16 bytes with no codec work, for links with bandwidth
+    to spare, where the codec's instructions cost the kernels running beside the collective more
+    than the bytes saved.  On the ``"lib"`` transport ``"verbatim"`` is a plain library all-gather
+    and ``"nibble"`` the same as ``"compressed"``.
 
     Non-bf16 inputs are gathered uncompressed (the reference value-casts them to bf16, which is
     lossy for fp32 and wrong for FSDP's mixed-dtype uint8 buffers).
@@ -155,7 +164,7 @@ class ZipCCLAllGather(_CommBase):
 
     def __init__(self, base_exponent: int = 122, base_update_interval: int = 16, *,
                  codec_version: str = "auto", transport: str = "auto", wire: str = "compressed"):
-        if wire not in ("compressed", "verbatim"):
+        if wire not in WIRES:
             raise ValueError(f"unknown wire format {wire!r}")
         self.wire = wire
         self.base_exponent = base_exponent
@@ -212,7 +221,7 @@ class ZipCCLAllGather(_CommBase):
             from . import symm_impl as symm
 
             return symm.channel_for(group, x.device, "ag").all_gather(
-                output_tensor, x, mode="zip", async_op=async_op, urgent=self.urgent, verbatim=self.wire == "verbatim",
+                output_tensor, x, mode="zip", async_op=async_op, urgent=self.urgent, wire=self.wire,
                 exclusive=self.exclusive)
         if self.wire == "verbatim":
             return dist.all_gather_into_tensor(output_tensor, x, group=group, async_op=async_op)
@@ -314,9 +323,10 @@ class ZipCCLReduceScatter(_CommBase):
     The sum is scaled according to ``op`` (SUM, AVG or NCCL's PreMulSum) and written to
     ``output_tensor``.  Wire volume is about 1.4 B/element instead of 4 (fp32 NCCL).
 
-    ``wire="verbatim"`` (fused ``"symm"`` transport only): the same kernel and the same arithmetic
-    (bf16 rounding with error feedback, fp32 sum in rank order) with the bf16 rows pushed as they
-    are, 2 B/element and no codec work.
+    ``wire="nibble"`` / ``"verbatim"`` (fused ``"symm"`` transport only): the same kernel and the same
+    arithmetic (bf16 rounding with error feedback, fp32 sum in rank order, hence the same bits) with
+    the rows encoded in nibble mode (about 1.5 B/element) or pushed as they are (2 B/element, no
+    codec work).
 
     The residual is training state: ``state_dict()`` / ``load_state_dict()`` expose it so a
     checkpoint can carry it per rank.
@@ -324,7 +334,7 @@ class ZipCCLReduceScatter(_CommBase):
 
     def __init__(self, error_feedback: bool = True, reduce_dtype: Optional[torch.dtype] = None, *,
                  residual_dtype: torch.dtype = torch.bfloat16, transport: str = "auto", wire: str = "compressed"):
-        if wire not in ("compressed", "verbatim"):
+        if wire not in WIRES:
             raise ValueError(f"unknown wire format {wire!r}")
         self.wire = wire
         self.error_feedback = error_feedback
@@ -373,7 +383,7 @@ class ZipCCLReduceScatter(_CommBase):
 
             return symm.channel_for(group, x.device, "rs").reduce_scatter(
                 output_tensor, x, scale=scale, residual=self._residual_for(x), async_op=async_op, urgent=self.urgent,
-                verbatim=self.wire == "verbatim", exclusive=self.exclusive)
+                wire=self.wire, exclusive=self.exclusive)
         return self._lib(output_tensor, x, group, world, scale, async_op)
 
     def _lib(self, output_tensor, x, group, world, scale, async_op):

@@ -107,6 +107,9 @@ def why_unavailable(group) -> str:
     return _WHY.get(key, "")
 
 
+_WIRE_CODE = {"compressed": 0, "verbatim": 1, "nibble": 2}
+
+
 class Channel:
     def __init__(self, group, device: torch.device, kind: str):
         self.group, self.device, self.kind = group, device, kind
@@ -244,9 +247,9 @@ class Channel:
                                                                 min(self.dec_ctas, self.bg_dec_ctas))
 
     def all_gather(self, output_tensor: torch.Tensor, x: torch.Tensor, mode: str = "zip", async_op: bool = False,
-                   urgent: bool = True, verbatim: bool = False, exclusive: bool = False):
-        """``mode="zip"``: lossless v2 codec, or with ``verbatim`` the raw bf16 bytes on the same
-        protocol.  ``mode="int8"``: per-shard absmax int8 (every rank, the source included, ends
+                   urgent: bool = True, wire: str = "compressed", exclusive: bool = False):
+        """``mode="zip"``: lossless v2 codec (``wire`` "compressed" or "nibble"), or with ``wire="verbatim"`` the
+        raw bf16 bytes on the same protocol.  ``mode="int8"``: per-shard absmax int8 (every rank, the source included, ends
         up with the dequantised values)."""
         if mode not in ("zip", "int8"):
             raise ValueError(f"unknown all-gather mode {mode!r}")
@@ -260,7 +263,7 @@ class Channel:
         args = (x.data_ptr(), output_tensor.data_ptr(), self.peers_dev, self.local_ptr, self.mc_ptr or None, n, self.rank,
                 self.world, self.nc_max, seq, push, dec, self.timeout_s)
         if mode == "zip":
-            args += (int(verbatim),)
+            args += (_WIRE_CODE[wire],)
         _lib.check(fn(*args, _lib.stream_ptr(self.device)), "zc_symm_all_gather")
         self.calls += 1
         self.elements += n * (self.world - 1)
@@ -272,7 +275,7 @@ class Channel:
         return AggregatedWork([], ready_event=ev)
 
     def reduce_scatter(self, output_tensor: torch.Tensor, x: torch.Tensor, scale: float, residual, async_op=False,
-                       urgent: bool = True, verbatim: bool = False, exclusive: bool = False):
+                       urgent: bool = True, wire: str = "compressed", exclusive: bool = False):
         shard = x.numel() // self.world
         if output_tensor.numel() != shard or output_tensor.dtype not in (torch.float32, torch.bfloat16):
             raise ValueError("output must hold numel/world fp32 or bf16 elements")
@@ -285,7 +288,7 @@ class Channel:
             x.data_ptr(), output_tensor.data_ptr(), _lib.ptr(residual), self.peers_dev, self.local_ptr, shard,
             self.rank, self.world, self.nc_max, seq, int(x.dtype == torch.float32),
             int(output_tensor.dtype == torch.float32), float(scale), push, dec,
-            self.timeout_s, int(verbatim), _lib.stream_ptr(self.device)), "zc_symm_reduce_scatter")
+            self.timeout_s, _WIRE_CODE[wire], _lib.stream_ptr(self.device)), "zc_symm_reduce_scatter")
         self.calls += 1
         self.elements += shard * (self.world - 1)
         return self._work() if async_op else None

@@ -194,13 +194,13 @@ def _verbatim_case(rank, world):
         g = torch.Generator().manual_seed(99 + rank)
         x = (torch.randn(world * shard, generator=g) * 1e-3).to(dtype).to(dev)
         outs = []
-        for wire in ("compressed", "verbatim"):
+        for wire in ("compressed", "verbatim", "nibble"):
             hook = ZipCCLReduceScatter(transport="symm", wire=wire)
             o = torch.zeros(shard, dtype=dtype, device=dev)
             hook(o, x.clone(), grp, dist.ReduceOp.AVG)
             torch.cuda.synchronize()
             outs.append(o)
-        assert torch.equal(outs[0], outs[1]), dtype
+        assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2]), dtype
     for c in symm_impl.all_channels():
         c.check_status()
         c.check_canaries()
@@ -257,7 +257,7 @@ def _back_to_back_case(rank, world, wire):
         c.check_canaries()
 
 
-@pytest.mark.parametrize("wire", ["compressed", "verbatim"])
+@pytest.mark.parametrize("wire", ["compressed", "nibble", "verbatim"])
 def test_back_to_back_collectives_without_host_sync(wire):
     run_ranks(_back_to_back_case, WORLD, (wire,), backend="nccl")
 

@@ -41,17 +41,17 @@ class _World:
     def status(self, r):
         return self.bufs[r][:4096].view(torch.int32)[65:68].tolist()
 
-    def all_gather(self, rank, x, out, push, dec, seq=1, verbatim=False):
+    def all_gather(self, rank, x, out, push, dec, seq=1, wire=0):
         _lib.check(self.lib.zc_symm_all_gather(
             x.data_ptr(), out.data_ptr(), self.ptrs.data_ptr(), self.bufs[rank].data_ptr(), None, x.numel(), rank,
-            self.world, self.nc_max, seq, push, dec, 1.0, int(verbatim), _lib.stream_ptr(DEV)), "zc_symm_all_gather")
+            self.world, self.nc_max, seq, push, dec, 1.0, wire, _lib.stream_ptr(DEV)), "zc_symm_all_gather")
 
-    def reduce_scatter(self, rank, x, out, push, dec, seq=1, scale=1.0, verbatim=False):
+    def reduce_scatter(self, rank, x, out, push, dec, seq=1, scale=1.0, wire=0):
         shard = x.numel() // self.world
         _lib.check(self.lib.zc_symm_reduce_scatter(
             x.data_ptr(), out.data_ptr(), None, self.ptrs.data_ptr(), self.bufs[rank].data_ptr(), shard, rank,
             self.world, self.nc_max, seq, int(x.dtype == torch.float32), int(out.dtype == torch.float32), scale,
-            push, dec, 1.0, int(verbatim), _lib.stream_ptr(DEV)), "zc_symm_reduce_scatter")
+            push, dec, 1.0, wire, _lib.stream_ptr(DEV)), "zc_symm_reduce_scatter")
 
 
 def _params(n, seed, outliers=False):
@@ -63,16 +63,40 @@ def _params(n, seed, outliers=False):
     return x.bfloat16()
 
 
-@pytest.mark.parametrize("verbatim", [False, True], ids=["compressed", "verbatim"])
+@pytest.mark.parametrize("wire", [0, 2, 1], ids=["compressed", "nibble", "verbatim"])
 @pytest.mark.parametrize("world,n", [(2, 1 << 20), (4, 300_001), (8, 1 << 18), (8, 5000)])
-def test_fused_all_gather_ranks_in_sequence(world, n, verbatim):
+def test_fused_all_gather_ranks_in_sequence(world, n, wire):
     w = _World(world, n)
     shards = [_params(n, 10 + r, outliers=(r % 2 == 1)) for r in range(world)]
     scratch = torch.empty(world * n, dtype=torch.bfloat16, device=DEV)
     for r in range(1, world):                      # the other ranks: encode and push only
-        w.all_gather(r, shards[r], scratch, push=32, dec=0, verbatim=verbatim)
+        w.all_gather(r, shards[r], scratch, push=32, dec=0, wire=wire)
     out = torch.zeros(world * n, dtype=torch.bfloat16, device=DEV)
-    w.all_gather(0, shards[0], out, push=32, dec=64, verbatim=verbatim)   # rank 0: push, then decode what has arrived
+    w.all_gather(0, shards[0], out, push=32, dec=64, wire=wire)   # rank 0: push, then decode what has arrived
+    torch.cuda.synchronize()
+    assert w.status(0) == [0, 0, 0] and w.canaries_intact()
+    assert torch.equal(out.view(torch.int16), torch.cat(shards).view(torch.int16))
+
+
+@pytest.mark.parametrize("wire", [0, 2], ids=["compressed", "nibble"])
+def test_fused_all_gather_adversarial_bit_patterns(wire):
+    """Inputs that reach every branch of the record coder: random bit patterns (exponents all over the range:
+    the raw fallback), zeros (one exponent: width 0), exponent fields below 15 (window base 0), and a
+    Gaussian body with a few huge values (escapes below the window of the nibble mode)."""
+    world, n = 4, 96 * 1024 + 77
+    g = torch.Generator(device="cuda").manual_seed(5)
+    rnd = torch.randint(0, 65536, (n,), device=DEV, generator=g, dtype=torch.int32).to(torch.int16).view(torch.bfloat16)
+    tiny = (torch.randint(0, 15 << 7, (n,), device=DEV, generator=g, dtype=torch.int32)
+            | (torch.randint(0, 2, (n,), device=DEV, generator=g, dtype=torch.int32) << 15)).to(torch.int16).view(torch.bfloat16)
+    body = (torch.randn(n, device=DEV, generator=g) * 1e-3).bfloat16()
+    body[::1500] = 3.0e4
+    shards = [rnd, torch.zeros(n, dtype=torch.bfloat16, device=DEV), tiny, body]
+    w = _World(world, n)
+    scratch = torch.empty(world * n, dtype=torch.bfloat16, device=DEV)
+    for r in range(1, world):
+        w.all_gather(r, shards[r], scratch, push=16, dec=0, wire=wire)
+    out = torch.zeros(world * n, dtype=torch.bfloat16, device=DEV)
+    w.all_gather(0, shards[0], out, push=16, dec=32, wire=wire)
     torch.cuda.synchronize()
     assert w.status(0) == [0, 0, 0] and w.canaries_intact()
     assert torch.equal(out.view(torch.int16), torch.cat(shards).view(torch.int16))
@@ -80,15 +104,15 @@ def test_fused_all_gather_ranks_in_sequence(world, n, verbatim):
 
 @pytest.mark.parametrize("world,shard,dtype", [(2, 1 << 19, torch.bfloat16), (4, 70_000, torch.float32),
                                                (8, 1 << 16, torch.bfloat16), (8, 3000, torch.bfloat16)])
-@pytest.mark.parametrize("verbatim", [False, True], ids=["compressed", "verbatim"])
-def test_fused_reduce_scatter_ranks_in_sequence(world, shard, dtype, verbatim):
+@pytest.mark.parametrize("wire", [0, 2, 1], ids=["compressed", "nibble", "verbatim"])
+def test_fused_reduce_scatter_ranks_in_sequence(world, shard, dtype, wire):
     w = _World(world, shard)
     rows = [(_params(world * shard, 40 + r, outliers=True).float() * 0.05).bfloat16().to(dtype) for r in range(world)]
     dummy = torch.empty(shard, dtype=torch.float32, device=DEV)
     for r in range(1, world):
-        w.reduce_scatter(r, rows[r], dummy, push=48, dec=0, verbatim=verbatim)
+        w.reduce_scatter(r, rows[r], dummy, push=48, dec=0, wire=wire)
     out = torch.zeros(shard, dtype=torch.float32, device=DEV)
-    w.reduce_scatter(0, rows[0], out, push=48, dec=64, scale=1.0 / world, verbatim=verbatim)
+    w.reduce_scatter(0, rows[0], out, push=48, dec=64, scale=1.0 / world, wire=wire)
     torch.cuda.synchronize()
     assert w.status(0) == [0, 0, 0] and w.canaries_intact()
     # the kernel adds its own row first, then the sources by rank, in fp32

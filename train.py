@@ -87,7 +87,7 @@ def _get_parser() -> argparse.ArgumentParser:
     p.add_argument("--steps", default=None, type=int)
     p.add_argument("--transport", default="auto", choices=["auto", "symm", "lib"])
     p.add_argument("--codec", default="auto", choices=["auto", "v1", "v2"])
-    p.add_argument("--wire", default="compressed", choices=["compressed", "verbatim"],
+    p.add_argument("--wire", default="compressed", choices=["compressed", "nibble", "verbatim"],
                    help="what the fused collectives move: v2 records, or the raw bf16 bytes on the same one-kernel "
                         "protocol (no codec work; for links with bandwidth to spare)")
     p.add_argument("--master-dtype", default="bf16", choices=["bf16", "fp32"])
