@@ -102,9 +102,10 @@ def parse_args():
                     help="reference arm: its shipped run uses -q --zip-ccl (zip)")
     ap.add_argument("--transport", default="auto", choices=["auto", "symm", "lib"])
     ap.add_argument("--no-compress", action="store_true", help="ours: stock NCCL collectives")
-    ap.add_argument("--wire", default="compressed", choices=["compressed", "nibble", "verbatim"],
-                    help="ours: what the fused collectives move (verbatim = raw bf16 bytes, no codec work; a "
-                         "comparison arm, the headline configuration is compressed)")
+    ap.add_argument("--wire", default="nibble", choices=["nibble", "compressed", "verbatim"],
+                    help="ours: what the fused collectives move: lossless exponent-coded records in nibble mode "
+                         "(default) or with bit planes (compressed: the smallest wire), or the raw bf16 bytes "
+                         "(verbatim: a comparison arm without codec work)")
     ap.add_argument("--act-ckpt", action="store_true")
     ap.add_argument("--gemm", default=None, choices=[None, "auto", "tcgen05", "tcgen05_2sm", "cublas"])
     ap.add_argument("--reshard-after-forward", default="auto", choices=["auto", "true", "false"],
@@ -138,9 +139,9 @@ def make_ours(args, device):
                                        args.reshard_after_forward]), device)
     info = {"gemm_backend": gemm.get_backend(), "native_lib": str(_lib.cuda_lib_path()), "sharding": args.sharding,
             "reshard_after_forward": eng.flat.reshard_after_forward if eng.flat is not None else True,
-            "comm_requested": ("nccl" if not comp else "zip all-gather + compressed reduce-scatter"
-                               if args.wire == "compressed" else
-                               "zip all-gather + compressed reduce-scatter, nibble-mode records" if args.wire == "nibble"
+            "comm_requested": ("nccl" if not comp else "zip all-gather + compressed reduce-scatter (nibble-mode records)"
+                               if args.wire == "nibble" else
+                               "zip all-gather + compressed reduce-scatter (bit-plane records)" if args.wire == "compressed"
                                else "fused all-gather + reduce-scatter, verbatim bf16 wire")}
     make_ours.engine = eng
     return eng.step_on_device, eng.step, info, _lib

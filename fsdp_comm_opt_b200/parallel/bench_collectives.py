@@ -2,7 +2,7 @@
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
         -m fsdp_comm_opt_b200.parallel.bench_collectives [--min-log2 20 --max-log2 30 --iters 4]
-        [--budget exclusive|in-step]
+        [--budget exclusive|in-step] [--wire nibble|compressed|verbatim]
 
 For total tensor sizes 2^20 .. 2^30 elements (powers of 4) it times
   * all-gather of bf16 shards   (parameter-like N(0, 0.02) data): fused symm kernel vs NCCL
@@ -57,13 +57,14 @@ def main():
     ap.add_argument("--iters", type=int, default=4)
     ap.add_argument("--transport", default="symm", choices=["symm", "lib"])
     ap.add_argument("--budget", default="exclusive", choices=["exclusive", "in-step"])
+    ap.add_argument("--wire", default="nibble", choices=["nibble", "compressed", "verbatim"])
     args = ap.parse_args()
     rank, world, device = init_distributed("cuda")
     from . import symm_impl
 
     group = dist.group.WORLD
-    ag = ZipCCLAllGather(transport=args.transport)
-    rs = ZipCCLReduceScatter(transport=args.transport)
+    ag = ZipCCLAllGather(transport=args.transport, wire=args.wire)
+    rs = ZipCCLReduceScatter(transport=args.transport, wire=args.wire)
     ag.exclusive = rs.exclusive = args.budget == "exclusive"
     for lg in range(args.min_log2, args.max_log2 + 1, 2):
         total = 1 << lg
@@ -86,7 +87,7 @@ def main():
         wire_pe = (w1 - w0) / ((args.iters + 2) * shard * (world - 1)) if ch else None
         roof_ms = (wire_pe * shard * (world - 1) / (PEER_GBS * 1e6)) if wire_pe else None
         if rank == 0:
-            print(json.dumps({"op": "all_gather", "elements": total, "world": world, "budget": args.budget, "data": "params N(0,0.02)",
+            print(json.dumps({"op": "all_gather", "elements": total, "world": world, "budget": args.budget, "wire": args.wire, "data": "params N(0,0.02)",
                               "zip_ms": round(ms_z, 4), "nccl_ms": round(ms_n, 4),
                               "zip_bus_gbs": round(payload * (world - 1) / world / ms_z / 1e6, 1),
                               "nccl_bus_gbs": round(payload * (world - 1) / world / ms_n / 1e6, 1),
@@ -118,7 +119,7 @@ def main():
         wire_pe = (w1 - w0) / ((args.iters + 2) * shard * (world - 1)) if ch else None
         roof_ms = (wire_pe * shard * (world - 1) / (PEER_GBS * 1e6)) if wire_pe else None
         if rank == 0:
-            print(json.dumps({"op": "reduce_scatter", "elements": total, "world": world, "budget": args.budget,
+            print(json.dumps({"op": "reduce_scatter", "elements": total, "world": world, "budget": args.budget, "wire": args.wire,
                               "data": "grads N(0,1e-3) + 1% x100 outliers, fp32 input",
                               "zip_ms": round(ms_z, 4), "nccl_ms": round(ms_n, 4),
                               "zip_bus_gbs": round(payload * (world - 1) / world / ms_z / 1e6, 1),

@@ -30,7 +30,7 @@ class FSDPPlan:
     reduce_dtype: torch.dtype = torch.float32
     transport: str = "auto"
     codec_version: str = "auto"
-    wire: str = "compressed"         # "compressed" | "verbatim" (fused transport: raw bf16 bytes, no codec work)
+    wire: str = "nibble"             # fused transport: "nibble" | "compressed" (bit planes) | "verbatim" (raw bf16)
     error_feedback: bool = True
     act_ckpt: bool = False
     mesh: Optional[object] = None
