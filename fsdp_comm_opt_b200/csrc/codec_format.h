@@ -43,6 +43,15 @@
 //            go to the smaller width, then the smaller d0; an estimate above 1024 selects raw.
 //            The escapes are then counted exactly; if 128*w + n_esc > 1024 the chunk is stored
 //            raw after all, so a record never exceeds its slot.
+//   nibble mode (streams staged by the fused collectives when the caller asks for it; a property of
+//   the stream, not marked in the record): only widths 0, 4 and 8 occur; a width-4 record is
+//            [sm: 1024 B][codes: 512 B][escapes: n_esc B]
+//            with base = max(emax - 14, 0) and lane l's sixteen code bytes at 1024 + 16 l, byte 4 k + j
+//            of them holding the code of element 32 l + 8 k + j in its low nibble and of element
+//            32 l + 8 k + 4 + j in its high nibble (k = 0..3, j = 0..3); escapes and the raw fallback
+//            (512 + n_esc > 1024) as above.  In the staging buffers of the fused collectives the sm
+//            section of every record is stored as two 512-byte halves (lane l's bytes 0..15 at 16 l,
+//            bytes 16..31 at 512 + 16 l).
 #pragma once
 #include <stdint.h>
 
