@@ -102,6 +102,71 @@ def test_fused_all_gather_adversarial_bit_patterns(wire):
     assert torch.equal(out.view(torch.int16), torch.cat(shards).view(torch.int16))
 
 
+def _decode_staged_records_on_host(buf, world, nc_max, parity, src, n, nibble):
+    """Second oracle for the staging format: rebuild a source's n bf16 values from the bytes the pusher
+    left in a staging buffer, using only the layout rules written down in ``csrc/codec_format.h``
+    (header word, sign+mantissa section in two 512-byte halves, bit planes or nibble-packed codes,
+    escapes in element order, raw records)."""
+    import numpy as np
+
+    b = buf.cpu().numpy()
+    align128 = lambda x: (x + 127) // 128 * 128
+    max_groups = (nc_max + 63) // 64
+    flag_bytes = align128(2 * world * max_groups * 4)
+    hdr_bytes = align128(nc_max * 4)
+    slot_bytes = hdr_bytes + nc_max * 2048
+    slot = 4096 + flag_bytes + parity * world * slot_bytes + src * slot_bytes
+    hdrs = b[slot:slot + hdr_bytes].view(np.uint32)
+    out = np.zeros(((n + 1023) // 1024) * 1024, dtype=np.uint16)
+    for c in range((n + 1023) // 1024):
+        h = int(hdrs[c])
+        base, width, n_esc = h & 0xFF, (h >> 8) & 0xF, h >> 16
+        rec = b[slot + hdr_bytes + c * 2048: slot + hdr_bytes + (c + 1) * 2048]
+        lane = np.arange(1024) // 32
+        j = np.arange(1024) % 32
+        sm = np.where(j < 16, rec[16 * lane + j], rec[512 + 16 * lane + (j - 16)]).astype(np.uint16)
+        if width == 8:
+            ex = rec[1024:2048].astype(np.uint16)
+        elif width == 0:
+            ex = np.full(1024, base, dtype=np.uint16)
+        else:
+            if nibble:
+                assert width == 4
+                k, jj = (j // 8), (j % 8)
+                byte = rec[1024 + 16 * lane + 4 * k + (jj % 4)]
+                code = np.where(jj < 4, byte & 0xF, byte >> 4).astype(np.int32)
+                tail = 1024 + 512
+            else:
+                planes = rec[1024:1024 + 128 * width].view(np.uint32).reshape(width, 32)
+                code = np.zeros(1024, dtype=np.int32)
+                for p_ in range(width):
+                    code |= ((planes[p_][lane] >> j) & 1).astype(np.int32) << p_
+                tail = 1024 + 128 * width
+            esc_pos = np.cumsum(code == 0) - 1
+            assert int((code == 0).sum()) == n_esc
+            esc = rec[tail:tail + max(n_esc, 1)].astype(np.int32)
+            ex = np.where(code == 0, esc[np.clip(esc_pos, 0, max(n_esc, 1) - 1)], base + code - 1).astype(np.uint16)
+        out[c * 1024:(c + 1) * 1024] = (sm & 0x7F) | (ex << 7) | ((sm >> 7) << 15)
+    return torch.from_numpy(out[:n].view(np.int16))
+
+
+@pytest.mark.parametrize("wire", [0, 2], ids=["compressed", "nibble"])
+def test_staged_records_follow_the_documented_layout(wire):
+    world, n = 2, 20 * 1024 + 300
+    g = torch.Generator(device="cuda").manual_seed(9)
+    x = (torch.randn(n, device=DEV, generator=g) * 0.02).bfloat16()
+    x[::700] = 250.0                                  # escapes
+    x[5 * 1024:6 * 1024] = 0.5                        # one exponent: width 0
+    x[7 * 1024:8 * 1024] = torch.randint(0, 65536, (1024,), device=DEV, generator=g, dtype=torch.int32).to(
+        torch.int16).view(torch.bfloat16)             # raw record
+    w = _World(world, n)
+    scratch = torch.empty(world * n, dtype=torch.bfloat16, device=DEV)
+    w.all_gather(1, x, scratch, push=8, dec=0, wire=wire)        # rank 1 pushes into rank 0's buffer, parity of seq 1
+    torch.cuda.synchronize()
+    got = _decode_staged_records_on_host(w.bufs[0], world, w.nc_max, parity=1, src=1, n=n, nibble=(wire == 2))
+    assert torch.equal(got, x.cpu().view(torch.int16))
+
+
 @pytest.mark.parametrize("world,shard,dtype", [(2, 1 << 19, torch.bfloat16), (4, 70_000, torch.float32),
                                                (8, 1 << 16, torch.bfloat16), (8, 3000, torch.bfloat16)])
 @pytest.mark.parametrize("wire", [0, 2, 1], ids=["compressed", "nibble", "verbatim"])
