@@ -468,26 +468,32 @@ __global__ void __launch_bounds__(256, 2) symm_reduce_scatter_kernel(const RsArg
         if (c >= nc) break;
         const long long e0 = c * V2_CHUNK_ELEMS + lane * 32;
         const long long valid = a.shard - e0;
-        float v[32];
-        load_lane_f32(a.in, a.in_fp32, (long long)q * a.shard + e0, valid, v);
         LaneIn li;
-        if (a.residual && a.in_fp32) {
-          uint16_t* rp = a.residual + (long long)q * a.shard + e0;
-          LaneIn r;
-          const bool ral = (reinterpret_cast<uintptr_t>(rp) & 15) == 0;
-          load_lane(rp, valid, ral, r);
-#pragma unroll
-          for (int k = 0; k < 16; ++k) {
-            const float x0 = v[2 * k] + bf16_bits_to_f(r.w[k] & 0xFFFFu);
-            const float x1 = v[2 * k + 1] + bf16_bits_to_f(r.w[k] >> 16);
-            const uint32_t b0 = f_to_bf16_bits(x0), b1 = f_to_bf16_bits(x1);
-            li.w[k] = b0 | (b1 << 16);
-            r.w[k] = f_to_bf16_bits(x0 - bf16_bits_to_f(b0)) | (f_to_bf16_bits(x1 - bf16_bits_to_f(b1)) << 16);
-          }
-          store_lane(rp, valid, ral, r);
+        if (!a.in_fp32) {
+          // bf16 rows go out as they are: no detour through fp32
+          const uint16_t* ip = reinterpret_cast<const uint16_t*>(a.in) + (long long)q * a.shard + e0;
+          load_lane(ip, valid, (reinterpret_cast<uintptr_t>(ip) & 15) == 0, li);
         } else {
+          float v[32];
+          load_lane_f32(a.in, 1, (long long)q * a.shard + e0, valid, v);
+          if (a.residual) {
+            uint16_t* rp = a.residual + (long long)q * a.shard + e0;
+            LaneIn r;
+            const bool ral = (reinterpret_cast<uintptr_t>(rp) & 15) == 0;
+            load_lane(rp, valid, ral, r);
 #pragma unroll
-          for (int k = 0; k < 16; ++k) li.w[k] = f_to_bf16_bits(v[2 * k]) | (f_to_bf16_bits(v[2 * k + 1]) << 16);
+            for (int k = 0; k < 16; ++k) {
+              const float x0 = v[2 * k] + bf16_bits_to_f(r.w[k] & 0xFFFFu);
+              const float x1 = v[2 * k + 1] + bf16_bits_to_f(r.w[k] >> 16);
+              const uint32_t b0 = f_to_bf16_bits(x0), b1 = f_to_bf16_bits(x1);
+              li.w[k] = b0 | (b1 << 16);
+              r.w[k] = f_to_bf16_bits(x0 - bf16_bits_to_f(b0)) | (f_to_bf16_bits(x1 - bf16_bits_to_f(b1)) << 16);
+            }
+            store_lane(rp, valid, ral, r);
+          } else {
+#pragma unroll
+            for (int k = 0; k < 16; ++k) li.w[k] = f_to_bf16_bits(v[2 * k]) | (f_to_bf16_bits(v[2 * k + 1]) << 16);
+          }
         }
         if constexpr (WIRE == 1) {
           if (!ZC_SLOT_OK(L, c, V2_SLOT_BYTES, a.local, q)) continue;

@@ -312,7 +312,10 @@ def test_fsdp_two_gpus_symm_vs_lib_vs_uncompressed(tmp_path):
               args=(["-q", "--zip-ccl", "--compress-rs", "--transport", "symm"], logs["symm"]))
     a, b, c = (_losses(logs[k]) for k in ("none", "lib", "symm"))
     assert len(a) == len(b) == len(c) == 4
-    assert a == b, "lossless all-gather: identical loss curve"
+    # the all-gather is lossless (bit-exact gathers are asserted in _ag_case); the curves themselves agree
+    # to fp32 summation order only: the attention backward adds its dQ tiles with bulk reductions whose
+    # order is not fixed from run to run
+    assert a[0] == b[0] and all(abs(x - y) / x < 5e-4 for x, y in zip(a, b)), (a, b)
     assert all(abs(x - y) / x < 0.01 for x, y in zip(a, c)), (a, c)
 
 
