@@ -124,6 +124,7 @@ class Channel:
         self.timeout_s = float(os.environ.get("ZC_SYMM_TIMEOUT_S", "120"))
         self.calls = 0
         self.elements = 0
+        self._wire_carry = 0   # bytes counted in buffers that were since replaced by larger ones
         sm = torch.cuda.get_device_properties(device).multi_processor_count
         # The codec is integer-ALU work, the GEMMs it overlaps with are tensor-pipe work, and a
         # collective CTA needs only 8 KB of shared memory, so two of them fit beside a GEMM CTA on
@@ -169,6 +170,8 @@ class Channel:
         if self.buf is not None:
             torch.cuda.synchronize(self.device)
             dist.barrier(group=self.group)  # nobody may still be pushing into the old buffer
+            # the byte counter lives in the buffer that is about to be replaced
+            self._wire_carry += int(self._ctrl()[CW_WIRE_LO:CW_WIRE_LO + 2].view(torch.int64).item())
         nc_max = max(nc, 1024)
         nbytes = int(self._lib._lib.zc_symm_buffer_bytes(self.world, nc_max))
         # [guard | buffer the kernels see | guard]: the guards carry a fixed pattern that no kernel may
@@ -237,7 +240,7 @@ class Channel:
         """Bytes this rank has pushed over NVLink on this channel so far (synchronises)."""
         if self.buf is None:
             return 0
-        return int(self._ctrl()[CW_WIRE_LO:CW_WIRE_LO + 2].view(torch.int64).item())
+        return self._wire_carry + int(self._ctrl()[CW_WIRE_LO:CW_WIRE_LO + 2].view(torch.int64).item())
 
     # -- collectives -----------------------------------------------------------------------------
     def _budget(self, urgent: bool, exclusive: bool = False):
