@@ -20,6 +20,8 @@ def declare(lib) -> None:
     # codec
     _sig(lib, "zc_v2_encode", P, L, P, P, P)
     _sig(lib, "zc_v2_decode", P, P, L, P, P)
+    _sig(lib, "zc_v2_encode_nibble", P, L, P, P, P)
+    _sig(lib, "zc_v2_decode_nibble", P, P, L, P, P)
     _sig(lib, "zc_v2_decode_ctas", P, P, L, P, I, P)
     _sig(lib, "zc_v1_encode_split", P, L, P, P, I, P, P, P, P, P, L, P)
     _sig(lib, "zc_v1_encode_fused", P, L, P, I, P, P, P, L, P, P, L, P)

@@ -46,6 +46,8 @@ def cpu() -> ctypes.CDLL:
                 _sig(lib.zc_cpu_v1_decode_fused, None, P, P, P, I, L, P)
                 _sig(lib.zc_cpu_v2_encode, L, P, L, P, P)
                 _sig(lib.zc_cpu_v2_decode, None, P, P, L, P)
+                _sig(lib.zc_cpu_v2_encode_nibble, L, P, L, P, P)
+                _sig(lib.zc_cpu_v2_decode_nibble, None, P, P, L, P)
                 _sig(lib.zc_cpu_v2_compact, L, P, P, L, P, P)
                 _sig(lib.zc_cpu_v2_expand, None, P, P, L, P)
                 _CPU = lib

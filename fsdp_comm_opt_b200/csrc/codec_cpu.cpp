@@ -297,6 +297,82 @@ void zc_cpu_v2_decode(const uint8_t* records, const uint32_t* headers, int64_t n
   }
 }
 
+// Nibble mode (codec_format.h): fixed four code bits, base = max(emax - 14, 0), lane l's sixteen code
+// bytes at 1024 + 16 l, byte 4 k + j holding element 32 l + 8 k + j (low nibble) and 32 l + 8 k + 4 + j
+// (high nibble); width 0, escapes and the raw fallback as in the plane format.
+int64_t zc_cpu_v2_encode_nibble(const uint16_t* in, int64_t n, uint8_t* records, uint32_t* headers) {
+  const int64_t nc = (n + V2_CHUNK_ELEMS - 1) / V2_CHUNK_ELEMS;
+  int64_t used = 0;
+  for (int64_t c = 0; c < nc; ++c) {
+    uint8_t* rec = records + c * V2_SLOT_BYTES;
+    uint8_t ex[V2_CHUNK_ELEMS];
+    int emax = 0, emin = 255;
+    for (int i = 0; i < V2_CHUNK_ELEMS; ++i) {
+      const int64_t g = c * V2_CHUNK_ELEMS + i;
+      const uint16_t v = g < n ? in[g] : (uint16_t)0;
+      rec[i] = bf16_sm(v);
+      ex[i] = bf16_exp(v);
+      if (ex[i] > emax) emax = ex[i];
+      if (ex[i] < emin) emin = ex[i];
+    }
+    uint32_t hdr;
+    if (emin == emax) {
+      hdr = v2_header(emax, 0, 0);
+    } else {
+      const int base = emax > 14 ? emax - 14 : 0;
+      int n_esc = 0;
+      for (int i = 0; i < V2_CHUNK_ELEMS; ++i) n_esc += ((unsigned)((int)ex[i] - base) < 15u) ? 0 : 1;
+      if (512 + n_esc > V2_CHUNK_ELEMS) {
+        hdr = v2_header(0, V2_RAW_WIDTH, 0);
+        std::memcpy(rec + 1024, ex, 1024);
+      } else {
+        hdr = v2_header(base, 4, n_esc);
+        uint8_t* codes = rec + 1024;
+        uint8_t* esc = rec + 1024 + 512;
+        std::memset(codes, 0, 512);
+        int k = 0;
+        for (int i = 0; i < V2_CHUNK_ELEMS; ++i) {
+          const unsigned d = (unsigned)((int)ex[i] - base);
+          const unsigned code = d < 15u ? d + 1 : 0u;
+          const int l = i >> 5, j = i & 31, kk = j >> 3, jj = j & 7;
+          codes[16 * l + 4 * kk + (jj & 3)] |= (uint8_t)(jj < 4 ? code : code << 4);
+          if (code == 0) esc[k++] = ex[i];
+        }
+      }
+    }
+    headers[c] = hdr;
+    used += v2_record_bytes(hdr);
+  }
+  return used;
+}
+
+void zc_cpu_v2_decode_nibble(const uint8_t* records, const uint32_t* headers, int64_t n, uint16_t* out) {
+  const int64_t nc = (n + V2_CHUNK_ELEMS - 1) / V2_CHUNK_ELEMS;
+  for (int64_t c = 0; c < nc; ++c) {
+    const uint8_t* rec = records + c * V2_SLOT_BYTES;
+    const uint32_t hdr = headers[c];
+    const int w = v2_hdr_width(hdr), base = v2_hdr_base(hdr);
+    const uint8_t* codes = rec + 1024;
+    const uint8_t* esc = rec + 1024 + 512;
+    int k = 0;
+    for (int i = 0; i < V2_CHUNK_ELEMS; ++i) {
+      const int64_t g = c * V2_CHUNK_ELEMS + i;
+      uint8_t e;
+      if (w == V2_RAW_WIDTH) {
+        e = rec[1024 + i];
+      } else if (w == 0) {
+        e = (uint8_t)base;
+      } else {
+        const int l = i >> 5, j = i & 31, kk = j >> 3, jj = j & 7;
+        const uint8_t b = codes[16 * l + 4 * kk + (jj & 3)];
+        const unsigned code = jj < 4 ? (b & 0xFu) : (unsigned)(b >> 4);
+        e = code ? (uint8_t)(base + code - 1) : esc[k++];
+      }
+      if (g < n) out[g] = bf16_join(rec[i], e);
+    }
+  }
+}
+
 // Gather the used bytes of every record into one dense stream.  offsets[c] (int64) receives the
 // start of record c; offsets[nc] the total.  Returns the total.
 int64_t zc_cpu_v2_compact(const uint8_t* records, const uint32_t* headers, int64_t nc, uint8_t* dense,

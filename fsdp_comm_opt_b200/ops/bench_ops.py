@@ -126,6 +126,16 @@ def main():
                                                        _lib.stream_ptr()), args.iters, args.warmup)
             emit(kernel="v2_decode_capped", ctas=ctas, elems=n, gbs=round((2 * n + used) / ms_c / 1e6, 1),
                  frac=round((2 * n + used) / ms_c / 1e6 / hbm, 3), frac_of=tag, gelems_per_s=round(n / ms_c / 1e6, 1))
+        rec_n, hdr_n = codec.v2_encode(x, nibble=True)
+        used_n = int(codec.v2_record_bytes(hdr_n).sum().item()) + 4 * hdr_n.numel()
+        ms_en = _time(lambda: codec.v2_encode(x, rec_n, hdr_n, nibble=True), args.iters, args.warmup)
+        ms_dn = _time(lambda: codec.v2_decode(rec_n, hdr_n, n, out, nibble=True), args.iters, args.warmup)
+        emit(kernel="v2_encode_nibble", elems=n, gbs=round((2 * n + used_n) / ms_en / 1e6, 1),
+             frac=round((2 * n + used_n) / ms_en / 1e6 / hbm, 3), frac_of=tag, bytes_per_elem=round(used_n / n, 4),
+             gelems_per_s=round(n / ms_en / 1e6, 1), plane_mode_gelems_per_s=round(n / ms_e / 1e6, 1))
+        emit(kernel="v2_decode_nibble", elems=n, gbs=round((2 * n + used_n) / ms_dn / 1e6, 1),
+             frac=round((2 * n + used_n) / ms_dn / 1e6 / hbm, 3), frac_of=tag,
+             gelems_per_s=round(n / ms_dn / 1e6, 1), plane_mode_gelems_per_s=round(n / ms_d / 1e6, 1))
         emit(kernel="v2_encode", elems=n, gbs=round((2 * n + used) / ms_e / 1e6, 1),
              frac=round((2 * n + used) / ms_e / 1e6 / hbm, 3), frac_of=tag, bytes_per_elem=round(used / n, 4),
              l2="input larger than L2")

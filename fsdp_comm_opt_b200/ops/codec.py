@@ -317,8 +317,11 @@ def v2_num_chunks(numel: int) -> int:
 
 
 def v2_encode(x: torch.Tensor, records: torch.Tensor | None = None,
-              headers: torch.Tensor | None = None):
+              headers: torch.Tensor | None = None, *, nibble: bool = False):
     """Encode a contiguous bf16 tensor into fixed-stride v2 records plus one uint32 header each.
+    ``nibble=True`` writes the records in nibble mode (fixed four code bits packed two per byte,
+    window anchored at the chunk's largest exponent: about 7 % larger, much cheaper to code; the
+    mode is a property of the stream and must be given to ``v2_decode`` again).
 
     Returns ``(records[uint8, nc*2048], headers[int32, nc])``.  The bytes that must travel are
     ``v2_wire_bytes(headers)``; the slot stride equals the raw bf16 size, so the staging buffer
@@ -336,15 +339,16 @@ def v2_encode(x: torch.Tensor, records: torch.Tensor | None = None,
     if nc == 0:
         return records, headers
     if dev.type == "cpu":
-        _lib.cpu().zc_cpu_v2_encode(x.data_ptr(), n, records.data_ptr(), headers.data_ptr())
+        fn = _lib.cpu().zc_cpu_v2_encode_nibble if nibble else _lib.cpu().zc_cpu_v2_encode
+        fn(x.data_ptr(), n, records.data_ptr(), headers.data_ptr())
     else:
-        _lib.check(_lib.cuda().zc_v2_encode(x.data_ptr(), n, records.data_ptr(), headers.data_ptr(),
-                                            _lib.stream_ptr(dev)), "zc_v2_encode")
+        fn = _lib.cuda().zc_v2_encode_nibble if nibble else _lib.cuda().zc_v2_encode
+        _lib.check(fn(x.data_ptr(), n, records.data_ptr(), headers.data_ptr(), _lib.stream_ptr(dev)), "zc_v2_encode")
     return records, headers
 
 
 def v2_decode(records: torch.Tensor, headers: torch.Tensor, numel: int,
-              out: torch.Tensor | None = None) -> torch.Tensor:
+              out: torch.Tensor | None = None, *, nibble: bool = False) -> torch.Tensor:
     nc = v2_num_chunks(numel)
     _req(records, torch.uint8, "records", nc * V2_SLOT)
     _req(headers, torch.int32, "headers", nc)
@@ -355,10 +359,12 @@ def v2_decode(records: torch.Tensor, headers: torch.Tensor, numel: int,
     if nc == 0:
         return out
     if dev.type == "cpu":
-        _lib.cpu().zc_cpu_v2_decode(records.data_ptr(), headers.data_ptr(), numel, out.data_ptr())
+        fn = _lib.cpu().zc_cpu_v2_decode_nibble if nibble else _lib.cpu().zc_cpu_v2_decode
+        fn(records.data_ptr(), headers.data_ptr(), numel, out.data_ptr())
     else:
-        _lib.check(_lib.cuda().zc_v2_decode(records.data_ptr(), headers.data_ptr(), numel,
-                                            out.data_ptr(), _lib.stream_ptr(dev)), "zc_v2_decode")
+        fn = _lib.cuda().zc_v2_decode_nibble if nibble else _lib.cuda().zc_v2_decode
+        _lib.check(fn(records.data_ptr(), headers.data_ptr(), numel, out.data_ptr(), _lib.stream_ptr(dev)),
+                   "zc_v2_decode")
     return out
 
 

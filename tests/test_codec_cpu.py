@@ -228,3 +228,59 @@ def test_v2_window_choice_prefers_bulk_over_rare_large_values():
     h = int(hdr[0]) & 0xFFFFFFFF
     width, nesc = (h >> 8) & 0xF, h >> 16
     assert width == 3 and nesc < 48
+
+
+# ------------------------------------------------------------------ v2, nibble mode
+
+def _decode_nibble_records_with_numpy(rec: torch.Tensor, hdr: torch.Tensor, n: int) -> torch.Tensor:
+    """Independent restatement of the nibble-mode record layout documented in ``csrc/codec_format.h``."""
+    import numpy as np
+
+    b = rec.numpy()
+    h = hdr.numpy().view(np.uint32)
+    nc = (n + 1023) // 1024
+    out = np.zeros(nc * 1024, dtype=np.uint16)
+    lane, j = np.arange(1024) // 32, np.arange(1024) % 32
+    for c in range(nc):
+        r = b[c * 2048:(c + 1) * 2048]
+        base, width, n_esc = int(h[c]) & 0xFF, (int(h[c]) >> 8) & 0xF, int(h[c]) >> 16
+        sm = r[:1024].astype(np.uint16)
+        if width == 8:
+            ex = r[1024:2048].astype(np.uint16)
+        elif width == 0:
+            ex = np.full(1024, base, dtype=np.uint16)
+        else:
+            assert width == 4
+            byte = r[1024 + 16 * lane + 4 * (j // 8) + (j % 4)]
+            code = np.where(j % 8 < 4, byte & 0xF, byte >> 4).astype(np.int32)
+            assert int((code == 0).sum()) == n_esc
+            esc = r[1536:1536 + max(n_esc, 1)].astype(np.int32)
+            pos = np.clip(np.cumsum(code == 0) - 1, 0, max(n_esc, 1) - 1)
+            ex = np.where(code == 0, esc[pos], base + code - 1).astype(np.uint16)
+        out[c * 1024:(c + 1) * 1024] = (sm & 0x7F) | (ex << 7) | ((sm >> 7) << 15)
+    return torch.from_numpy(out[:n].view(np.int16))
+
+
+@pytest.mark.parametrize("n", [1, 1023, 1025, 5000, 1 << 16])
+@pytest.mark.parametrize("maker", [rand_bits, gauss])
+def test_v2_nibble_mode_roundtrip_and_layout(n, maker):
+    x = maker(n, seed=n % 5)
+    rec, hdr = codec.v2_encode(x, nibble=True)
+    assert torch.equal(bits(codec.v2_decode(rec, hdr, n, nibble=True)), bits(x))
+    assert torch.equal(_decode_nibble_records_with_numpy(rec, hdr, n), bits(x))
+    assert set(((hdr.view(torch.int32) >> 8) & 0xF).tolist()) <= {0, 4, 8}
+    assert int(codec.v2_record_bytes(hdr).max()) <= 2048
+
+
+def test_v2_nibble_mode_size_and_escapes():
+    g = torch.Generator().manual_seed(4)
+    x = (torch.randn(1 << 18, generator=g) * 0.02).to(torch.bfloat16)
+    rec_n, hdr_n = codec.v2_encode(x, nibble=True)
+    rec_p, hdr_p = codec.v2_encode(x)
+    bn, bp = codec.v2_wire_bytes(hdr_n) / x.numel(), codec.v2_wire_bytes(hdr_p) / x.numel()
+    assert 1.49 < bn < 1.53 and bp < bn < 1.1 * bp          # 7-8 % more bytes than the bit planes
+    y = x.clone()
+    y[::300] = 2.0                                          # large values move the window up: the smallest elements escape
+    rec, hdr = codec.v2_encode(y, nibble=True)
+    assert int((hdr.view(torch.int32) >> 16).sum()) > 0     # escapes are present
+    assert torch.equal(bits(codec.v2_decode(rec, hdr, y.numel(), nibble=True)), bits(y))

@@ -54,6 +54,23 @@ def test_v2_gpu_matches_cpu_bytes_and_roundtrips(n, maker):
     assert torch.equal(bits(out2), bits(x))
 
 
+@pytest.mark.parametrize("n", [1000, 4097, 1 << 20, (1 << 20) + 77])
+@pytest.mark.parametrize("maker", [gauss, rand_bits])
+def test_v2_nibble_mode_gpu_matches_cpu_bytes_and_roundtrips(n, maker):
+    x = maker(n, seed=4)
+    if maker is gauss:
+        x[::700] = 2.0                                   # escapes below the window
+    rec, hdr = codec.v2_encode(x, nibble=True)
+    rec_c, hdr_c = codec.v2_encode(x.cpu(), nibble=True)
+    assert torch.equal(hdr.cpu(), hdr_c)
+    sizes = codec.v2_record_bytes(hdr_c)
+    mask = torch.arange(2048)[None, :] < sizes[:, None]
+    assert torch.equal(rec.cpu().view(-1, 2048)[mask], rec_c.view(-1, 2048)[mask])
+    assert torch.equal(bits(codec.v2_decode(rec, hdr, n, nibble=True)), bits(x))
+    assert torch.equal(bits(codec.v2_decode(rec_c.to(DEV), hdr_c.to(DEV), n, nibble=True)), bits(x))
+    assert torch.equal(bits(codec.v2_decode(rec.cpu(), hdr.cpu(), n, nibble=True)), bits(x.cpu()))
+
+
 def test_v2_unaligned_output_and_input():
     x = gauss(5000 + 3, seed=5)[3:]          # 6-byte offset: not 16-byte aligned
     rec, hdr = codec.v2_encode(x.contiguous() if False else x)
