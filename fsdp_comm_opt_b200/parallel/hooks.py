@@ -155,8 +155,8 @@ class ZipCCLAllGather(_CommBase):
     links); ``"verbatim"`` runs the same one-kernel
     push / flag / gather protocol on the raw bf16 bytes with no codec work, for links with bandwidth
     to spare, where the codec's instructions cost the kernels running beside the collective more
-    than the bytes saved.  On the ``"lib"`` transport ``"verbatim"`` is a plain library all-gather
-    and ``"nibble"`` the same as ``"compressed"``.
+    than the bytes saved.  On the ``"lib"`` transport the v2 protocol encodes its records in the same
+    mode (the v1 protocol has one format), and ``"verbatim"`` is a plain library all-gather.
 
     Non-bf16 inputs are gathered uncompressed (the reference value-casts them to bf16, which is
     lossy for fp32 and wrong for FSDP's mixed-dtype uint8 buffers).
@@ -238,14 +238,15 @@ class ZipCCLAllGather(_CommBase):
         dev = x.device
         rec_all = torch.empty(world, nc * codec.V2_SLOT, dtype=torch.uint8, device=dev)
         hdr_all = torch.empty(world, nc, dtype=torch.int32, device=dev)
-        codec.v2_encode(x.view(-1), rec_all[rank], hdr_all[rank])
+        nib = self.wire == "nibble"
+        codec.v2_encode(x.view(-1), rec_all[rank], hdr_all[rank], nibble=nib)
         w1 = dist.all_gather_into_tensor(rec_all.view(-1), rec_all[rank], group=group, async_op=async_op)
         w2 = dist.all_gather_into_tensor(hdr_all.view(-1), hdr_all[rank], group=group, async_op=async_op)
         out_flat = output_tensor.view(-1)
 
         def _finish():
             for r in range(world):
-                codec.v2_decode(rec_all[r], hdr_all[r], n, out_flat[r * n:(r + 1) * n])
+                codec.v2_decode(rec_all[r], hdr_all[r], n, out_flat[r * n:(r + 1) * n], nibble=nib)
             _record_streams(rec_all, hdr_all)
 
         if not async_op:
@@ -408,7 +409,7 @@ class ZipCCLReduceScatter(_CommBase):
         send_hdr = torch.empty(world, nc, dtype=torch.int32, device=dev)
         for j in range(world):
             if j != rank:
-                codec.v2_encode(q[j].contiguous(), send_rec[j], send_hdr[j])
+                codec.v2_encode(q[j].contiguous(), send_rec[j], send_hdr[j], nibble=self.wire == "nibble")
         send_hdr[rank].zero_()
         recv_rec = torch.empty_like(send_rec)
         recv_hdr = torch.empty_like(send_hdr)
@@ -424,7 +425,7 @@ class ZipCCLReduceScatter(_CommBase):
                 if j == rank:
                     acc += own.to(torch.float32)
                 else:
-                    codec.v2_decode(recv_rec[j], recv_hdr[j], shard, tmp)
+                    codec.v2_decode(recv_rec[j], recv_hdr[j], shard, tmp, nibble=self.wire == "nibble")
                     acc += tmp.to(torch.float32)
             if scale != 1.0:
                 acc *= scale
