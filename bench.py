@@ -102,7 +102,7 @@ def parse_args():
                     help="reference arm: its shipped run uses -q --zip-ccl (zip)")
     ap.add_argument("--transport", default="auto", choices=["auto", "symm", "lib"])
     ap.add_argument("--no-compress", action="store_true", help="ours: stock NCCL collectives")
-    ap.add_argument("--wire", default="nibble", choices=["nibble", "compressed", "verbatim"],
+    ap.add_argument("--wire", default="auto", choices=["auto", "nibble", "compressed", "verbatim"],
                     help="ours: what the fused collectives move: lossless exponent-coded records in nibble mode "
                          "(default) or with bit planes (compressed: the smallest wire), or the raw bf16 bytes "
                          "(verbatim: a comparison arm without codec work)")
@@ -140,7 +140,7 @@ def make_ours(args, device):
     info = {"gemm_backend": gemm.get_backend(), "native_lib": str(_lib.cuda_lib_path()), "sharding": args.sharding,
             "reshard_after_forward": eng.flat.reshard_after_forward if eng.flat is not None else True,
             "comm_requested": ("nccl" if not comp else "zip all-gather + compressed reduce-scatter (nibble-mode records)"
-                               if args.wire == "nibble" else
+                               if args.wire in ("auto", "nibble") else
                                "zip all-gather + compressed reduce-scatter (bit-plane records)" if args.wire == "compressed"
                                else "fused all-gather + reduce-scatter, verbatim bf16 wire")}
     make_ours.engine = eng

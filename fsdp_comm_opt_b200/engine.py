@@ -40,7 +40,7 @@ class EngineConfig:
     forward_prefetch_distance: int = 1
     transport: str = "auto"
     codec_version: str = "auto"
-    wire: str = "nibble"            # "nibble" | "compressed" | "verbatim": what the fused collectives put on the wire
+    wire: str = "auto"              # "auto" | "nibble" | "compressed" | "verbatim": what the collectives put on the wire
     seed: int = 0
     sharding: str = "flat"          # "flat" | "fsdp2"
     cpu_offload: bool = False       # fsdp2 only

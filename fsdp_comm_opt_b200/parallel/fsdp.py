@@ -30,7 +30,7 @@ class FSDPPlan:
     reduce_dtype: torch.dtype = torch.float32
     transport: str = "auto"
     codec_version: str = "auto"
-    wire: str = "nibble"             # fused transport: "nibble" | "compressed" (bit planes) | "verbatim" (raw bf16)
+    wire: str = "auto"               # "auto" (nibble on the fused transport, bit planes on lib) | "nibble" | "compressed" | "verbatim"
     error_feedback: bool = True
     act_ckpt: bool = False
     mesh: Optional[object] = None

@@ -54,7 +54,16 @@ def _resolve_transport(transport: str, device: torch.device, group) -> str:
 
 # what the fused transport moves: v2 records with bit planes (smallest), v2 records in nibble mode
 # (about 7 % larger, roughly half the codec instructions), or the raw bf16 bytes
-WIRES = ("compressed", "nibble", "verbatim")
+WIRES = ("auto", "compressed", "nibble", "verbatim")
+
+
+def _resolve_wire(wire: str, transport: str) -> str:
+    """``"auto"``: nibble-mode records where the links have bandwidth to spare and the codec's instructions are
+    what a collective costs (the fused NVLink transport), bit-plane records (the smallest wire) on the
+    library transport, which is the one that crosses slower links."""
+    if wire != "auto":
+        return wire
+    return "nibble" if transport == "symm" else "compressed"
 
 
 class _CommBase:
@@ -147,7 +156,8 @@ class ZipCCLAllGather(_CommBase):
     are gathered with two collectives and no host sync; on ``"symm"`` only the used bytes of each
     record cross NVLink.
 
-    ``wire`` (fused ``"symm"`` transport only): ``"nibble"`` (default) moves v2 records with 4-bit codes
+    ``wire``: ``"auto"`` (default) is ``"nibble"`` on the fused ``"symm"`` transport and ``"compressed"`` on
+    ``"lib"``.  ``"nibble"`` moves v2 records with 4-bit codes
     packed two per byte and the window anchored at the chunk's largest exponent (1.42-1.50 bytes per
     element, lossless, roughly half the codec instructions of the bit-plane layout: measured 3 %
     faster per Llama-3-8B step at four GPUs, where the links are not the bottleneck);
@@ -165,7 +175,7 @@ class ZipCCLAllGather(_CommBase):
     ELEMS_PER_BLOCK = codec.ELEMS_PER_BLOCK
 
     def __init__(self, base_exponent: int = 122, base_update_interval: int = 16, *,
-                 codec_version: str = "auto", transport: str = "auto", wire: str = "nibble"):
+                 codec_version: str = "auto", transport: str = "auto", wire: str = "auto"):
         if wire not in WIRES:
             raise ValueError(f"unknown wire format {wire!r}")
         self.wire = wire
@@ -223,7 +233,7 @@ class ZipCCLAllGather(_CommBase):
             from . import symm_impl as symm
 
             return symm.channel_for(group, x.device, "ag").all_gather(
-                output_tensor, x, mode="zip", async_op=async_op, urgent=self.urgent, wire=self.wire,
+                output_tensor, x, mode="zip", async_op=async_op, urgent=self.urgent, wire=_resolve_wire(self.wire, "symm"),
                 exclusive=self.exclusive)
         if self.wire == "verbatim":
             return dist.all_gather_into_tensor(output_tensor, x, group=group, async_op=async_op)
@@ -238,7 +248,7 @@ class ZipCCLAllGather(_CommBase):
         dev = x.device
         rec_all = torch.empty(world, nc * codec.V2_SLOT, dtype=torch.uint8, device=dev)
         hdr_all = torch.empty(world, nc, dtype=torch.int32, device=dev)
-        nib = self.wire == "nibble"
+        nib = _resolve_wire(self.wire, "lib") == "nibble"
         codec.v2_encode(x.view(-1), rec_all[rank], hdr_all[rank], nibble=nib)
         w1 = dist.all_gather_into_tensor(rec_all.view(-1), rec_all[rank], group=group, async_op=async_op)
         w2 = dist.all_gather_into_tensor(hdr_all.view(-1), hdr_all[rank], group=group, async_op=async_op)
@@ -336,7 +346,7 @@ class ZipCCLReduceScatter(_CommBase):
     """
 
     def __init__(self, error_feedback: bool = True, reduce_dtype: Optional[torch.dtype] = None, *,
-                 residual_dtype: torch.dtype = torch.bfloat16, transport: str = "auto", wire: str = "nibble"):
+                 residual_dtype: torch.dtype = torch.bfloat16, transport: str = "auto", wire: str = "auto"):
         if wire not in WIRES:
             raise ValueError(f"unknown wire format {wire!r}")
         self.wire = wire
@@ -386,7 +396,7 @@ class ZipCCLReduceScatter(_CommBase):
 
             return symm.channel_for(group, x.device, "rs").reduce_scatter(
                 output_tensor, x, scale=scale, residual=self._residual_for(x), async_op=async_op, urgent=self.urgent,
-                wire=self.wire, exclusive=self.exclusive)
+                wire=_resolve_wire(self.wire, "symm"), exclusive=self.exclusive)
         return self._lib(output_tensor, x, group, world, scale, async_op)
 
     def _lib(self, output_tensor, x, group, world, scale, async_op):
@@ -409,7 +419,7 @@ class ZipCCLReduceScatter(_CommBase):
         send_hdr = torch.empty(world, nc, dtype=torch.int32, device=dev)
         for j in range(world):
             if j != rank:
-                codec.v2_encode(q[j].contiguous(), send_rec[j], send_hdr[j], nibble=self.wire == "nibble")
+                codec.v2_encode(q[j].contiguous(), send_rec[j], send_hdr[j], nibble=_resolve_wire(self.wire, "lib") == "nibble")
         send_hdr[rank].zero_()
         recv_rec = torch.empty_like(send_rec)
         recv_hdr = torch.empty_like(send_hdr)
@@ -425,7 +435,7 @@ class ZipCCLReduceScatter(_CommBase):
                 if j == rank:
                     acc += own.to(torch.float32)
                 else:
-                    codec.v2_decode(recv_rec[j], recv_hdr[j], shard, tmp, nibble=self.wire == "nibble")
+                    codec.v2_decode(recv_rec[j], recv_hdr[j], shard, tmp, nibble=_resolve_wire(self.wire, "lib") == "nibble")
                     acc += tmp.to(torch.float32)
             if scale != 1.0:
                 acc *= scale

@@ -183,6 +183,14 @@ def _verbatim_case(rank, world):
     ZipCCLReduceScatter(wire="verbatim")(o1, rows.clone(), dist.group.WORLD, dist.ReduceOp.AVG)
     ZipCCLReduceScatter()(o2, rows.clone(), dist.group.WORLD, dist.ReduceOp.AVG)
     assert torch.equal(o1, o2)
+    # nibble-mode records on the library transport's v2 protocol: still bit exact, same reduce-scatter result
+    out_n = torch.zeros_like(out)
+    hook_n = ZipCCLAllGather(wire="nibble", codec_version="v2")
+    hook_n(out_n, x, dist.group.WORLD)
+    assert torch.equal(_bits(out_n), _bits(ref))
+    o3 = torch.zeros(3000)
+    ZipCCLReduceScatter(wire="nibble")(o3, rows.clone(), dist.group.WORLD, dist.ReduceOp.AVG)
+    assert torch.equal(o3, o2)
     with pytest.raises(ValueError):
         ZipCCLAllGather(wire="zstd")
 

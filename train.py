@@ -11,7 +11,8 @@ optimizer / LR step -> zero_grad -> profiler step -> logging -> checkpoint), and
   --act-ckpt                    activation checkpointing per decoder block
   --steps N                     stop after N optimizer steps
   --transport / --codec         symm | lib | auto,  v1 | v2 | auto
-  --wire                        nibble | compressed | verbatim (fused transport: cheap 4-bit codes, bit planes, raw bf16)
+  --wire                        auto | nibble | compressed | verbatim (cheap 4-bit codes, bit planes, raw bf16;
+                                auto = nibble on the fused transport, bit planes on the library transport)
   --master-dtype fp32           keep fp32 master weights (communication stays bf16)
   --sharding {flat,fsdp2}       the package's flat-shard ZeRO-3 engine (default) or PyTorch FSDP2
                                 (the reference's wrapping; chosen automatically for --cpu-offload)
@@ -87,7 +88,7 @@ def _get_parser() -> argparse.ArgumentParser:
     p.add_argument("--steps", default=None, type=int)
     p.add_argument("--transport", default="auto", choices=["auto", "symm", "lib"])
     p.add_argument("--codec", default="auto", choices=["auto", "v1", "v2"])
-    p.add_argument("--wire", default="nibble", choices=["nibble", "compressed", "verbatim"],
+    p.add_argument("--wire", default="auto", choices=["auto", "nibble", "compressed", "verbatim"],
                    help="what the fused collectives move: lossless exponent-coded records with 4-bit codes (nibble), "
                         "with bit planes (compressed: smallest wire, more codec work), or the raw bf16 bytes on the "
                         "same one-kernel protocol (verbatim)")
