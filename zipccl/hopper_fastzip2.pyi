@@ -24,27 +24,27 @@ from torch import Tensor
 # fused layout: one stream per work holding the deterministic part followed by its outliers
 # --------------------------------------------------------------------------------------------
 
-def compress_8(
-    input: Tensor,                  # bf16 [sum(n_8)]: the works' values back to back
-    n_8: Tensor,                    # int32 [n_works]: elements per work (multiples of 4096)
-    nbytes_8: Tensor,               # int32 [n_works], OUT: bytes of each work's stream (128-aligned)
-    bases_in: Tensor,               # int32 [256]: window base in [0]
-    output: Tensor,                 # uint8 scratch, at least 4 bytes per input element
-    output_final: Tensor,           # uint8, OUT: the streams, work i at the sum of nbytes_8[:i]
-    global_zero_counter_8: Tensor,  # int32 [n_works], OUT: outlier count of each work
-    n_works: int,
-) -> None:
-    """Encode ``n_works`` works into one compact stream each (deterministic part, then outliers)."""
+def compress_8(input: Tensor, n_8: Tensor, nbytes_8: Tensor, bases_in: Tensor, output: Tensor, output_final: Tensor, global_zero_counter_8: Tensor, n_works: int) -> None:
+    """Encode ``n_works`` works into one compact stream each (deterministic part, then outliers).
+
+    input: bf16 [sum(n_8)]: the works' values back to back
+    n_8: int32 [n_works]: elements per work (multiples of 4096)
+    nbytes_8: int32 [n_works], OUT: bytes of each work's stream (128-aligned)
+    bases_in: int32 [256]: window base in [0]
+    output: uint8 scratch, at least 4 bytes per input element
+    output_final: uint8, OUT: the streams, work i at the sum of nbytes_8[:i]
+    global_zero_counter_8: int32 [n_works], OUT: outlier count of each work
+    """
     ...
 
-def decompress_8(
-    compressed_input: Tensor,       # uint8: streams as written by compress_8
-    n_8: Tensor,                    # int32 [n_works]
-    nbytes_8: Tensor,               # int32 [n_works]: stream sizes from compress_8
-    output: Tensor,                 # bf16 [sum(n_8)], OUT
-    n_works: int,
-) -> None:
-    """Inverse of :func:`compress_8`."""
+def decompress_8(compressed_input: Tensor, n_8: Tensor, nbytes_8: Tensor, output: Tensor, n_works: int) -> None:
+    """Inverse of :func:`compress_8`.
+
+    compressed_input: uint8: streams as written by compress_8
+    n_8: int32 [n_works]
+    nbytes_8: int32 [n_works]: stream sizes from compress_8
+    output: bf16 [sum(n_8)], OUT
+    """
     ...
 
 def compress_8_padded(input: Tensor, bases_in: Tensor, n_works: int = ...) -> Tensor:
@@ -59,15 +59,15 @@ def decompress_8_padded(compressed_input: Tensor, orig_numel: int, nbytes_8: Ten
     block offsets, so its size is not needed to decode it."""
     ...
 
-def decompress_8_unpad(
-    compressed_input: Tensor,       # uint8: streams as written by compress_8
-    n_8: Tensor,                    # int32 [n_works]: padded element counts
-    nbytes_8: Tensor,               # int32 [n_works]
-    output: Tensor,                 # bf16 [n_works * orig_ele_num], OUT: works packed without padding
-    orig_ele_num: int,              # elements to keep from the start of every work
-    n_works: int,
-) -> None:
-    """Decode and drop each work's padding: work ``i`` lands at ``output[i * orig_ele_num]``."""
+def decompress_8_unpad(compressed_input: Tensor, n_8: Tensor, nbytes_8: Tensor, output: Tensor, orig_ele_num: int, n_works: int) -> None:
+    """Decode and drop each work's padding: work ``i`` lands at ``output[i * orig_ele_num]``.
+
+    compressed_input: uint8: streams as written by compress_8
+    n_8: int32 [n_works]: padded element counts
+    nbytes_8: int32 [n_works]
+    output: bf16 [n_works * orig_ele_num], OUT: works packed without padding
+    orig_ele_num: elements to keep from the start of every work
+    """
     ...
 
 # --------------------------------------------------------------------------------------------
@@ -75,71 +75,58 @@ def decompress_8_unpad(
 # a gather can move the fixed-size parts first and size the second transfer from the counts
 # --------------------------------------------------------------------------------------------
 
-def compress_split_store(
-    input: Tensor,                  # bf16 [sum(n_8)]
-    n_8: Tensor,                    # int32 [n_works]
-    bases_in: Tensor,               # int32 [256]
-    output: Tensor,                 # uint8, OUT: deterministic parts, work i at sum(align128(det_bytes(n_8[:i])))
-    output1: Tensor,                # uint8 scratch, one byte per input element
-    output_final: Tensor,           # uint8, OUT: outlier bytes, work i at sum(align128(count[:i]))
-    global_zero_counter_8: Tensor,  # int32 [n_works], OUT: outlier count of each work
-    n_works: int,
-) -> None:
-    """Encode into the split layout."""
+def compress_split_store(input: Tensor, n_8: Tensor, bases_in: Tensor, output: Tensor, output1: Tensor, output_final: Tensor, global_zero_counter_8: Tensor, n_works: int) -> None:
+    """Encode into the split layout.
+
+    input: bf16 [sum(n_8)]
+    n_8: int32 [n_works]
+    bases_in: int32 [256]
+    output: uint8, OUT: deterministic parts, work i at sum(align128(det_bytes(n_8[:i])))
+    output1: uint8 scratch, one byte per input element
+    output_final: uint8, OUT: outlier bytes, work i at sum(align128(count[:i]))
+    global_zero_counter_8: int32 [n_works], OUT: outlier count of each work
+    """
     ...
 
-def decompress_split_store(
-    compressed_input: Tensor,       # uint8: deterministic parts
-    zero_input: Tensor,             # uint8: outlier bytes, work i at sum(align128(nbytes_8[:i]))
-    n_8: Tensor,                    # int32 [n_works]
-    nbytes_8: Tensor,               # int32 [n_works]: outlier bytes (or the stride) of each work
-    output: Tensor,                 # bf16 [sum(n_8)], OUT
-    n_works: int,
-) -> None:
-    """Inverse of :func:`compress_split_store`."""
+def decompress_split_store(compressed_input: Tensor, zero_input: Tensor, n_8: Tensor, nbytes_8: Tensor, output: Tensor, n_works: int) -> None:
+    """Inverse of :func:`compress_split_store`.
+
+    compressed_input: uint8: deterministic parts
+    zero_input: uint8: outlier bytes, work i at sum(align128(nbytes_8[:i]))
+    n_8: int32 [n_works]
+    nbytes_8: int32 [n_works]: outlier bytes (or the stride) of each work
+    output: bf16 [sum(n_8)], OUT
+    """
     ...
 
-def decompress_split_store_unpad(
-    compressed_input: Tensor,
-    zero_input: Tensor,
-    n_8: Tensor,
-    nbytes_8: Tensor,
-    output: Tensor,                 # bf16 [n_works * orig_ele_num], OUT
-    orig_ele_num: int,              # elements to keep from the start of every work
-    n_works: int,
-) -> None:
+def decompress_split_store_unpad(compressed_input: Tensor, zero_input: Tensor, n_8: Tensor, nbytes_8: Tensor, output: Tensor, orig_ele_num: int, n_works: int) -> None:
     """Split-layout decode that drops the padding of every work (the all-gather's receive side: work
     ``i`` is rank ``i``'s shard and lands at ``output[i * orig_ele_num]``; any alignment of the
-    destination is accepted)."""
+    destination is accepted).
+
+    output: bf16 [n_works * orig_ele_num], OUT
+    orig_ele_num: elements to keep from the start of every work
+    """
     ...
 
-def decompress_split_store_unpad_v(
-    compressed_input: Tensor,
-    zero_input: Tensor,
-    n_8: Tensor,
-    nbytes_8: Tensor,
-    out_off: Tensor,                # int32 [n_works]: element offset of work i in `output`
-    orig_n_8: Tensor,               # int32 [n_works]: elements to keep from work i
-    output: Tensor,                 # bf16, OUT
-    padded_n_total: int,            # sum of n_8 (host-side copy, sizes the launch without a device read)
-    n_works: int,
-) -> None:
+def decompress_split_store_unpad_v(compressed_input: Tensor, zero_input: Tensor, n_8: Tensor, nbytes_8: Tensor, out_off: Tensor, orig_n_8: Tensor, output: Tensor, padded_n_total: int, n_works: int) -> None:
     """Variable form of :func:`decompress_split_store_unpad`: every work has its own kept length and
-    its own destination offset."""
+    its own destination offset.
+
+    out_off: int32 [n_works]: element offset of work i in `output`
+    orig_n_8: int32 [n_works]: elements to keep from work i
+    output: bf16, OUT
+    padded_n_total: sum of n_8 (host-side copy, sizes the launch without a device read)
+    """
     ...
 
-def compress_split_store_pad(
-    input: Tensor,                  # bf16 [sum(orig_n_8)]: the works' unpadded values back to back
-    n_8: Tensor,                    # int32 [n_works]: padded element counts (multiples of 4096)
-    orig_n_8: Tensor,               # int32 [n_works]: real element counts; the rest encodes as zeros
-    bases_in: Tensor,
-    output: Tensor,
-    output1: Tensor,
-    output_final: Tensor,
-    global_zero_counter_8: Tensor,
-    padded_n_total: int,            # sum of n_8 (host-side copy)
-    n_works: int,
-) -> None:
+def compress_split_store_pad(input: Tensor, n_8: Tensor, orig_n_8: Tensor, bases_in: Tensor, output: Tensor, output1: Tensor, output_final: Tensor, global_zero_counter_8: Tensor, padded_n_total: int, n_works: int) -> None:
     """Split-layout encode of works whose lengths are not multiples of 4096: the padding is supplied
-    by the encoder instead of a padded copy of the input."""
+    by the encoder instead of a padded copy of the input.
+
+    input: bf16 [sum(orig_n_8)]: the works' unpadded values back to back
+    n_8: int32 [n_works]: padded element counts (multiples of 4096)
+    orig_n_8: int32 [n_works]: real element counts; the rest encodes as zeros
+    padded_n_total: sum of n_8 (host-side copy)
+    """
     ...
