@@ -10,7 +10,7 @@ For total tensor sizes 2^20 .. 2^30 elements (powers of 4) it times
     bf16-representable values as FSDP produces them): fused symm kernel vs NCCL fp32
 and reports, per line of JSON: bus GB/s of both (nccl-tests convention: bytes * (W-1)/W / time, with
 the UNCOMPRESSED payload as bytes, so a compressed collective can exceed the link rate), the
-measured wire bytes per element, the max abs error against NCCL, and the achieved fraction of the
+measured wire bytes per element and the compression ratio they mean, the max abs error against NCCL, and the achieved fraction of the
 NVLink roofline (compressed bytes that must leave a GPU / 770 GB/s measured peer bandwidth).
 Timing: CUDA events on the launching stream, 2 warm-up calls, max over ranks; inputs alternate
 between two buffers so consecutive calls do not hit the same L2 lines for sizes under the L2.
@@ -92,6 +92,7 @@ def main():
                               "zip_bus_gbs": round(payload * (world - 1) / world / ms_z / 1e6, 1),
                               "nccl_bus_gbs": round(payload * (world - 1) / world / ms_n / 1e6, 1),
                               "wire_bytes_per_elem": None if wire_pe is None else round(wire_pe, 4),
+                              "compression_ratio_vs_bf16": None if not wire_pe else round(2.0 / wire_pe, 3),
                               "frac_of_nvlink_roofline": None if roof_ms is None else round(roof_ms / ms_z, 3),
                               "max_abs_err": err}), flush=True)
         del xs, out, ref
@@ -125,6 +126,7 @@ def main():
                               "zip_bus_gbs": round(payload * (world - 1) / world / ms_z / 1e6, 1),
                               "nccl_bus_gbs": round(payload * (world - 1) / world / ms_n / 1e6, 1),
                               "wire_bytes_per_elem": None if wire_pe is None else round(wire_pe, 4),
+                              "compression_ratio_vs_fp32": None if not wire_pe else round(4.0 / wire_pe, 3),
                               "frac_of_nvlink_roofline": None if roof_ms is None else round(roof_ms / ms_z, 3),
                               "max_abs_err": err}), flush=True)
         # ---------------- reduce-scatter of bf16 rows (what the flat-shard engine hands over) --------
